@@ -1,0 +1,118 @@
+/* C ABI of the B200 sparse-attention forward path (libswv_b200.so).
+ *
+ * The reference project (p-adema/sparse-wsi-vit) has no FFI layer: its operator
+ * boundary is two torch.autograd.Function classes that launch Triton kernels.
+ * Each entry point below replaces the device work of one of those launches and
+ * cites it as  <file>:<lines>  with
+ *   K = src/sparse_wsi_vit/models/deepseek_sparse_attention_kernels/kernels.py
+ *   M = src/sparse_wsi_vit/models/deepseek_sparse_attention.py
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers unless the name ends in `_host`.
+ *   - Strides are in ELEMENTS (not bytes), int64, order given per argument.
+ *   - The caller owns every buffer (inputs, outputs, workspace, status word);
+ *     no entry point allocates, frees or synchronises.  Work is enqueued on
+ *     `stream` (a cudaStream_t passed as void*).
+ *   - Return value: 0 on success, a negative SWV_ERR_* when an argument is
+ *     rejected before anything is launched.
+ *   - `status` points to one int32 in device memory, zeroed by the caller.
+ *     Kernels write a positive code there when a bounded device-side wait gave
+ *     up (see swv_strerror); the results of that call are then undefined.
+ *   - Re-entrant; no global mutable state.  Calls sharing a workspace, a mask
+ *     buffer or a status word must be ordered on the GPU by the caller.
+ */
+#ifndef SWV_B200_H_
+#define SWV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SWV_OK 0
+#define SWV_ERR_NULL (-1)        /* a required pointer is NULL                      */
+#define SWV_ERR_ALIGN (-2)       /* pointer/stride alignment the kernels cannot take */
+#define SWV_ERR_DTYPE (-3)       /* unsupported element type                        */
+#define SWV_ERR_SHAPE (-4)       /* non-positive or unsupported size                */
+#define SWV_ERR_WORKSPACE (-5)   /* workspace / mask buffer too small               */
+#define SWV_ERR_CUDA (-6)        /* a CUDA runtime call failed                      */
+#define SWV_ERR_TENSORMAP (-7)   /* the driver rejected a TMA descriptor            */
+#define SWV_ERR_UNSUPPORTED (-8) /* valid request this build has no kernel for      */
+
+#define SWV_F32 0
+#define SWV_BF16 1
+#define SWV_F16 2
+
+/* Library ABI version (major*100 + minor). */
+int swv_version(void);
+
+/* Text for a negative return code or a positive device status code. */
+const char* swv_strerror(int code);
+
+/* Bytes of scratch swv_dsa_indexer_topk_fwd / swv_dsa_forward need for B
+ * batches of Tq queries against Tk keys. */
+int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes);
+
+/* Bytes of the tile-major membership bitmask for B x Tq x Tk:
+ * [B][ceil(Tq/128)][ceil(Tk/128)][128 rows][4 x uint32]; bit c of word w of
+ * row r says whether key 128*kt + 32*w + c is selected for query 128*qt + r. */
+int swv_dsa_mask_bytes(int B, int Tq, int Tk, size_t* bytes);
+
+/* DSA lightning indexer + per-query top-k.
+ * Replaces LightningIndexerFunction.forward and its kernel (K:346-386, K:19-113):
+ *   score[q,k] = relu( (sum_h W[h] q_idx[q,h,:]) . (sum_h W[h] k_idx[k,h,:]) )
+ * (heads collapsed before the dot product, no scaling; TF32 tensor-core dot
+ * with fp32 accumulation, as the reference's tl.dot on fp32 operands), then
+ * for every query the top_k largest scores, ties broken towards the LOWER key
+ * index.  Outputs, each contiguous (B, Tq, top_k):
+ *   idx    int32  selected key indices in ASCENDING key order,
+ *   valid  f32    1.0 for the first min(top_k, Tk) slots, else 0.0,
+ *   scores f32    the score of each selected key (0 for unfilled slots).
+ * N x N scores never reach memory: four radix passes recompute score tiles on
+ * the tensor cores and keep per-row digit histograms on chip.
+ *   q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID): strides (b,t,h,d); dtype SWV_F32/BF16/F16.
+ *   w: (IH,) f32.   ID <= 64.   maskbits: optional (may be NULL) bitmask output
+ *   (see swv_dsa_mask_bytes) consumed by swv_dsa_attn_masked_fwd.
+ */
+int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], const void* k_idx,
+                             const int64_t k_strides[4], int idx_dtype, const float* w, int B, int Tq, int Tk,
+                             int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
+                             uint32_t* maskbits, void* workspace, size_t workspace_bytes, int* status,
+                             void* stream);
+
+/* Routing-weighted attention over an explicit per-query key list.
+ * Replaces DSAAttentionFunction.forward and its kernel (K:769-810, K:450-564):
+ *   logit_j = q . k[idx_j] / sqrt(D)  for valid_j > 0,   m = max_j logit_j,
+ *   p_j = exp(logit_j - m) * rw_j,    o = sum_j p_j v[idx_j] / max(sum_j p_j, 1e-6).
+ * Accepts any index list (unsorted, repeated entries count twice, as in the
+ * reference).  fp32 accumulation.
+ *   q (B,H,Tq,D), k, v (B,H,Tk,D): strides (b,h,t,d), last stride 1; dtype F32/BF16/F16.
+ *   idx int32, valid f32, rw f32: (B,Tq,top_k), strides (b,t,k).
+ *   o (B,H,Tq,D): strides (b,h,t,d); o_dtype F32/BF16/F16.  D in {32, 64, 128}.
+ */
+int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                            const void* v, const int64_t v_strides[4], int qkv_dtype, const int32_t* idx,
+                            const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3],
+                            const float* rw, const int64_t rw_strides[3], void* o, const int64_t o_strides[4],
+                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
+                            void* stream);
+
+/* Same arithmetic as swv_dsa_attn_gather_fwd for key lists produced by
+ * swv_dsa_indexer_topk_fwd in the same call sequence, computed as a dense
+ * tensor-core flash-attention sweep (tcgen05 QK^T and PV, TMA-fed) with the
+ * membership bitmask and the ascending-order scores applied inside the
+ * online softmax (M:73-85 fused).  bf16 q/k/v only, D == 64.
+ *   maskbits: as written by swv_dsa_indexer_topk_fwd for the same B,Tq,Tk.
+ *   weights : the `scores` output (routing weights; valid slots only).
+ */
+int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                            const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
+                            const float* weights, int top_k, void* o, const int64_t o_strides[4], int o_dtype,
+                            int B, int H, int Tq, int Tk, int D, int* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWV_B200_H_ */
