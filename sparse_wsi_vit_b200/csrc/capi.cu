@@ -1,0 +1,86 @@
+// extern "C" surface of libswv_b200.so (declared in include/swv_b200.h).
+// Plain pointers and sizes only; every function validates its arguments before
+// enqueuing work and never allocates or synchronises.
+#include "common.cuh"
+
+namespace swv {
+int dsa_workspace_bytes_impl(int B, int Tq, int Tk, size_t* bytes);
+int dsa_mask_bytes_impl(int B, int Tq, int Tk, size_t* bytes);
+int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks, int dtype,
+                          const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
+                          float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
+                          int* status, cudaStream_t st);
+int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                         const int64_t* vs, const uint32_t* maskbits, const float* weights, int top_k, void* o,
+                         const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
+                         cudaStream_t st);
+int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                         const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
+                         const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
+                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
+                         cudaStream_t st);
+}  // namespace swv
+
+extern "C" {
+
+int swv_version(void) { return 100; }
+
+const char* swv_strerror(int code) {
+  switch (code) {
+    case SWV_OK: return "ok";
+    case SWV_ERR_NULL: return "a required pointer is NULL";
+    case SWV_ERR_ALIGN: return "pointer or stride alignment not supported (need 16-byte aligned rows, unit inner stride)";
+    case SWV_ERR_DTYPE: return "unsupported element type";
+    case SWV_ERR_SHAPE: return "non-positive or unsupported size";
+    case SWV_ERR_WORKSPACE: return "workspace or mask buffer too small";
+    case SWV_ERR_CUDA: return "a CUDA runtime call failed";
+    case SWV_ERR_TENSORMAP: return "the driver rejected a TMA descriptor";
+    case SWV_ERR_UNSUPPORTED: return "no kernel in this build for the requested shape";
+    case swv::kDevWaitTmaFull: return "device: timed out waiting for a TMA tile";
+    case swv::kDevWaitStageEmpty: return "device: timed out waiting for a free shared-memory stage";
+    case swv::kDevWaitAccFull: return "device: timed out waiting for an accumulator tile";
+    case swv::kDevWaitAccEmpty: return "device: timed out waiting for a free accumulator";
+    case swv::kDevWaitPReady: return "device: timed out waiting for the probability tile";
+    case swv::kDevWaitPvDone: return "device: timed out waiting for the PV product";
+    case swv::kDevWaitQ: return "device: timed out waiting for the query tile";
+    case swv::kDevBadIndex: return "device: key index out of range";
+    default: return "unknown code";
+  }
+}
+
+int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes) {
+  return swv::dsa_workspace_bytes_impl(B, Tq, Tk, bytes);
+}
+
+int swv_dsa_mask_bytes(int B, int Tq, int Tk, size_t* bytes) { return swv::dsa_mask_bytes_impl(B, Tq, Tk, bytes); }
+
+int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], const void* k_idx,
+                             const int64_t k_strides[4], int idx_dtype, const float* w, int B, int Tq, int Tk,
+                             int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
+                             uint32_t* maskbits, void* workspace, size_t workspace_bytes, int* status,
+                             void* stream) {
+  return swv::dsa_indexer_topk_impl(q_idx, q_strides, k_idx, k_strides, idx_dtype, w, B, Tq, Tk, IH, ID, top_k, idx,
+                                    valid, scores, maskbits, workspace, workspace_bytes, status,
+                                    static_cast<cudaStream_t>(stream));
+}
+
+int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                            const void* v, const int64_t v_strides[4], int qkv_dtype, const int32_t* idx,
+                            const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3],
+                            const float* rw, const int64_t rw_strides[3], void* o, const int64_t o_strides[4],
+                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
+                            void* stream) {
+  return swv::dsa_attn_gather_impl(q, q_strides, k, k_strides, v, v_strides, qkv_dtype, idx, idx_strides, valid,
+                                   valid_strides, rw, rw_strides, o, o_strides, o_dtype, B, H, Tq, Tk, D, top_k,
+                                   status, static_cast<cudaStream_t>(stream));
+}
+
+int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                            const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
+                            const float* weights, int top_k, void* o, const int64_t o_strides[4], int o_dtype,
+                            int B, int H, int Tq, int Tk, int D, int* status, void* stream) {
+  return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, weights, top_k, o, o_strides,
+                                   o_dtype, B, H, Tq, Tk, D, status, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

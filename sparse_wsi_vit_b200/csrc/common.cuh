@@ -98,4 +98,20 @@ inline int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType 
   return r == CUDA_SUCCESS ? SWV_OK : SWV_ERR_TENSORMAP;
 }
 
+// rank-4 tiled map (d, t, h, b) with 128-byte swizzle; strides in BYTES for dims 1..3.
+inline int make_tmap_4d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, uint64_t d0, uint64_t d1,
+                        uint64_t d2, uint64_t d3, uint64_t s1, uint64_t s2, uint64_t s3, uint32_t box0,
+                        uint32_t box1) {
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return SWV_ERR_CUDA;
+  cuuint64_t dims[4] = {d0, d1, d2, d3};
+  cuuint64_t strides[3] = {s1, s2, s3};
+  cuuint32_t box[4] = {box0, box1, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SWV_OK : SWV_ERR_TENSORMAP;
+}
+
 }  // namespace swv

@@ -1,0 +1,480 @@
+// DSA lightning indexer + per-query top-k for sm_100a.
+//
+// Replaces the reference's `_indexer_fwd` Triton kernel
+// (src/sparse_wsi_vit/models/deepseek_sparse_attention_kernels/kernels.py:19-113).
+//
+// Pipeline (all on the caller's stream):
+//   1. collapse_heads_kernel : wq[t,:] = sum_h W[h] q_idx[t,h,:]  (and wk), fp32, padded to 64.
+//   2. indexer_tiles_kernel<HIST> x 4 : radix select, 8 bits per pass.  Each CTA owns 128
+//      query rows, streams all key tiles through TMA, recomputes the 128x128 score tile with
+//      tcgen05 TF32 MMAs into TMEM, and its epilogue warps keep a 256-bin histogram per row
+//      in shared memory.  After pass p each row knows 8 more bits of its K-th largest score.
+//   3. indexer_tiles_kernel<EMIT> : recomputes the tiles once more (bit-identical: same
+//      instruction sequence) and writes idx / scores in ascending key order plus the
+//      tile-major membership bitmask.  Ties at the threshold go to the lower key index.
+//   4. fill_valid_kernel : valid[.., s] = s < min(K, Tk); zero padding of idx/scores.
+// The N x N score matrix never reaches global memory.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace swv {
+
+// ------------------------------------------------------------------ collapse
+template <typename T>
+__device__ __forceinline__ float to_f32(T x);
+template <>
+__device__ __forceinline__ float to_f32<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <>
+__device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
+
+// out[(b*T + t)*64 + d] = sum_h w[h] * x[b,t,h,d]  (d < ID), 0 for ID <= d < 64.
+// Products are rounded before the sum (no FMA contraction), heads in ascending order.
+template <typename T>
+__global__ void collapse_heads_kernel(const T* __restrict__ x, int64_t sb, int64_t st, int64_t sh, int64_t sd,
+                                      const float* __restrict__ w, float* __restrict__ out, int B, int Tn, int IH,
+                                      int ID) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(B) * Tn * kIdxDim;
+  if (gid >= total) return;
+  const int d = static_cast<int>(gid % kIdxDim);
+  const int64_t bt = gid / kIdxDim;
+  const int t = static_cast<int>(bt % Tn);
+  const int b = static_cast<int>(bt / Tn);
+  float acc = 0.f;
+  if (d < ID) {
+    const T* p = x + b * sb + t * st + d * sd;
+    for (int h = 0; h < IH; ++h) {
+      acc = __fadd_rn(acc, __fmul_rn(to_f32<T>(p[h * sh]), w[h]));
+    }
+  }
+  out[gid] = acc;
+}
+
+// --------------------------------------------------------------- tile kernel
+constexpr int kModeHist = 0;
+constexpr int kModeEmit = 1;
+constexpr int kStages = 2;                         // wk ring depth
+constexpr int kTileBytes = kTile * kIdxDim * 4;    // 32 KiB fp32 tile (two 16 KiB K-halves)
+constexpr int kHistStride = 257;                   // words per histogram row (+1: bank spread)
+constexpr int kHistBytes = kTile * kHistStride * 4;
+constexpr int kTmemCols = 256;                     // two 128-column score buffers
+
+struct IndexerParams {
+  int B, Tq, Tk, top_k;
+  int nQT, nKT;
+  int pass;               // HIST: 0..3
+  uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
+  uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
+  int32_t* idx;           // EMIT outputs
+  float* scores;
+  uint32_t* maskbits;     // may be null
+  int* status;
+};
+
+struct TileSmemCtl {
+  uint64_t q_full;
+  uint64_t k_full[kStages];
+  uint64_t k_empty[kStages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+constexpr size_t tile_smem_bytes(int mode) {
+  return 1024 /*alignment slack*/ + kTileBytes * (1 + kStages) + (mode == kModeHist ? kHistBytes : 0) +
+         sizeof(TileSmemCtl) + 64;
+}
+
+__device__ __forceinline__ uint32_t relu_bits(uint32_t raw) {
+  const float x = __uint_as_float(raw);
+  return x > 0.f ? raw : 0u;   // -0, negatives and NaN all map to +0
+}
+
+// Adds the 64 scores of one thread (two 32-column TMEM chunks) to its row histogram.
+// Pass 0 bins on the top byte; later passes only count scores whose known high
+// bits equal `prefix` and bin on the next byte.  CHECK guards the ragged last key tile.
+template <bool CHECK>
+__device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint32_t (&r1)[32], uint32_t* hrow,
+                                            int pass, int shift, uint32_t prefix, int nvalid) {
+  if (pass == 0) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (!CHECK || i < nvalid) atomicAdd(hrow + (relu_bits(r0[i]) >> 24), 1u);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      if (!CHECK || i + 32 < nvalid) atomicAdd(hrow + (relu_bits(r1[i]) >> 24), 1u);
+    }
+  } else {
+    const int hs = shift + 8;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t u = relu_bits(r0[i]);
+      if ((!CHECK || i < nvalid) && (u >> hs) == prefix) atomicAdd(hrow + ((u >> shift) & 255u), 1u);
+    }
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const uint32_t u = relu_bits(r1[i]);
+      if ((!CHECK || i + 32 < nvalid) && (u >> hs) == prefix) atomicAdd(hrow + ((u >> shift) & 255u), 1u);
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHist ? 1 : 2)
+    indexer_tiles_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                         const IndexerParams p) {
+  constexpr int kEpiWarps = MODE == kModeHist ? 8 : 4;
+  constexpr uint32_t kIdesc = make_idesc(/*tf32*/ 2, kTile, kTile, 0, 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sm_q = smem;
+  uint8_t* sm_k = smem + kTileBytes;
+  uint32_t* sm_hist = reinterpret_cast<uint32_t*>(smem + kTileBytes * (1 + kStages));
+  TileSmemCtl* ctl = reinterpret_cast<TileSmemCtl*>(smem + kTileBytes * (1 + kStages) +
+                                                    (MODE == kModeHist ? kHistBytes : 0));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int b = blockIdx.x / p.nQT;
+  const int qt = blockIdx.x % p.nQT;
+  const int nKT = p.nKT;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&ctl->q_full, 1);
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&ctl->k_full[s], 1);
+      mbar_init(&ctl->k_empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&ctl->acc_full[a], 1);
+      mbar_init(&ctl->acc_empty[a], kEpiWarps);
+    }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      mbar_expect_tx(&ctl->q_full, kTileBytes);
+      tma_load_3d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, b);
+      tma_load_3d(sm_q + kTileBytes / 2, &tm_q, &ctl->q_full, 32, qt * kTile, b);
+      for (int j = 0; j < nKT; ++j) {
+        const int s = j % kStages;
+        if (!mbar_wait_bounded(&ctl->k_empty[s], ((j / kStages) & 1) ^ 1, abort_flag)) {
+          record_status(p.status, kDevWaitStageEmpty);
+          break;
+        }
+        uint8_t* dst = sm_k + s * kTileBytes;
+        mbar_expect_tx(&ctl->k_full[s], kTileBytes);
+        tma_load_3d(dst, &tm_k, &ctl->k_full[s], 0, j * kTile, b);
+        tma_load_3d(dst + kTileBytes / 2, &tm_k, &ctl->k_full[s], 32, j * kTile, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
+      if (!ok) record_status(p.status, kDevWaitQ);
+      const uint32_t q_addr = smem_u32(sm_q);
+      for (int j = 0; ok && j < nKT; ++j) {
+        const int s = j % kStages;
+        const int a = j & 1;
+        if (!mbar_wait_bounded(&ctl->k_full[s], (j / kStages) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitTmaFull);
+          break;
+        }
+        if (!mbar_wait_bounded(&ctl->acc_empty[a], ((j >> 1) & 1) ^ 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccEmpty);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(sm_k + s * kTileBytes);
+        const uint32_t d_tmem = tmem_base + a * kTile;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t off = (ks >> 2) * (kTileBytes / 2) + (ks & 3) * 32;
+          umma_tf32_ss(d_tmem, smem_desc_sw128(q_addr + off), smem_desc_sw128(k_addr + off), kIdesc, ks > 0);
+        }
+        umma_commit(&ctl->k_empty[s]);
+        umma_commit(&ctl->acc_full[a]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;                 // 0..kEpiWarps-1
+    const int quarter = warp & 3;            // TMEM lane quarter this warp may touch
+    const int row = quarter * 32 + lane;     // row inside the query tile
+    const int qrow = qt * kTile + row;       // query index
+    const bool row_ok = qrow < p.Tq;
+    const int64_t grow = static_cast<int64_t>(b) * p.Tq + qrow;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    bool ok = true;
+
+    if constexpr (MODE == kModeHist) {
+      const int ch = ew >> 2;                // column half 0/1
+      const int et = threadIdx.x - 64;       // 0..255
+      for (int i = et; i < kTile * kHistStride; i += 256) sm_hist[i] = 0u;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+
+      const int pass = p.pass;
+      const int shift = 24 - 8 * pass;
+      const uint32_t prefix = (pass > 0 && row_ok) ? p.st_prefix[grow] : 0u;
+      uint32_t* hrow = sm_hist + row * kHistStride;
+
+      for (int j = 0; j < nKT; ++j) {
+        const int a = j & 1;
+        if (!mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t r0[32], r1[32];
+        const uint32_t taddr = lane_base + a * kTile + ch * 64;
+        tmem_ld32(taddr, r0);
+        tmem_ld32(taddr + 32, r1);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
+
+        const int nvalid = p.Tk - (j * kTile + ch * 64);   // columns of this half that are real keys
+        if (nvalid >= 64) {
+          hist_update<false>(r0, r1, hrow, pass, shift, prefix, 64);
+        } else {
+          hist_update<true>(r0, r1, hrow, pass, shift, prefix, nvalid);
+        }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (ok && ch == 0 && row_ok && *abort_flag == 0u) {
+        uint32_t kth = pass == 0 ? static_cast<uint32_t>(min(p.top_k, p.Tk)) : p.st_kth[grow];
+        uint32_t cum = 0;
+        int digit = 0;
+        for (int bin = 255; bin >= 0; --bin) {
+          const uint32_t c = hrow[bin];
+          if (cum + c >= kth) {
+            digit = bin;
+            break;
+          }
+          cum += c;
+        }
+        p.st_prefix[grow] = (prefix << 8) | static_cast<uint32_t>(digit);
+        p.st_kth[grow] = kth - cum;
+      }
+    } else {
+      // EMIT: one thread per query row, all 128 columns of every tile, ascending keys.
+      const uint32_t thr = row_ok ? p.st_prefix[grow] : 0xFFFFFFFFu;
+      const uint32_t take_eq = row_ok ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
+      uint32_t eq_seen = 0;
+      int cnt = 0;
+      int32_t* idx_row = p.idx + grow * p.top_k;
+      float* sc_row = p.scores + grow * p.top_k;
+      uint4* mask_row = nullptr;
+      if (p.maskbits != nullptr) {
+        mask_row = reinterpret_cast<uint4*>(p.maskbits) +
+                   (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
+      }
+      for (int j = 0; j < nKT; ++j) {
+        const int a = j & 1;
+        if (!mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t words[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld32(lane_base + a * kTile + c * 32, r);
+          tc_wait_ld();
+          if (c == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
+          }
+          const int key0 = j * kTile + c * 32;
+          const int nvalid = p.Tk - key0;
+          uint32_t w = 0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t u = relu_bits(r[i]);
+            bool member = u > thr;
+            if (u == thr && i < nvalid) {
+              member = eq_seen < take_eq;
+              ++eq_seen;
+            }
+            member = member && (i < nvalid);
+            if (member) {
+              w |= 1u << i;
+              if (row_ok && cnt < p.top_k) {
+                idx_row[cnt] = key0 + i;
+                sc_row[cnt] = __uint_as_float(u);
+              }
+              ++cnt;
+            }
+          }
+          words[c] = w;
+        }
+        if (mask_row != nullptr) {
+          mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(words[0], words[1], words[2], words[3]);
+        }
+      }
+      (void)ok;
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// valid[b,t,s] = s < k_eff ; slots >= k_eff of idx / scores are zeroed.
+__global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict__ idx, float* __restrict__ scores,
+                                  int64_t total, int top_k, int k_eff) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= total) return;
+  const int s = static_cast<int>(gid % top_k);
+  const bool filled = s < k_eff;
+  valid[gid] = filled ? 1.f : 0.f;
+  if (!filled) {
+    idx[gid] = 0;
+    scores[gid] = 0.f;
+  }
+}
+
+// -------------------------------------------------------------------- host
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+struct WorkspaceLayout {
+  size_t wq_off, wk_off, prefix_off, kth_off, total;
+};
+static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
+  WorkspaceLayout L;
+  size_t off = 0;
+  L.wq_off = off;
+  off += align_up(static_cast<size_t>(B) * Tq * kIdxDim * 4, 1024);
+  L.wk_off = off;
+  off += align_up(static_cast<size_t>(B) * Tk * kIdxDim * 4, 1024);
+  L.prefix_off = off;
+  off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+  L.kth_off = off;
+  off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+  L.total = off;
+  return L;
+}
+
+template <typename T>
+static void launch_collapse(const void* x, const int64_t* s, const float* w, float* out, int B, int Tn, int IH,
+                            int ID, cudaStream_t st) {
+  const int64_t total = static_cast<int64_t>(B) * Tn * kIdxDim;
+  const int threads = 256;
+  const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
+  collapse_heads_kernel<T><<<blocks, threads, 0, st>>>(static_cast<const T*>(x), s[0], s[1], s[2], s[3], w, out, B,
+                                                         Tn, IH, ID);
+}
+
+int dsa_workspace_bytes_impl(int B, int Tq, int Tk, size_t* bytes) {
+  if (bytes == nullptr) return SWV_ERR_NULL;
+  if (B < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
+  *bytes = workspace_layout(B, Tq, Tk).total;
+  return SWV_OK;
+}
+
+int dsa_mask_bytes_impl(int B, int Tq, int Tk, size_t* bytes) {
+  if (bytes == nullptr) return SWV_ERR_NULL;
+  if (B < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
+  const size_t nQT = (Tq + kTile - 1) / kTile, nKT = (Tk + kTile - 1) / kTile;
+  *bytes = static_cast<size_t>(B) * nQT * nKT * kTile * 16;
+  return SWV_OK;
+}
+
+int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks, int dtype,
+                          const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
+                          float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
+                          int* status, cudaStream_t st) {
+  if (!q_idx || !k_idx || !w || !idx || !valid || !scores || !workspace || !status || !qs || !ks)
+    return SWV_ERR_NULL;
+  if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
+  if (B < 1 || Tq < 1 || Tk < 1 || IH < 1 || ID < 1 || top_k < 1) return SWV_ERR_SHAPE;
+  if (ID > kIdxDim) return SWV_ERR_UNSUPPORTED;
+  const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
+  if (workspace_bytes < L.total) return SWV_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 1023) != 0) return SWV_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(idx) & 3) || (reinterpret_cast<uintptr_t>(scores) & 3) ||
+      (reinterpret_cast<uintptr_t>(valid) & 3) || (maskbits && (reinterpret_cast<uintptr_t>(maskbits) & 15)))
+    return SWV_ERR_ALIGN;
+
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* wq = reinterpret_cast<float*>(ws + L.wq_off);
+  float* wk = reinterpret_cast<float*>(ws + L.wk_off);
+
+  CUtensorMap tm_q, tm_k;
+  int rc = make_tmap_3d(&tm_q, wq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kIdxDim, Tq, B, kIdxDim * 4,
+                        static_cast<uint64_t>(Tq) * kIdxDim * 4, 32, kTile);
+  if (rc != SWV_OK) return rc;
+  rc = make_tmap_3d(&tm_k, wk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kIdxDim, Tk, B, kIdxDim * 4,
+                    static_cast<uint64_t>(Tk) * kIdxDim * 4, 32, kTile);
+  if (rc != SWV_OK) return rc;
+
+  if (dtype == SWV_F32) {
+    launch_collapse<float>(q_idx, qs, w, wq, B, Tq, IH, ID, st);
+    launch_collapse<float>(k_idx, ks, w, wk, B, Tk, IH, ID, st);
+  } else if (dtype == SWV_BF16) {
+    launch_collapse<__nv_bfloat16>(q_idx, qs, w, wq, B, Tq, IH, ID, st);
+    launch_collapse<__nv_bfloat16>(k_idx, ks, w, wk, B, Tk, IH, ID, st);
+  } else {
+    launch_collapse<__half>(q_idx, qs, w, wq, B, Tq, IH, ID, st);
+    launch_collapse<__half>(k_idx, ks, w, wk, B, Tk, IH, ID, st);
+  }
+
+  IndexerParams p;
+  p.B = B; p.Tq = Tq; p.Tk = Tk; p.top_k = top_k;
+  p.nQT = (Tq + kTile - 1) / kTile;
+  p.nKT = (Tk + kTile - 1) / kTile;
+  p.st_prefix = reinterpret_cast<uint32_t*>(ws + L.prefix_off);
+  p.st_kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
+  p.idx = idx; p.scores = scores; p.maskbits = maskbits; p.status = status; p.pass = 0;
+
+  SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeHist>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(tile_smem_bytes(kModeHist))));
+  SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(tile_smem_bytes(kModeEmit))));
+  const unsigned grid = static_cast<unsigned>(B) * p.nQT;
+  for (int pass = 0; pass < 4; ++pass) {
+    p.pass = pass;
+    indexer_tiles_kernel<kModeHist><<<grid, 320, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
+  }
+  indexer_tiles_kernel<kModeEmit><<<grid, 192, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
+
+  const int64_t total = static_cast<int64_t>(B) * Tq * top_k;
+  fill_valid_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(valid, idx, scores, total, top_k,
+                                                                                   top_k < Tk ? top_k : Tk);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+}  // namespace swv

@@ -2,18 +2,15 @@
 // tcgen05 (TMEM allocation, UMMA issue/commit, TMEM load/store) and the shared
 // memory / instruction descriptors the UMMA instructions take.
 //
-// Every wait in this file is BOUNDED: after `kSpinLimit` polls the caller gets
-// `false`, records an error code in the kernel's status word and unwinds, so a
-// protocol bug shows up as an error return instead of a hung GPU.
+// Waiting on an mbarrier is exposed only as the non-blocking `mbar_try_wait`;
+// the time-bounded wait loop built on it lives in common.cuh, so a protocol
+// bug shows up as an error status instead of a hung GPU.
 #pragma once
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_runtime.h>
 
 namespace swv {
-
-// ~1-2 s worth of polls (each try_wait may itself block for a HW-defined time slice).
-constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -47,13 +44,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
-  return false;
-}
 
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
@@ -63,6 +53,13 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* m, uin
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z,
+                                            int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* m, uint64_t* bar, int x, int y, int z) {
@@ -139,7 +136,7 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 
 // Instruction descriptor for kind::f16 / kind::tf32, fp32 accumulate.
 //   fmt: 0 = f16, 1 = bf16, 2 = tf32.   major: 0 = K-major, 1 = MN-major.
-constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_major, uint32_t b_major) {
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_major, uint32_t b_major) {
   return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_major << 15) | (b_major << 16) | ((n >> 3) << 17) |
          ((m >> 4) << 24);
 }

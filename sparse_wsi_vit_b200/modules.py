@@ -1,0 +1,135 @@
+"""Drop-in nn.Modules for the DSA slide encoder.
+
+Constructor arguments, forward signatures, parameter names and shapes follow
+src/sparse_wsi_vit/models/deepseek_sparse_attention.py of the reference
+(DeepSeekSparseAttention :19-88, IndexerProjection :93-105, DSAViTBlock :108-166,
+DSAViTSlideEncoder :169-305) so that a reference ``state_dict`` loads unchanged
+and configs that name these classes keep working.  The attention itself runs on
+the sm_100a kernels (``ops.dsa_sparse_attention``); projections, LayerNorm and
+the MLP stay PyTorch/cuBLAS.  Forward only.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from .ops import dsa_sparse_attention
+
+
+class IndexerProjection(nn.Module):
+    """Two Linears producing the indexer queries/keys, (B, T, IH, ID) each."""
+
+    def __init__(self, d_model, indexer_heads, indexer_dim):
+        super().__init__()
+        self.indexer_heads = indexer_heads
+        self.indexer_dim = indexer_dim
+        self.q_proj = nn.Linear(d_model, indexer_heads * indexer_dim)
+        self.k_proj = nn.Linear(d_model, indexer_heads * indexer_dim)
+
+    def forward(self, x):
+        shape = (*x.shape[:2], self.indexer_heads, self.indexer_dim)
+        return self.q_proj(x).view(shape), self.k_proj(x).view(shape)
+
+
+class DeepSeekSparseAttention(nn.Module):
+    """Token-level top-k sparse attention with a lightning indexer.
+
+    ``BLOCK_Q/BLOCK_K/BLOCK_D`` are the reference's Triton tile sizes; they are
+    accepted for signature compatibility and ignored.
+    """
+
+    def __init__(self, d_model, attention_heads, indexer_heads, indexer_dim, top_k, BLOCK_Q=None, BLOCK_K=None,
+                 BLOCK_D=None):
+        super().__init__()
+        if d_model % attention_heads != 0:
+            raise ValueError(f"d_model ({d_model}) must be divisible by attention_heads ({attention_heads})")
+        self.d_model = d_model
+        self.attention_heads = attention_heads
+        self.head_dim = d_model // attention_heads
+        self.indexer_heads = indexer_heads
+        self.indexer_dim = indexer_dim
+        self.top_k = top_k
+        self.BLOCK_Q, self.BLOCK_K, self.BLOCK_D = BLOCK_Q, BLOCK_K, BLOCK_D
+
+        self.indexer_head_weights = nn.Parameter(torch.randn(indexer_heads))
+        self.indexer_proj = IndexerProjection(d_model, indexer_heads, indexer_dim)
+        self.qkv_proj = nn.Linear(d_model, 3 * d_model)
+        self.out_proj = nn.Linear(d_model, d_model)
+
+    def forward(self, x):
+        B, T, _ = x.shape
+        H, D = self.attention_heads, self.head_dim
+        # [q | k | v] outermost, then head, then head-dim; the kernels take the
+        # (B, H, T, D) views as they are (strided), no contiguous copies.
+        qkv = self.qkv_proj(x).view(B, T, 3, H, D)
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        q_idx, k_idx = self.indexer_proj(x)
+        o = dsa_sparse_attention(q, k, v, q_idx, k_idx, self.indexer_head_weights, self.top_k, out_dtype=x.dtype)
+        return self.out_proj(o.transpose(1, 2).reshape(B, T, H * D).to(x.dtype))
+
+
+class DSAViTBlock(nn.Module):
+    """Pre-norm transformer block: x + attn(LN(x)); x + MLP(LN(x))."""
+
+    def __init__(self, embed_dim: int, num_heads: int, indexer_heads: int = 4, indexer_dim: int = 32,
+                 top_k: int = 512, block_q: int = 16, block_k: int = 32, block_d: int = 32,
+                 expansion_factor: float = 4.0, attn_dropout: float = 0.0, proj_dropout: float = 0.0) -> None:
+        super().__init__()
+        hidden = int(embed_dim * expansion_factor)
+        self.norm1 = nn.LayerNorm(embed_dim)
+        self.attn = DeepSeekSparseAttention(embed_dim, num_heads, indexer_heads, indexer_dim, top_k, block_q,
+                                            block_k, block_d)
+        self.drop1 = nn.Dropout(proj_dropout)
+        self.norm2 = nn.LayerNorm(embed_dim)
+        self.mlp = nn.Sequential(nn.Linear(embed_dim, hidden), nn.GELU(), nn.Dropout(proj_dropout),
+                                 nn.Linear(hidden, embed_dim), nn.Dropout(proj_dropout))
+
+    def forward(self, x: Tensor) -> Tensor:
+        x = x + self.drop1(self.attn(self.norm1(x)))
+        return x + self.mlp(self.norm2(x))
+
+
+class DSAViTSlideEncoder(nn.Module):
+    """Bag of patch embeddings -> slide logits: input projection, learned CLS
+    tokens in front, DSA blocks, LayerNorm, softmax-weighted pooling over the
+    CLS tokens, linear head.  Returns ``{"logits": (B, out_features)}``."""
+
+    def __init__(self, in_features: int = 1280, out_features: int = 1, embed_dim: int = 384, num_heads: int = 6,
+                 num_layers: int = 6, num_cls: int = 2, indexer_heads: int = 4, indexer_dim: int = 32,
+                 top_k: int = 512, block_q: int = 16, block_k: int = 32, block_d: int = 32,
+                 expansion_factor: float = 4.0, attn_dropout: float = 0.0, proj_dropout: float = 0.0,
+                 gradient_checkpointing: bool = False) -> None:
+        super().__init__()
+        if embed_dim % num_heads != 0:
+            raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads}). "
+                             f"Recommended: embed_dim // num_heads == 64 or 128.")
+        self.gradient_checkpointing = gradient_checkpointing
+        self.num_cls = num_cls
+        self.embed_dim = embed_dim
+        self.out_features = out_features
+
+        self.input_proj = nn.Linear(in_features, embed_dim)
+        self.cls_tokens = nn.Parameter(torch.zeros(1, num_cls, embed_dim))
+        nn.init.trunc_normal_(self.cls_tokens, std=0.02)
+        self.blocks = nn.ModuleList(
+            DSAViTBlock(embed_dim, num_heads, indexer_heads, indexer_dim, top_k, block_q, block_k, block_d,
+                        expansion_factor, attn_dropout, proj_dropout) for _ in range(num_layers))
+        self.norm = nn.LayerNorm(embed_dim)
+        self.cls_pool = nn.Linear(embed_dim, 1, bias=False)
+        self.head = nn.Linear(embed_dim, out_features)
+        nn.init.xavier_uniform_(self.input_proj.weight)
+        nn.init.zeros_(self.input_proj.bias)
+        nn.init.zeros_(self.head.bias)
+
+    def forward(self, x: Tensor) -> dict[str, Tensor]:
+        if x.dim() == 2:
+            x = x.unsqueeze(0)
+        x = self.input_proj(x)
+        x = torch.cat([self.cls_tokens.expand(x.shape[0], -1, -1).to(x.dtype), x], dim=1)
+        for blk in self.blocks:
+            x = blk(x)
+        x = self.norm(x)
+        cls = x[:, :self.num_cls]
+        pooled = (torch.softmax(self.cls_pool(cls), dim=1) * cls).sum(dim=1)
+        return {"logits": self.head(pooled)}

@@ -1,0 +1,217 @@
+"""Operator layer: the reference's two autograd.Function signatures backed by
+the sm_100a kernels, plus the fused module-level forward.
+
+Mirrors  src/sparse_wsi_vit/models/deepseek_sparse_attention_kernels/kernels.py
+  LightningIndexerFunction (kernels.py:344-386)   -> swv_dsa_indexer_topk_fwd
+  DSAAttentionFunction     (kernels.py:767-810)   -> swv_dsa_attn_gather_fwd
+and the op sequence of DeepSeekSparseAttention.forward
+  (src/sparse_wsi_vit/models/deepseek_sparse_attention.py:59-85) -> dsa_sparse_attention.
+
+Forward only.  All work runs on the current CUDA stream of the inputs' device.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+from ._lib import SwvError, check, dtype_code, lib, strides
+
+_scratch: dict = {}
+_status: dict = {}
+_CHECK = os.environ.get("SWV_CHECK_STATUS", "0") == "1"
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise SwvError("sparse_wsi_vit_b200 ops run on CUDA tensors only (no CPU path)")
+
+
+def _stream(dev):
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def status_word(dev) -> torch.Tensor:
+    """Per-device int32 the kernels report bounded-wait failures into."""
+    key = dev.index
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=dev)
+    return _status[key]
+
+
+def check_status(dev, what="kernel"):
+    """Synchronising read of the device status word; raises on a device-side error."""
+    st = status_word(dev)
+    code = int(st.item())
+    if code != 0:
+        st.zero_()
+        raise SwvError(f"{what}: {_lib.strerror(code)} (device status {code})")
+
+
+def _buffer(kind, dev, nbytes):
+    key = (kind, dev.index)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(int(nbytes), dtype=torch.uint8, device=dev)
+        _scratch[key] = buf
+    return buf
+
+
+def workspace_bytes(B, Tq, Tk):
+    n = ctypes.c_size_t()
+    check(lib.swv_dsa_workspace_bytes(B, Tq, Tk, ctypes.byref(n)), "swv_dsa_workspace_bytes")
+    return n.value
+
+
+def mask_bytes(B, Tq, Tk):
+    n = ctypes.c_size_t()
+    check(lib.swv_dsa_mask_bytes(B, Tq, Tk, ctypes.byref(n)), "swv_dsa_mask_bytes")
+    return n.value
+
+
+def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=None):
+    """q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID), w (IH,) -> idx int32, valid f32, scores f32,
+    each (B,Tq,top_k), keys in ascending order; optionally the tile-major bitmask."""
+    _require_cuda(q_idx, k_idx, w)
+    if q_idx.dim() != 4 or k_idx.dim() != 4:
+        raise SwvError("indexer projections must be (B, T, IH, ID)")
+    B, Tq, IH, ID = q_idx.shape
+    Tk = k_idx.shape[1]
+    if k_idx.shape[0] != B or k_idx.shape[2] != IH or k_idx.shape[3] != ID or w.numel() != IH:
+        raise SwvError("indexer shape mismatch")
+    if k_idx.dtype != q_idx.dtype:
+        k_idx = k_idx.to(q_idx.dtype)
+    dev = q_idx.device
+    w32 = w.detach().to(torch.float32).contiguous()
+    if out is None:
+        idx = torch.empty((B, Tq, top_k), dtype=torch.int32, device=dev)
+        valid = torch.empty((B, Tq, top_k), dtype=torch.float32, device=dev)
+        scores = torch.empty((B, Tq, top_k), dtype=torch.float32, device=dev)
+    else:
+        idx, valid, scores = out
+    ws = _buffer("ws", dev, workspace_bytes(B, Tq, Tk))
+    mptr = None
+    if want_mask:
+        if mask is None:
+            mask = torch.empty(mask_bytes(B, Tq, Tk) // 4, dtype=torch.int32, device=dev)
+        mptr = mask.data_ptr()
+    st = status_word(dev)
+    rc = lib.swv_dsa_indexer_topk_fwd(
+        q_idx.data_ptr(), strides(q_idx), k_idx.data_ptr(), strides(k_idx), dtype_code(q_idx.dtype),
+        w32.data_ptr(), B, Tq, Tk, IH, ID, top_k, idx.data_ptr(), valid.data_ptr(), scores.data_ptr(), mptr,
+        ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_indexer_topk_fwd")
+    if _CHECK:
+        check_status(dev, "swv_dsa_indexer_topk_fwd")
+    return (idx, valid, scores, mask) if want_mask else (idx, valid, scores)
+
+
+def dsa_attention_gather(q, k, v, idx, valid, rw, o):
+    """Routing-weighted attention over explicit key lists; writes ``o`` in place."""
+    _require_cuda(q, k, v, idx, valid, rw, o)
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    top_k = idx.shape[-1]
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        k, v = k.to(q.dtype), v.to(q.dtype)
+    if idx.dtype != torch.int32:
+        idx = idx.to(torch.int32)
+    valid = valid.to(torch.float32)
+    rw = rw.detach().to(torch.float32)
+    dev = q.device
+    st = status_word(dev)
+    rc = lib.swv_dsa_attn_gather_fwd(
+        q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), dtype_code(q.dtype),
+        idx.data_ptr(), strides(idx), valid.data_ptr(), strides(valid), rw.data_ptr(), strides(rw),
+        o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D, top_k, st.data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_attn_gather_fwd")
+    return o
+
+
+def _tma_ok(t):
+    es = t.element_size()
+    return (t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and
+            all((s * es) % 16 == 0 for s in t.stride()[:-1]))
+
+
+def dsa_attention_masked(q, k, v, mask, weights, o):
+    """Dense tensor-core sweep with the indexer's bitmask and ascending-order weights."""
+    _require_cuda(q, k, v, mask, weights, o)
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    top_k = weights.shape[-1]
+    if q.dtype != torch.bfloat16 or D != 64:
+        raise SwvError("dsa_attention_masked needs bf16 q/k/v with head_dim 64")
+    q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+    if not weights.is_contiguous():
+        weights = weights.contiguous()
+    dev = q.device
+    st = status_word(dev)
+    rc = lib.swv_dsa_attn_masked_fwd(
+        q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), mask.data_ptr(),
+        weights.data_ptr(), top_k, o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D,
+        st.data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_attn_masked_fwd")
+    if _CHECK:
+        check_status(dev, "swv_dsa_attn_masked_fwd")
+    return o
+
+
+def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False):
+    """Indexer + top-k + routing-weighted attention (deepseek_sparse_attention.py:59-85).
+
+    q (B,H,Tq,D), k, v (B,H,Tk,D); q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID); w (IH,).
+    bf16 with D == 64 takes the dense tensor-core path; anything else the gather
+    kernel.  Both are CUDA kernels of this library.
+    """
+    B, H, Tq, D = q.shape
+    dev = q.device
+    out_dtype = out_dtype or q.dtype
+    o = torch.empty((B, H, Tq, D), dtype=out_dtype, device=dev)
+    dense = q.dtype == torch.bfloat16 and D == 64
+    if dense:
+        idx, valid, scores, mask = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True)
+        dsa_attention_masked(q, k, v, mask, scores, o)
+    else:
+        idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k)
+        dsa_attention_gather(q, k, v, idx, valid, scores * valid, o)
+    return (o, idx, valid, scores) if return_topk else o
+
+
+class LightningIndexerFunction(torch.autograd.Function):
+    """Same positional signature as the reference (kernels.py:346-352).  The tile
+    sizes are accepted and ignored; outputs are allocated here (kernels.py:355-357)."""
+
+    @staticmethod
+    def forward(ctx, q_proj, k_proj, W, B, T, H, D, TOP_K, BLOCK_Q=None, BLOCK_K=None, BLOCK_D=None,
+                BLOCK_INDEXER_H=None):
+        if tuple(q_proj.shape) != (B, T, H, D):
+            raise SwvError(f"q_proj has shape {tuple(q_proj.shape)}, expected {(B, T, H, D)}")
+        idx, valid, scores = dsa_indexer_topk(q_proj.detach(), k_proj.detach(), W.detach(), TOP_K)
+        ctx.mark_non_differentiable(idx, valid)
+        return idx, valid, scores
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("sparse_wsi_vit_b200 implements the forward path only")
+
+
+class DSAAttentionFunction(torch.autograd.Function):
+    """Same positional signature as the reference (kernels.py:769-775): the caller
+    owns ``o``; it is written in place and returned (kernels.py:810)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, idx, valid, routing_weights, o, B, H, T, D, TOP_K, BLOCK_Q=None, BLOCK_K=None,
+                BLOCK_ATTENTION_H=None, BLOCK_D=None):
+        if tuple(q.shape) != (B, H, T, D):
+            raise SwvError(f"q has shape {tuple(q.shape)}, expected {(B, H, T, D)}")
+        dsa_attention_gather(q.detach(), k.detach(), v.detach(), idx, valid, routing_weights.detach(), o)
+        ctx.mark_dirty(o)
+        return o
+
+    @staticmethod
+    def backward(ctx, *grads):
+        raise NotImplementedError("sparse_wsi_vit_b200 implements the forward path only")

@@ -1,0 +1,230 @@
+"""GPU parity tests of the DSA forward path: the CUDA kernels, called through the
+C ABI, against the CPU oracle and the reference-generated fixtures."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import dsa as O
+from tests.golden.make_golden import dsa_cases
+from tests.util import make_dsa_inputs, overlap_fraction, own_scores, sets_equal
+
+pytestmark = pytest.mark.gpu
+
+# TF32 operands (10-bit mantissa): |score error| <= ~2^-10 * sum|wq_d wk_d|; scores here are O(1).
+SCORE_ATOL = 4e-3
+
+
+@pytest.fixture(scope="module")
+def swv():
+    import sparse_wsi_vit_b200 as m
+    return m
+
+
+def _dev():
+    return torch.device("cuda:0")
+
+
+def _check(swv):
+    swv.check_status(_dev())
+
+
+@pytest.mark.parametrize("T,K", [(1, 8), (5, 8), (63, 8), (64, 64), (65, 16), (127, 64), (200, 256), (1000, 64),
+                                 (1000, 2048), (384, 128)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_indexer_topk_small(swv, T, K, dtype):
+    q, k, v, qi, ki, w = make_dsa_inputs(T, 1, 64, 4, 64, seed=T * 7 + K, dtype=dtype, device=_dev())
+    idx, valid, scores = swv.dsa_indexer_topk(qi, ki, w, K)
+    full = own_scores(qi, ki, w)[0]                      # (T, T) the library's own scores
+    _check(swv)
+    k_eff = min(K, T)
+    # (1) bit-exact: the selected set is the lower-index top-k of the same score values
+    ridx, rvalid, rsel = O.topk_lower_index(full.cpu(), K)
+    assert torch.equal(idx[0].cpu(), ridx), "index sets differ from stable top-k of own scores"
+    assert torch.equal(valid[0].cpu(), rvalid)
+    assert torch.equal(scores[0].cpu(), rsel)
+    # (2) the scores themselves against the fp32 oracle
+    s_ref = O.indexer_scores(qi[0].cpu(), ki[0].cpu(), w.cpu())
+    assert (full.cpu() - s_ref).abs().max() < SCORE_ATOL
+    # (3) set overlap with the fp32 oracle's selection
+    oidx, _, _ = O.topk_lower_index(s_ref, K)
+    tie = O.rows_with_straddling_tie(s_ref, K)
+    if (~tie).any() and T > K:
+        ov = overlap_fraction(idx[0, ~tie.to(idx.device), :k_eff], oidx[~tie, :k_eff], T)
+        assert ov > 0.97, ov
+
+
+def test_indexer_batch_and_strided_inputs(swv):
+    B, T, IH, ID, K = 3, 150, 4, 32, 16
+    g = torch.Generator().manual_seed(3)
+    big_q = torch.randn(B, T, IH, 2 * ID, generator=g).to(_dev())
+    big_k = torch.randn(T, B, IH, ID, generator=g).to(_dev())
+    qi = big_q[..., ::2]                 # inner stride 2
+    ki = big_k.transpose(0, 1)           # batch/time swapped strides
+    w = torch.tensor([0.5, -1.0, 0.0, 2.0], device=_dev())
+    idx, valid, scores = swv.dsa_indexer_topk(qi, ki, w, K)
+    for b in range(B):
+        full = own_scores(qi[b:b + 1].contiguous(), ki[b:b + 1].contiguous(), w)[0]
+        ridx, _, rsel = O.topk_lower_index(full.cpu(), K)
+        assert torch.equal(idx[b].cpu(), ridx)
+        assert torch.equal(scores[b].cpu(), rsel)
+        s_ref = O.indexer_scores(qi[b].cpu(), ki[b].cpu(), w.cpu())
+        assert (full.cpu() - s_ref).abs().max() < 2e-2     # unscaled N(0,1) inputs: scores are O(10)
+    _check(swv)
+
+
+def test_indexer_ties_go_to_lower_index(swv):
+    """Few distinct key rows -> many exact ties straddling the K-th value; rows with
+    fewer than K positive scores -> ties at zero."""
+    T, IH, ID, K = 300, 2, 16, 32
+    g = torch.Generator().manual_seed(11)
+    base = torch.randn(1, 7, IH, ID, generator=g)
+    ki = base[:, torch.arange(T) % 7].contiguous().to(_dev())
+    qi = torch.randn(1, T, IH, ID, generator=g).to(_dev())
+    w = torch.tensor([1.0, 0.5], device=_dev())
+    idx, valid, scores = swv.dsa_indexer_topk(qi, ki, w, K)
+    full = own_scores(qi, ki, w)[0].cpu()
+    assert O.rows_with_straddling_tie(full, K).sum() > T // 2
+    ridx, _, rsel = O.topk_lower_index(full, K)
+    assert torch.equal(idx[0].cpu(), ridx)
+    assert torch.equal(scores[0].cpu(), rsel)
+    # all-negative products: every score is 0, the first K keys win
+    idx2, _, sc2 = swv.dsa_indexer_topk(qi.abs(), -ki.abs(), w, K)
+    assert torch.equal(idx2[0].cpu(), torch.arange(K, dtype=torch.int32).expand(T, K))
+    assert float(sc2.abs().max()) == 0.0
+    _check(swv)
+
+
+@pytest.mark.parametrize("case", [c[0] for c in dsa_cases()])
+def test_against_reference_fixtures(swv, golden_dir, case):
+    g = np.load(os.path.join(golden_dir, "dsa_reference.npz"))
+    B, T, H, D, IH, ID, K = [int(x) for x in g[f"{case}.dims"]]
+    t = lambda n: torch.from_numpy(g[f"{case}.{n}"]).to(_dev())
+    # attention kernel on the REFERENCE's own idx/valid/scores: same inputs -> same output
+    o = torch.zeros(B, H, T, D, device=_dev())
+    rw = t("scores") * t("valid")
+    out = swv.DSAAttentionFunction.apply(t("q"), t("k"), t("v"), t("idx"), t("valid"), rw, o, B, H, T, D, K,
+                                         16, 16, H, 16)
+    assert out.data_ptr() == o.data_ptr()
+    assert (o - t("o")).abs().max() < 1e-4
+    # indexer: scores per selected key agree with the reference's, sets agree off ties
+    idx, valid, scores = swv.LightningIndexerFunction.apply(t("qi"), t("ki"), t("w"), B, T, IH, ID, K, 16, 16, 16,
+                                                            IH)
+    assert torch.equal(valid.sum(-1), t("valid").sum(-1))
+    k_eff = min(K, T)
+    for b in range(B):
+        s_ref = O.indexer_scores(t("qi")[b].cpu(), t("ki")[b].cpu(), t("w").cpu())
+        mine = torch.gather(s_ref, 1, idx[b, :, :k_eff].long().cpu())
+        assert (mine - scores[b, :, :k_eff].cpu()).abs().max() < SCORE_ATOL
+        tie = O.rows_with_straddling_tie(s_ref, K)
+        rows = ~tie
+        if rows.any() and T > K:
+            ref_idx = t("idx")[b].cpu()
+            ov = overlap_fraction(idx[b].cpu()[rows], ref_idx[rows], T)
+            assert ov > 0.95, (case, ov)
+    if T < K:
+        assert bool((idx[..., T:] == 0).all()) and bool((scores[..., T:] == 0).all())
+        assert bool((valid[..., T:] == 0).all())
+    _check(swv)
+
+
+@pytest.mark.parametrize("T,H,D,K", [(200, 2, 64, 32), (77, 1, 32, 8), (130, 2, 128, 64)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gather_attention_vs_oracle(swv, T, H, D, K, dtype):
+    q, k, v, qi, ki, w = make_dsa_inputs(T, H, D, 4, 64, seed=5 + T, dtype=dtype, device=_dev())
+    idx, valid, scores = swv.dsa_indexer_topk(qi, ki, w, K)
+    # unsorted list with a repeated entry and an invalid slot: the kernel must honour all of it
+    perm = torch.randperm(K, generator=torch.Generator().manual_seed(1)).to(_dev())
+    idx, valid, scores = idx[..., perm].contiguous(), valid[..., perm].contiguous(), scores[..., perm].contiguous()
+    idx[:, :, 1] = idx[:, :, 0]
+    valid[:, :, 2] = 0.0
+    rw = scores * valid
+    o = torch.zeros(1, H, T, D, device=_dev(), dtype=torch.float32)
+    swv.dsa_attention_gather(q, k, v, idx, valid, rw, o)
+    ref = O.dsa_attention(q[0].float().cpu(), k[0].float().cpu(), v[0].float().cpu(), idx[0].cpu(), valid[0].cpu(),
+                          rw[0].cpu())
+    assert (o[0].cpu() - ref).abs().max() < 1e-4          # fp32 accumulation on identical inputs
+    _check(swv)
+
+
+def _masked_vs_oracle(swv, T, H, K, seed, rows=None, out_dtype=torch.float32, w_mode="randn"):
+    q, k, v, qi, ki, w = make_dsa_inputs(T, H, 64, 4, 64, seed=seed, dtype=torch.bfloat16, device=_dev(),
+                                         w_mode=w_mode)
+    o, idx, valid, scores = swv.dsa_sparse_attention(q, k, v, qi, ki, w, K, out_dtype=out_dtype, return_topk=True)
+    _check(swv)
+    assert torch.isfinite(o.float()).all()
+    r = slice(None) if rows is None else rows
+    ref = O.dsa_attention(q[0, :, r].float().cpu(), k[0].float().cpu(), v[0].float().cpu(), idx[0, r].cpu(),
+                          valid[0, r].cpu(), (scores * valid)[0, r].cpu())
+    diff = (o[0, :, r].float().cpu() - ref).abs()
+    return diff, o, idx, valid, scores, (q, k, v, qi, ki, w)
+
+
+@pytest.mark.parametrize("T,H,K", [(128, 1, 16), (200, 2, 32), (1000, 2, 64), (333, 1, 512), (1536, 2, 256)])
+def test_masked_attention_vs_oracle(swv, T, H, K):
+    """bf16 tensor-core path vs the fp32 oracle on the same (bf16-rounded) inputs and the same key lists.
+    Tolerance from the specification of the path: 2e-2 max-abs, 1e-3 mean-abs."""
+    diff, *_ = _masked_vs_oracle(swv, T, H, K, seed=T + K)
+    assert diff.max() < 2e-2, float(diff.max())
+    assert diff.mean() < 1e-3, float(diff.mean())
+
+
+def test_masked_matches_gather_and_bf16_out(swv):
+    diff, o, idx, valid, scores, (q, k, v, qi, ki, w) = _masked_vs_oracle(swv, 700, 2, 128, seed=9,
+                                                                         out_dtype=torch.bfloat16)
+    assert diff.max() < 2e-2
+    og = torch.zeros(1, 2, 700, 64, device=_dev())
+    swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, og)
+    assert (og - o.float()).abs().max() < 2e-2
+    _check(swv)
+
+
+def test_all_zero_weights_give_exact_zero(swv):
+    """Rows whose selected scores are all 0 produce exactly 0 (the 1e-6 clamp on the denominator)."""
+    T, H, K = 256, 1, 32
+    q, k, v, qi, ki, w = make_dsa_inputs(T, H, 64, 4, 64, seed=2, dtype=torch.bfloat16, device=_dev(), w_mode="abs")
+    o = swv.dsa_sparse_attention(q, k, v, qi.abs(), -ki.abs(), w, K, out_dtype=torch.float32)
+    assert float(o.abs().max()) == 0.0
+    _check(swv)
+
+
+def test_module_matches_reference_fixture(swv, golden_dir):
+    g = np.load(os.path.join(golden_dir, "dsa_module_reference.npz"))
+    m = swv.DeepSeekSparseAttention(d_model=64, attention_heads=2, indexer_heads=4, indexer_dim=16, top_k=16,
+                                    BLOCK_Q=16, BLOCK_K=16, BLOCK_D=16)
+    sd = {k[3:]: torch.from_numpy(g[k]) for k in g.files if k.startswith("sd.")}
+    m.load_state_dict(sd, strict=True)
+    m = m.to(_dev())
+    with torch.no_grad():
+        y = m(torch.from_numpy(g["x"]).to(_dev()))
+    ref = torch.from_numpy(g["y"])
+    # fp32 inputs: exact attention arithmetic; the TF32 indexer may swap two keys whose scores
+    # differ by < 1e-3 at the K-th place, which moves one of 16 weights by that much.
+    assert (y.cpu() - ref).abs().max() < 5e-3
+    assert (y.cpu() - ref).abs().mean() < 2e-4
+    _check(swv)
+
+
+def test_benchmark_config_sampled_rows(swv):
+    """N=16384, 8 heads x 64, 4x64 indexer, top-2048, bf16 (the single-layer DSA configuration):
+    full GPU run, oracle on 192 sampled query rows; own-score bit-exactness on the same rows."""
+    T, H, K = 16384, 8, 2048
+    rows = torch.randperm(T, generator=torch.Generator().manual_seed(0))[:192].sort().values
+    diff, o, idx, valid, scores, (q, k, v, qi, ki, w) = _masked_vs_oracle(swv, T, H, K, seed=1234, rows=rows)
+    assert diff.max() < 2e-2 and diff.mean() < 1e-3, (float(diff.max()), float(diff.mean()))
+    # structural properties on every row
+    assert bool((valid == 1).all())
+    assert bool((idx[..., 1:] > idx[..., :-1]).all()) and int(idx.min()) >= 0 and int(idx.max()) < T
+    # bit-exact top-k on the sampled rows: recompute those rows' full score vectors as a
+    # (Tq=192, Tk=T, top_k=T) call and take the stable top-k on the CPU
+    full = own_scores(qi[:, rows.to(_dev())].contiguous(), ki, w)[0].cpu()
+    ridx, _, rsel = O.topk_lower_index(full, K)
+    assert torch.equal(idx[0, rows.to(_dev())].cpu(), ridx)
+    assert torch.equal(scores[0, rows.to(_dev())].cpu(), rsel)
+    # against the fp32 oracle's selection
+    s_ref = O.indexer_scores(qi[0, rows.to(_dev())].cpu(), ki[0].cpu(), w.cpu())
+    assert (full - s_ref).abs().max() < SCORE_ATOL
+    oidx, _, _ = O.topk_lower_index(s_ref, K)
+    assert overlap_fraction(ridx, oidx, T) > 0.99
+    _check(swv)
