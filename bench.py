@@ -1,0 +1,334 @@
+"""Benchmark of the DSA sparse-attention forward (indexer + top-k + attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens T]
+
+Workload ("dsa_fwd_64k"): one DSA attention layer, 65536 tokens, 8 heads x 64,
+4 x 64 indexer, top-2048, bf16, batch 1, non-causal; seeded synthetic inputs with
+the shapes and distributions of the reference's Virchow2 feature bags (q, k, v ~
+N(0,1), q scaled by 1/8; indexer q/k ~ N(0, 1/64); W ~ N(0,1)).  One step = one
+forward over the whole slide.  With N > 1 (torchrun, one rank per GPU) the slide
+is sequence-sharded: total work is fixed ("strong" scaling), every step
+all-gathers the indexer keys, K and V over NCCL.
+
+Prints ONE JSON line (rank 0).  `value` is whole-job tokens/s with inputs resident
+in HBM; `e2e` is the same through the public API with inputs in pinned host
+memory and the output read back, copies inside the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
+METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
+
+# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch on the bench workload, from the
+# ncu capture summarised in profiles/ (scaled from the captured case); None until measured.
+ATTN_DRAM_BYTES_PER_LAUNCH = None
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return p.get("bf16_tflops_sustained", 1411.6), p.get("hbm_gbs", 6453.1), "measured"
+    return 1400.0, 6650.0, "fallback"
+
+
+def make_inputs(T, seed, device, pinned=False):
+    """Token-major tensors (1, T, H, D) / (1, T, IH, ID), bf16, seeded on the CPU."""
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(1, T, H, D, generator=g) / D ** 0.5).to(torch.bfloat16)
+    k = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16)
+    v = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16)
+    qi = (torch.randn(1, T, IH, ID, generator=g) / ID ** 0.5).to(torch.bfloat16)
+    ki = (torch.randn(1, T, IH, ID, generator=g) / ID ** 0.5).to(torch.bfloat16)
+    w = torch.randn(IH, generator=g)
+    ts = [q, k, v, qi, ki]
+    if pinned:
+        ts = [t.pin_memory() for t in ts]
+    elif device is not None:
+        ts = [t.to(device) for t in ts]
+    return (*ts, w.to(device) if device is not None else w)
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            with open(self.path) as f:
+                for line in f:
+                    c = [x.strip() for x in line.split(",")]
+                    if len(c) < 9:
+                        continue
+                    try:
+                        sm.append(float(c[1]))
+                        mx.append(float(c[2]))
+                    except ValueError:
+                        continue
+                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                          "sw_power_cap"), c[5:9]):
+                        if val.lower().startswith("active"):
+                            reasons.add(name)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                   "samples": len(sm)}
+        return out
+
+
+# ----------------------------------------------------------------- CPU baseline
+_CPU_INPUTS = {}
+
+
+def cpu_baseline(T, budget_s=15.0, threads=None):
+    """The CPU oracle (a port of the reference's arithmetic) on a bounded sample of the same
+    workload: `rows` query rows against all T keys, all heads.  Returns tokens/s."""
+    from oracle import dsa as O
+    if threads:
+        torch.set_num_threads(threads)
+    if T not in _CPU_INPUTS:
+        q, k, v, qi, ki, w = make_inputs(T, seed=0, device=None)
+        q, k, v = (t[0].transpose(0, 1).float() for t in (q, k, v))        # (H, T, D)
+        _CPU_INPUTS[T] = (q, k, v, qi[0].float(), ki[0].float(), w)
+    q, k, v, qi, ki, w = _CPU_INPUTS[T]
+
+    def run(rows):
+        t0 = time.perf_counter()
+        wq = O.collapse_heads(qi[:rows], w)
+        wk = O.collapse_heads(ki, w)
+        s = torch.relu(wq @ wk.T)
+        idx, valid, sel = O.topk_lower_index(s, TOP_K)
+        O.dsa_attention(q[:, :rows], k, v, idx, valid, sel * valid, chunk=64)
+        return time.perf_counter() - t0
+
+    rows = 32
+    t = run(rows)
+    target = max(rows, min(T, int(rows * budget_s / max(t, 1e-3))))
+    target = max(32, min(target, 4096))
+    if target > rows * 2:
+        rows = target
+        t = run(rows)
+    return {"value": rows / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{rows} of {T} query rows against all {T} keys, {H} heads, fp32, {t:.1f} s"}
+
+
+def run_reference(args):
+    """`--impl reference`: the reference's forward arithmetic on the host cores.  The reference is
+    Python + Triton (no compiled CPU library to build), so its CPU port in oracle/ is what is timed."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    T = args.tokens
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    per_step = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(T, budget_s=6.0 if i >= args.warmup else 2.0, threads=threads)
+        if i >= args.warmup:
+            per_step.append(base["value"])
+    value = statistics.mean(per_step)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * T / value, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"dsa_fwd_{T // 1024}k", "tokens": T, "heads": H, "head_dim": D,
+                   "indexer": f"{IH}x{ID}", "top_k": TOP_K},
+        "cpu_baseline": {**base, "value": value},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------- GPU arm
+def run_ours(args):
+    import torch.distributed as dist
+
+    import sparse_wsi_vit_b200 as swv
+    from sparse_wsi_vit_b200 import ops
+    from sparse_wsi_vit_b200.dist import plan_shards, sharded_dsa_attention
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    T = args.tokens
+    plan = plan_shards(T, world, rank, align=128)
+    sl = slice(plan.start, plan.stop)
+
+    host = make_inputs(T, seed=0, device=None)
+    w = host[5].to(dev)
+    pinned = [t[:, sl].contiguous().pin_memory() for t in host[:5]]
+    q, k, v, qi, ki = (t.to(dev) for t in pinned)
+    comm = torch.cuda.Stream(dev) if world > 1 else None
+    cur = torch.cuda.current_stream(dev)
+
+    ev_a = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ev_b = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    attn_events = []
+
+    def step(qd, kd, vd, qid, kid, timed_idx=None):
+        if world == 1:
+            B = 1
+            qv, kv, vv = (t.transpose(1, 2) for t in (qd, kd, vd))
+            idx, valid, scores, mask = ops.dsa_indexer_topk(qid, kid, w, TOP_K, want_mask=True)
+            o = torch.empty((B, H, qd.shape[1], D), dtype=torch.bfloat16, device=dev)
+            if timed_idx is not None:
+                ev_a[timed_idx].record(cur)
+            ops.dsa_attention_masked(qv, kv, vv, mask, scores, o)
+            if timed_idx is not None:
+                ev_b[timed_idx].record(cur)
+            return o, idx
+        o, idx, valid, scores = sharded_dsa_attention(qd, kd, vd, qid, kid, w, TOP_K, plan, out_dtype=torch.bfloat16,
+                                                      return_topk=True, comm_stream=comm)
+        return o, idx
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step(q, k, v, qi, ki)
+    ops.check_status(dev, "bench warm-up")
+
+    # ---- device-resident timing
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record(cur)
+    for i in range(args.steps):
+        step(q, k, v, qi, ki, timed_idx=i)
+    t1.record(cur)
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = t0.elapsed_time(t1) / args.steps
+    ops.check_status(dev, "bench timed region")
+
+    # ---- end to end: pinned host inputs -> device, forward, output back to pinned host
+    o_host = torch.empty((1, H, plan.local, D), dtype=torch.bfloat16).pin_memory()
+    dbuf = [torch.empty_like(t, device=dev) for t in pinned]
+
+    def e2e_step():
+        for d_, h_ in zip(dbuf, pinned):
+            d_.copy_(h_, non_blocking=True)
+        o, _ = step(*dbuf)
+        o_host.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record(cur)
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record(cur)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+
+    if world > 1:
+        tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms, ms_e2e = float(tt[0]), float(tt[1])
+
+    if rank == 0:
+        tf_peak, hbm_peak, peak_src = measured_peaks()
+        line = {
+            "metric": METRIC, "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"dsa_fwd_{T // 1024}k", "tokens": T, "heads": H, "head_dim": D,
+                       "indexer": f"{IH}x{ID} tf32", "top_k": TOP_K, "batch": 1,
+                       "parallelism": f"sp{world}" if world > 1 else "single",
+                       "l2": "inputs+outputs per step (>1.9 GiB) exceed the 126 MB L2"},
+            "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned) * world,
+                    "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world},
+            "gpu_launches": args.steps * 9 * world,
+            "clocks": clocks,
+        }
+        if world == 1:
+            attn_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev_a, ev_b))
+            kept = 4.0 * T * min(TOP_K, T) * H * D
+            executed = 4.0 * T * T * H * D
+            ach = kept / (attn_ms * 1e-3) / 1e12
+            line["roofline"] = {
+                "kernel": "dsa_attn_masked_kernel", "bound": "tensor", "achieved": ach, "peak": tf_peak,
+                "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH,
+                "peak_source": f"bf16_tflops_sustained of {peak_src}",
+                "kernel_ms": attn_ms, "algorithmic_flops": kept,
+                "executed_flops": executed, "executed_tflops": executed / (attn_ms * 1e-3) / 1e12,
+                "executed_frac": executed / (attn_ms * 1e-3) / 1e12 / tf_peak,
+                "other_kernels_ms": ms - attn_ms,
+            }
+            line["cpu_baseline"] = cpu_baseline(T, budget_s=15.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=65536)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -90,7 +90,7 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
  * reference).  fp32 accumulation.
  *   q (B,H,Tq,D), k, v (B,H,Tk,D): strides (b,h,t,d), last stride 1; dtype F32/BF16/F16.
  *   idx int32, valid f32, rw f32: (B,Tq,top_k), strides (b,t,k).
- *   o (B,H,Tq,D): strides (b,h,t,d); o_dtype F32/BF16/F16.  D in {32, 64, 128}.
+ *   o (B,H,Tq,D): strides (b,h,t,d); o_dtype F32/BF16/F16.  1 <= D <= 256.
  */
 int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], int qkv_dtype, const int32_t* idx,

@@ -363,7 +363,7 @@ struct GatherParams {
   void* o;
   int64_t os[4];
   int o_dtype;
-  int B, H, Tq, Tk, top_k;
+  int B, H, Tq, Tk, D, top_k;
   float scale;
 };
 
@@ -382,10 +382,12 @@ __device__ __forceinline__ void st_out(void* o, int dtype, int64_t off, float x)
   else static_cast<__half*>(o)[off] = __float2half_rn(x);
 }
 
-template <typename T, int D>
+// DPL = head-dim elements per lane in the PV phase; handles any D <= 32*DPL.
+template <typename T, int DPL>
 __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams p) {
-  constexpr int DPL = D / 32;
-  __shared__ float qsm[4][D];
+  constexpr int DMAX = 32 * DPL;
+  __shared__ float qsm[4][DMAX];
+  const int D = p.D;
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + wib;
   const int64_t total = static_cast<int64_t>(p.B) * p.H * p.Tq;
@@ -426,7 +428,7 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
     if (ok) {
       const T* kr = kbase + static_cast<int64_t>(id) * p.ks[2];
       float acc = 0.f;
-#pragma unroll 8
+#pragma unroll 4
       for (int d = 0; d < D; ++d) acc = fmaf(qsm[wib][d], ld_f32<T>(kr + d * p.ks[3]), acc);
       logit = acc * p.scale;
     }
@@ -449,7 +451,10 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
       if (pp != 0.f) {
         const T* vr = vbase + static_cast<int64_t>(ii) * p.vs[2];
 #pragma unroll
-        for (int i = 0; i < DPL; ++i) o[i] = fmaf(pp, ld_f32<T>(vr + (lane * DPL + i) * p.vs[3]), o[i]);
+        for (int i = 0; i < DPL; ++i) {
+          const int d = lane * DPL + i;
+          if (d < D) o[i] = fmaf(pp, ld_f32<T>(vr + d * p.vs[3]), o[i]);
+        }
       }
     }
     m = m_new;
@@ -457,7 +462,10 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
   const float inv = 1.f / fmaxf(l, 1e-6f);
   const int64_t obase = b * p.os[0] + h * p.os[1] + qi * p.os[2];
 #pragma unroll
-  for (int i = 0; i < DPL; ++i) st_out(p.o, p.o_dtype, obase + (lane * DPL + i) * p.os[3], o[i] * inv);
+  for (int i = 0; i < DPL; ++i) {
+    const int d = lane * DPL + i;
+    if (d < D) st_out(p.o, p.o_dtype, obase + d * p.os[3], o[i] * inv);
+  }
 }
 
 // ---------------------------------------------------------------------- host
@@ -515,9 +523,10 @@ template <typename T>
 static int launch_gather(const GatherParams& p, int D, cudaStream_t st) {
   const int64_t total = static_cast<int64_t>(p.B) * p.H * p.Tq;
   const unsigned grid = static_cast<unsigned>((total + 3) / 4);
-  if (D == 32) dsa_attn_gather_kernel<T, 32><<<grid, 128, 0, st>>>(p);
-  else if (D == 64) dsa_attn_gather_kernel<T, 64><<<grid, 128, 0, st>>>(p);
-  else if (D == 128) dsa_attn_gather_kernel<T, 128><<<grid, 128, 0, st>>>(p);
+  if (D <= 32) dsa_attn_gather_kernel<T, 1><<<grid, 128, 0, st>>>(p);
+  else if (D <= 64) dsa_attn_gather_kernel<T, 2><<<grid, 128, 0, st>>>(p);
+  else if (D <= 128) dsa_attn_gather_kernel<T, 4><<<grid, 128, 0, st>>>(p);
+  else if (D <= 256) dsa_attn_gather_kernel<T, 8><<<grid, 128, 0, st>>>(p);
   else return SWV_ERR_UNSUPPORTED;
   return cudaGetLastError() == cudaSuccess ? SWV_OK : SWV_ERR_CUDA;
 }
@@ -532,12 +541,12 @@ int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const 
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1 || top_k < 1) return SWV_ERR_SHAPE;
   if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
   if (o_dtype != SWV_F32 && o_dtype != SWV_BF16 && o_dtype != SWV_F16) return SWV_ERR_DTYPE;
-  if (D != 32 && D != 64 && D != 128) return SWV_ERR_UNSUPPORTED;
+  if (D < 1 || D > 256) return SWV_ERR_UNSUPPORTED;
   GatherParams p;
   p.q = q; p.k = k; p.v = v; p.idx = idx; p.valid = valid; p.rw = rw; p.o = o; p.o_dtype = o_dtype;
   for (int i = 0; i < 4; ++i) { p.qs[i] = qs[i]; p.ks[i] = ks[i]; p.vs[i] = vs[i]; p.os[i] = os[i]; }
   for (int i = 0; i < 3; ++i) { p.is[i] = is[i]; p.vls[i] = vls[i]; p.rs[i] = rs[i]; }
-  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.top_k = top_k;
+  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k;
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   if (dtype == SWV_F32) return launch_gather<float>(p, D, st);
   if (dtype == SWV_BF16) return launch_gather<__nv_bfloat16>(p, D, st);

@@ -423,7 +423,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   if (ID > kIdxDim) return SWV_ERR_UNSUPPORTED;
   const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
   if (workspace_bytes < L.total) return SWV_ERR_WORKSPACE;
-  if ((reinterpret_cast<uintptr_t>(workspace) & 1023) != 0) return SWV_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SWV_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(idx) & 3) || (reinterpret_cast<uintptr_t>(scores) & 3) ||
       (reinterpret_cast<uintptr_t>(valid) & 3) || (maskbits && (reinterpret_cast<uintptr_t>(maskbits) & 15)))
     return SWV_ERR_ALIGN;

@@ -1,0 +1,107 @@
+"""Sequence sharding of the DSA forward across the GPUs of one box.
+
+Every query row is independent given all keys, so each rank keeps a contiguous
+slice of the slide's tokens (its queries) and the only exchange per attention
+layer is an all-gather of the keys: the indexer keys first (small; the top-k
+passes start as soon as they land), then K and V on a side stream, overlapped
+with the indexer/top-k kernels.  Nothing is reduced: each rank writes its own
+query rows.  The reference has no counterpart (it runs one slide per rank under
+DDP, src/sparse_wsi_vit/experiments/trainer.py:100-106).
+
+Layout: sharded K/V/indexer-K are TOKEN-major, (B, T_local, H, D), so that the
+gathered tensor (B, T, H, D) is contiguous; the kernels read it through the
+strided (B, H, T, D) view.  The last shard may be short; gathered rows past the
+true length are padding the kernels never see (they take Tk explicitly).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class ShardPlan:
+    total: int       # tokens of the slide
+    world: int
+    rank: int
+    per_rank: int    # padded shard length (equal on every rank)
+    start: int       # first token owned by this rank
+    stop: int        # one past the last token owned (start == stop: empty shard)
+
+    @property
+    def local(self) -> int:
+        return self.stop - self.start
+
+
+def plan_shards(total: int, world: int, rank: int, align: int = 8) -> ShardPlan:
+    """Contiguous, equal-length (padded to `align`) token shards; only the tail may be short or empty."""
+    if total < 1 or world < 1 or not 0 <= rank < world:
+        raise ValueError(f"bad shard request total={total} world={world} rank={rank}")
+    per = -(-total // world)
+    per = -(-per // align) * align
+    start = min(rank * per, total)
+    stop = min(start + per, total)
+    return ShardPlan(total, world, rank, per, start, stop)
+
+
+def plan_ragged(lengths, world: int, rank: int, align: int = 8):
+    """One plan per slide of a ragged batch: every slide is split over all ranks, so the
+    all-gathers stay regular and the load stays balanced whatever the slide lengths."""
+    return [plan_shards(int(n), world, rank, align) for n in lengths]
+
+
+def _pad_tokens(x: torch.Tensor, per_rank: int) -> torch.Tensor:
+    if x.shape[1] == per_rank:
+        return x.contiguous()
+    out = x.new_zeros((x.shape[0], per_rank, *x.shape[2:]))
+    out[:, :x.shape[1]] = x
+    return out
+
+
+def all_gather_tokens(x_local: torch.Tensor, plan: ShardPlan, group=None, out=None) -> torch.Tensor:
+    """(B, T_local, ...) on every rank -> (B, world*per_rank, ...), rows >= plan.total are padding."""
+    B = x_local.shape[0]
+    xl = _pad_tokens(x_local, plan.per_rank)
+    if plan.world == 1:
+        return xl
+    if B == 1:
+        if out is None:
+            out = xl.new_empty((1, plan.world * plan.per_rank, *xl.shape[2:]))
+        dist.all_gather_into_tensor(out.view(plan.world * plan.per_rank, *xl.shape[2:]), xl[0], group=group)
+        return out
+    stage = xl.new_empty((plan.world, B, plan.per_rank, *xl.shape[2:]))
+    dist.all_gather_into_tensor(stage, xl, group=group)
+    return stage.transpose(0, 1).reshape(B, plan.world * plan.per_rank, *xl.shape[2:])
+
+
+def sharded_dsa_attention(q_loc, k_loc, v_loc, qi_loc, ki_loc, w, top_k, plan: ShardPlan, group=None,
+                          out_dtype=None, return_topk=False, compute=None, comm_stream=None):
+    """DSA forward for this rank's queries against the whole slide.
+
+    q_loc, k_loc, v_loc: (B, T_local, H, D) token-major; qi_loc, ki_loc: (B, T_local, IH, ID).
+    Returns o (B, H, T_local, D) [and idx/valid/scores for the local queries].
+    `compute` defaults to the CUDA path; tests on CPU ranks inject a checker.
+    """
+    if compute is None:
+        from .ops import dsa_sparse_attention as compute
+    use_side = comm_stream is not None and k_loc.is_cuda and plan.world > 1
+    ki_all = all_gather_tokens(ki_loc, plan, group)
+    if use_side:
+        cur = torch.cuda.current_stream(k_loc.device)
+        comm_stream.wait_stream(cur)
+        with torch.cuda.stream(comm_stream):
+            k_all = all_gather_tokens(k_loc, plan, group)
+            v_all = all_gather_tokens(v_loc, plan, group)
+        kv_ready = comm_stream.record_event()
+    else:
+        k_all = all_gather_tokens(k_loc, plan, group)
+        v_all = all_gather_tokens(v_loc, plan, group)
+        kv_ready = None
+    T = plan.total
+    q = q_loc.transpose(1, 2)                    # (B, H, T_local, D) view
+    k = k_all[:, :T].transpose(1, 2)             # (B, H, T, D) view of the gathered buffer
+    v = v_all[:, :T].transpose(1, 2)
+    return compute(q, k, v, qi_loc, ki_all[:, :T], w, top_k, out_dtype=out_dtype, return_topk=return_topk,
+                   **({"kv_ready": kv_ready} if kv_ready is not None else {}))

@@ -160,12 +160,14 @@ def dsa_attention_masked(q, k, v, mask, weights, o):
     return o
 
 
-def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False):
+def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False, kv_ready=None):
     """Indexer + top-k + routing-weighted attention (deepseek_sparse_attention.py:59-85).
 
     q (B,H,Tq,D), k, v (B,H,Tk,D); q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID); w (IH,).
     bf16 with D == 64 takes the dense tensor-core path; anything else the gather
-    kernel.  Both are CUDA kernels of this library.
+    kernel.  Both are CUDA kernels of this library.  `kv_ready` is an optional CUDA
+    event after which k and v are complete (they may still be in flight on another
+    stream while the indexer runs, which needs only q_idx / k_idx).
     """
     B, H, Tq, D = q.shape
     dev = q.device
@@ -174,9 +176,13 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
     dense = q.dtype == torch.bfloat16 and D == 64
     if dense:
         idx, valid, scores, mask = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True)
+        if kv_ready is not None:
+            torch.cuda.current_stream(dev).wait_event(kv_ready)
         dsa_attention_masked(q, k, v, mask, scores, o)
     else:
         idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k)
+        if kv_ready is not None:
+            torch.cuda.current_stream(dev).wait_event(kv_ready)
         dsa_attention_gather(q, k, v, idx, valid, scores * valid, o)
     return (o, idx, valid, scores) if return_topk else o
 

@@ -12,8 +12,15 @@ from tests.util import make_dsa_inputs, overlap_fraction, own_scores, sets_equal
 
 pytestmark = pytest.mark.gpu
 
-# TF32 operands (10-bit mantissa): |score error| <= ~2^-10 * sum|wq_d wk_d|; scores here are O(1).
-SCORE_ATOL = 4e-3
+# TF32 operands keep 10 mantissa bits: each product is off by at most ~2^-9 relative.
+SCORE_ATOL = 1e-2          # for the benchmark-distributed inputs, whose scores are O(1)
+
+
+def score_error_bound(qi, ki, w):
+    """Elementwise bound 2^-9 * sum_d |wq_d| |wk_d| on |tf32 score - fp32 score|."""
+    wq = O.collapse_heads(qi, w).abs()
+    wk = O.collapse_heads(ki, w).abs()
+    return 2.0 ** -9 * (wq @ wk.T) + 1e-6
 
 
 @pytest.fixture(scope="module")
@@ -46,7 +53,7 @@ def test_indexer_topk_small(swv, T, K, dtype):
     assert torch.equal(scores[0].cpu(), rsel)
     # (2) the scores themselves against the fp32 oracle
     s_ref = O.indexer_scores(qi[0].cpu(), ki[0].cpu(), w.cpu())
-    assert (full.cpu() - s_ref).abs().max() < SCORE_ATOL
+    assert bool(((full.cpu() - s_ref).abs() <= score_error_bound(qi[0].cpu(), ki[0].cpu(), w.cpu())).all())
     # (3) set overlap with the fp32 oracle's selection
     oidx, _, _ = O.topk_lower_index(s_ref, K)
     tie = O.rows_with_straddling_tie(s_ref, K)
@@ -70,7 +77,7 @@ def test_indexer_batch_and_strided_inputs(swv):
         assert torch.equal(idx[b].cpu(), ridx)
         assert torch.equal(scores[b].cpu(), rsel)
         s_ref = O.indexer_scores(qi[b].cpu(), ki[b].cpu(), w.cpu())
-        assert (full.cpu() - s_ref).abs().max() < 2e-2     # unscaled N(0,1) inputs: scores are O(10)
+        assert bool(((full.cpu() - s_ref).abs() <= score_error_bound(qi[b].cpu(), ki[b].cpu(), w.cpu())).all())
     _check(swv)
 
 
@@ -224,7 +231,7 @@ def test_benchmark_config_sampled_rows(swv):
     assert torch.equal(scores[0, rows.to(_dev())].cpu(), rsel)
     # against the fp32 oracle's selection
     s_ref = O.indexer_scores(qi[0, rows.to(_dev())].cpu(), ki[0].cpu(), w.cpu())
-    assert (full - s_ref).abs().max() < SCORE_ATOL
+    assert bool(((full - s_ref).abs() <= score_error_bound(qi[0, rows.to(_dev())].cpu(), ki[0].cpu(), w.cpu())).all())
     oidx, _, _ = O.topk_lower_index(s_ref, K)
     assert overlap_fraction(ridx, oidx, T) > 0.99
     _check(swv)
