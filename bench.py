@@ -216,11 +216,11 @@ def run_ours(args):
         if world == 1:
             B = 1
             qv, kv, vv = (t.transpose(1, 2) for t in (qd, kd, vd))
-            idx, valid, scores, mask = ops.dsa_indexer_topk(qid, kid, w, TOP_K, want_mask=True)
+            idx, valid, scores, sel = ops.dsa_indexer_topk(qid, kid, w, TOP_K, want_mask=True)
             o = torch.empty((B, H, qd.shape[1], D), dtype=torch.bfloat16, device=dev)
             if timed_idx is not None:
                 ev_a[timed_idx].record(cur)
-            ops.dsa_attention_masked(qv, kv, vv, mask, scores, o)
+            ops.dsa_attention_masked(qv, kv, vv, sel, o)
             if timed_idx is not None:
                 ev_b[timed_idx].record(cur)
             return o, idx

@@ -51,8 +51,9 @@ int swv_version(void);
 /* Text for a negative return code or a positive device status code. */
 const char* swv_strerror(int code);
 
-/* Bytes of scratch swv_dsa_indexer_topk_fwd / swv_dsa_forward need for B
- * batches of Tq queries against Tk keys. */
+/* Bytes of scratch swv_dsa_indexer_topk_fwd needs for B batches of Tq queries
+ * against Tk keys (256-byte aligned).  After the call it holds the collapsed
+ * indexer vectors swv_dsa_attn_masked_fwd reads. */
 int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes);
 
 /* Bytes of the tile-major membership bitmask for B x Tq x Tk:
@@ -99,18 +100,19 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
                             int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
                             void* stream);
 
-/* Same arithmetic as swv_dsa_attn_gather_fwd for key lists produced by
- * swv_dsa_indexer_topk_fwd in the same call sequence, computed as a dense
- * tensor-core flash-attention sweep (tcgen05 QK^T and PV, TMA-fed) with the
- * membership bitmask and the ascending-order scores applied inside the
- * online softmax (M:73-85 fused).  bf16 q/k/v only, D == 64.
- *   maskbits: as written by swv_dsa_indexer_topk_fwd for the same B,Tq,Tk.
- *   weights : the `scores` output (routing weights; valid slots only).
+/* Same arithmetic as swv_dsa_attn_gather_fwd for the key lists of the
+ * swv_dsa_indexer_topk_fwd call that last wrote `maskbits` and `workspace`
+ * (same B, Tq, Tk), fused with `routing_weights = scores * valid` (M:73-85):
+ * a dense tensor-core flash-attention sweep (tcgen05 QK^T and PV, TMA-fed) with
+ * the membership bitmask applied inside the online softmax and the routing
+ * weights recomputed on the tensor cores from the collapsed indexer vectors
+ * kept in the workspace (bit-identical to the emitted scores).
+ * bf16 q/k/v only, D == 64; q,k,v,o rows 16-byte aligned, unit inner stride.
  */
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
-                            const float* weights, int top_k, void* o, const int64_t o_strides[4], int o_dtype,
-                            int B, int H, int Tq, int Tk, int D, int* status, void* stream);
+                            const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
+                            int Tq, int Tk, int D, int* status, void* stream);
 
 #ifdef __cplusplus
 }

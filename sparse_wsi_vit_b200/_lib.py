@@ -44,7 +44,7 @@ def _load():
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, i64p, c_void_p, i64p, c_void_p, i64p,
         c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.swv_dsa_attn_masked_fwd.argtypes = [
-        c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_int, c_void_p, i64p, c_int,
+        c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_void_p, i64p, c_int,
         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     for name in EXPORTS[2:]:
         getattr(lib, name).restype = c_int

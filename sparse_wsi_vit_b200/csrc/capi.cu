@@ -11,7 +11,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
                           float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
                           int* status, cudaStream_t st);
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
-                         const int64_t* vs, const uint32_t* maskbits, const float* weights, int top_k, void* o,
+                         const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
                          cudaStream_t st);
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
@@ -77,9 +77,9 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
 
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
-                            const float* weights, int top_k, void* o, const int64_t o_strides[4], int o_dtype,
-                            int B, int H, int Tq, int Tk, int D, int* status, void* stream) {
-  return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, weights, top_k, o, o_strides,
+                            const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
+                            int Tq, int Tk, int D, int* status, void* stream) {
+  return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, status, static_cast<cudaStream_t>(stream));
 }
 

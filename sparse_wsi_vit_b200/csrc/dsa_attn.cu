@@ -2,25 +2,32 @@
 //
 // Replaces the reference's `_dsa_attention_fwd` Triton kernel
 // (src/sparse_wsi_vit/models/deepseek_sparse_attention_kernels/kernels.py:450-564)
-// for key lists produced by the indexer of this library.
+// for key lists produced by the indexer of this library, fused with the
+// `routing_weights = scores * valid` step of the module
+// (src/sparse_wsi_vit/models/deepseek_sparse_attention.py:73).
 //
 // With per-query token-granular selection and one K/V per head, gathering the
 // selected rows moves one byte per FLOP; at top_k/T >= ~1/64 it is faster to
 // sweep ALL key tiles on the tensor cores and apply the selection inside the
-// online softmax.  One CTA owns (batch, head, 128 queries):
-//   warp 0      : TMA producer (Q once, K and V tiles through 2-deep rings)
-//   warp 1      : UMMA issuer  S = Q K^T (bf16, fp32 accumulate in TMEM),
-//                               O += P V  (P read from TMEM, V MN-major from smem)
-//   warps 2..5  : softmax, one thread per query row.  Membership comes from the
-//                 tile-major bitmask, the routing weight of the c-th selected key
-//                 of a row is weights[row][c] (ascending key order).
-//                   p = 2^(s*scale*log2e - m_used) * w      (members only)
-//                 The exact maximum over the selected logits is tracked beside the
-//                 (lazily raised) stabiliser m_used so that the reference's
-//                 1e-6 clamp on the denominator is reproduced exactly.
-// TMEM columns: S [0,128) fp32 | P [128,192) bf16x2 | O [192,256) fp32.
-// Two CTAs share an SM (80 KiB smem, 256 TMEM columns each), so one CTA's MMAs
-// overlap the other's softmax.
+// online softmax.  One CTA owns (batch, 128 queries, a PAIR of heads):
+//   warp 0      : TMA producer: collapsed indexer queries + Q of both heads once;
+//                 per key tile the collapsed indexer keys, K and V of both heads.
+//   warp 1      : UMMA issuer (one thread, event driven):
+//                   R   = wq wk^T        TF32, the routing-weight tile, shared by both heads;
+//                                        bit-identical to the scores the indexer emitted
+//                   S_h = Q_h K_h^T      bf16
+//                   PV_h = P_h V_h       P from TMEM, V MN-major from smem
+//   warps 2..5  : softmax of head 0, one thread per query row
+//   warps 6..9  : softmax of head 1
+// Per (row, tile): membership from the tile-major bitmask the indexer wrote,
+//   p = 2^(s*scale*log2e - m_used) * relu(R)   for selected keys, 0 otherwise.
+// The exact maximum over the selected logits is tracked beside the lazily
+// raised stabiliser m_used, so the reference's 1e-6 clamp on the denominator
+// is reproduced: out = O*c / max(l*c, 1e-6), c = 2^(m_used - m_true).
+// The output accumulator lives in registers (64 fp32 per row).
+// TMEM (512 columns): R double buffer [0,256) | per head 128 columns at 256 + 128*h:
+//   S fp32 [0,128); P (bf16x2) overwrites [0,64) as the row is consumed; the PV
+//   product of the tile lands in [64,128) and is folded into the registers.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -29,15 +36,24 @@
 namespace swv {
 
 constexpr int kHeadDim = 64;
-constexpr int kQTileBytes = kTile * kHeadDim * 2;   // 16 KiB bf16 tile
-constexpr int kAttnTmemCols = 256;
-constexpr uint32_t kColS = 0, kColP = 128, kColO = 192;
-constexpr float kRescaleStep = 8.0f;                // raise the stabiliser only in steps of 2^8
+constexpr int kQTileBytes = kTile * kHeadDim * 2;     // 16 KiB bf16 tile
+constexpr int kWTileBytes = kTile * kIdxDim * 4;      // 32 KiB fp32 indexer tile (two K halves)
+constexpr int kAttnTmemCols = 512;
+constexpr uint32_t kColR = 0, kColHead = 256;
+constexpr float kRescaleStep = 8.0f;                  // raise the stabiliser only in steps of 2^8
+
+// shared memory map (bytes from the 1024-aligned base)
+constexpr int kOffWq = 0;
+constexpr int kOffWk = kOffWq + kWTileBytes;              // 2 stages
+constexpr int kOffQ = kOffWk + 2 * kWTileBytes;           // 2 heads
+constexpr int kOffK = kOffQ + 2 * kQTileBytes;            // [head][2 stages]
+constexpr int kOffV = kOffK + 4 * kQTileBytes;            // [head] single stage
+constexpr int kOffCtl = kOffV + 2 * kQTileBytes;
 
 struct AttnParams {
-  int B, H, Tq, Tk, top_k, nQT, nKT;
+  int B, H, Tq, Tk, nQT, nKT, nHP;
   const uint32_t* maskbits;
-  const float* weights;
+  const uint32_t *st_prefix, *st_kth, *st_neq;   // per query row, written by the indexer's select passes
   void* o;
   int64_t osb, osh, ost;
   int o_dtype;
@@ -47,46 +63,218 @@ struct AttnParams {
 
 struct AttnCtl {
   uint64_t q_full;
-  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full, s_free, p_full, pv_done;
+  uint64_t wk_full[2], wk_empty[2];
+  uint64_t k_full[2][2], k_empty[2][2];
+  uint64_t v_full[2], v_empty[2];
+  uint64_t r_full[2], r_free[2];
+  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
 
-constexpr size_t attn_smem_bytes() { return 1024 + kQTileBytes * 5 + sizeof(AttnCtl) + 64; }
+constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
 
-__global__ void __launch_bounds__(192, 2)
-    dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+// gives up (and raises the CTA's abort flag) after kWaitLimitNs without progress
+struct ProgressClock {
+  uint64_t t0;
+  __device__ void reset() { t0 = globaltimer_ns(); }
+  __device__ bool expired(volatile uint32_t* abort_flag) {
+    if (*abort_flag != 0u) return true;
+    if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1u;
+      return true;
+    }
+    return false;
+  }
+};
+
+// ------------------------------------------------------------ softmax helpers
+// m = max(m, s) where r >= thr   (one compare + one predicated max)
+__device__ __forceinline__ void max_where_ge(float& m, float s, float r, float thr) {
+  asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %2, %3;\n\t@p max.f32 %0, %0, %1;\n\t}" : "+f"(m) : "f"(s), "f"(r), "f"(thr));
+}
+// r >= thr ? v : 0
+__device__ __forceinline__ float keep_where_ge(float v, float r, float thr) {
+  float out;
+  asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %2, %3;\n\tselp.f32 %0, %1, 0f00000000, p;\n\t}"
+      : "=f"(out)
+      : "f"(v), "f"(r), "f"(thr));
+  return out;
+}
+
+struct SoftmaxRow {
+  float acc[kHeadDim];     // output accumulator of this query row, relative to 2^m_used
+  float m_true, m_used, l;
+  float thr_ge;            // fast path: a key is selected iff its raw score >= thr_ge
+  float sc;
+  uint32_t lane_base, s_col;
+  const uint4* mask_tile;
+};
+
+// The per-tile loop of one softmax thread (one query row of one head).
+//   kExact = false: membership by comparing the recomputed score with the row threshold.
+//   kExact = true : membership from the indexer's bitmask (ties cut by key index, members
+//                   with zero weight); routing weight relu(score).
+template <bool kExact>
+__device__ __forceinline__ bool softmax_tiles(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane, int* status,
+                                              volatile uint32_t* abort_flag) {
+  const float ninf = -__int_as_float(0x7f800000);
+  const float sc = st.sc, thr = st.thr_ge;
+  const uint32_t s_col = st.s_col;
+  uint4 mw = make_uint4(0, 0, 0, 0);
+  if (kExact) mw = __ldg(st.mask_tile);
+
+  for (int j = 0; j < nKT; ++j) {
+    uint4 mw_next = make_uint4(0, 0, 0, 0);
+    if (kExact && j + 1 < nKT) mw_next = __ldg(st.mask_tile + static_cast<int64_t>(j + 1) * kTile);
+    const uint32_t words[4] = {mw.x, mw.y, mw.z, mw.w};
+    const uint32_t r_col = st.lane_base + kColR + (j & 1) * kTile;
+
+    if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag) ||
+        !mbar_wait_bounded(&ctl->r_full[j & 1], (j >> 1) & 1, abort_flag)) {
+      record_status(status, kDevWaitAccFull);
+      return false;
+    }
+    tc_fence_after();
+
+    // pass 1: maximum over the selected logits of this tile (four independent chains)
+    float mt0 = ninf, mt1 = ninf, mt2 = ninf, mt3 = ninf;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      uint32_t s[16], r[16];
+      tmem_ld16(s_col + u * 16, s);
+      if (!kExact) tmem_ld16(r_col + u * 16, r);
+      tc_wait_ld();
+      const uint32_t w = words[u >> 1] >> ((u & 1) * 16);
+#pragma unroll
+      for (int i = 0; i < 16; i += 4) {
+        if (kExact) {
+          mt0 = fmaxf(mt0, (w & (1u << i)) ? __uint_as_float(s[i]) : ninf);
+          mt1 = fmaxf(mt1, (w & (2u << i)) ? __uint_as_float(s[i + 1]) : ninf);
+          mt2 = fmaxf(mt2, (w & (4u << i)) ? __uint_as_float(s[i + 2]) : ninf);
+          mt3 = fmaxf(mt3, (w & (8u << i)) ? __uint_as_float(s[i + 3]) : ninf);
+        } else {
+          max_where_ge(mt0, __uint_as_float(s[i]), __uint_as_float(r[i]), thr);
+          max_where_ge(mt1, __uint_as_float(s[i + 1]), __uint_as_float(r[i + 1]), thr);
+          max_where_ge(mt2, __uint_as_float(s[i + 2]), __uint_as_float(r[i + 2]), thr);
+          max_where_ge(mt3, __uint_as_float(s[i + 3]), __uint_as_float(r[i + 3]), thr);
+        }
+      }
+    }
+    const float mt = fmaxf(fmaxf(mt0, mt1), fmaxf(mt2, mt3));
+    st.m_true = fmaxf(st.m_true, mt * sc);
+    if (__any_sync(0xffffffffu, st.m_true > st.m_used + kRescaleStep)) {
+      const float factor = (st.m_true == st.m_used) ? 1.f : ex2_approx(st.m_used - st.m_true);
+      st.m_used = st.m_true;
+      st.l *= factor;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) st.acc[i] *= factor;
+    }
+    const float neg_m = -st.m_used;
+
+    // pass 2: routing-weighted probabilities of the selected keys -> TMEM (bf16),
+    // 16 columns at a time to keep the live register set small
+    float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      uint32_t s[16], r[16];
+      tmem_ld16(s_col + u * 16, s);
+      tmem_ld16(r_col + u * 16, r);
+      tc_wait_ld();
+      if (u == 7) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
+      }
+      const uint32_t w = words[u >> 1] >> ((u & 1) * 16);
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        const float e0 = ex2_approx(fmaf(__uint_as_float(s[i]), sc, neg_m));
+        const float e1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sc, neg_m));
+        float p0, p1;
+        if (kExact) {
+          p0 = e0 * fmaxf(__uint_as_float(r[i]), 0.f);
+          p1 = e1 * fmaxf(__uint_as_float(r[i + 1]), 0.f);
+          p0 = (w & (1u << i)) ? p0 : 0.f;
+          p1 = (w & (2u << i)) ? p1 : 0.f;
+        } else {
+          p0 = keep_where_ge(e0 * __uint_as_float(r[i]), __uint_as_float(r[i]), thr);
+          p1 = keep_where_ge(e1 * __uint_as_float(r[i + 1]), __uint_as_float(r[i + 1]), thr);
+        }
+        l0 += p0;
+        l1 += p1;
+        packed[i >> 1] = pack_bf16x2(p0, p1);
+      }
+      tmem_st8(s_col + u * 8, packed);
+    }
+    st.l += l0 + l1;
+    tc_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+
+    // fold the PV product of this tile into the register accumulator
+    if (!mbar_wait_bounded(&ctl->pv_done[x], j & 1, abort_flag)) {
+      record_status(status, kDevWaitPvDone);
+      return false;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t o[16];
+      tmem_ld16(s_col + 64 + c * 16, o);
+      tc_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 16; ++i) st.acc[c * 16 + i] += __uint_as_float(o[i]);
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->s_free[x]);
+    mw = mw_next;
+  }
+  return true;
+}
+
+__global__ void __launch_bounds__(320, 1)
+    dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
+                           const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+  constexpr uint32_t kIdescR = make_idesc(/*tf32*/ 2, kTile, kTile, 0, 0);
   constexpr uint32_t kIdescQK = make_idesc(/*bf16*/ 1, kTile, kTile, 0, 0);
   constexpr uint32_t kIdescPV = make_idesc(/*bf16*/ 1, kTile, kHeadDim, 0, /*V is MN-major*/ 1);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* sm_q = smem;
-  uint8_t* sm_k = smem + kQTileBytes;
-  uint8_t* sm_v = smem + kQTileBytes * 3;
-  AttnCtl* ctl = reinterpret_cast<AttnCtl*>(smem + kQTileBytes * 5);
+  AttnCtl* ctl = reinterpret_cast<AttnCtl*>(smem + kOffCtl);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int h = blockIdx.x % p.H;
-  const int qt = (blockIdx.x / p.H) % p.nQT;
-  const int b = blockIdx.x / (p.H * p.nQT);
+  const int hp = blockIdx.x % p.nHP;
+  const int qt = (blockIdx.x / p.nHP) % p.nQT;
+  const int b = blockIdx.x / (p.nHP * p.nQT);
   const int nKT = p.nKT;
+  const int h0 = hp * 2;
+  const int nh = (h0 + 1 < p.H) ? 2 : 1;   // heads handled by this CTA
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&ctl->k_full[s], 1);
-      mbar_init(&ctl->k_empty[s], 1);
+      mbar_init(&ctl->wk_full[s], 1);
+      mbar_init(&ctl->wk_empty[s], 1);
+      mbar_init(&ctl->r_full[s], 1);
+      mbar_init(&ctl->r_free[s], 4 * nh);
       mbar_init(&ctl->v_full[s], 1);
       mbar_init(&ctl->v_empty[s], 1);
+      mbar_init(&ctl->s_full[s], 1);
+      mbar_init(&ctl->s_free[s], 4);
+      mbar_init(&ctl->p_full[s], 4);
+      mbar_init(&ctl->pv_done[s], 1);
+      for (int t = 0; t < 2; ++t) {
+        mbar_init(&ctl->k_full[s][t], 1);
+        mbar_init(&ctl->k_empty[s][t], 1);
+      }
     }
-    mbar_init(&ctl->s_full, 1);
-    mbar_init(&ctl->s_free, 4);
-    mbar_init(&ctl->p_full, 4);
-    mbar_init(&ctl->pv_done, 1);
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
@@ -103,238 +291,208 @@ __global__ void __launch_bounds__(192, 2)
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      tma_prefetch_desc(&tm_wq);
+      tma_prefetch_desc(&tm_wk);
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_expect_tx(&ctl->q_full, kQTileBytes);
-      tma_load_4d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, h, b);
-      for (int j = 0; j < nKT; ++j) {
-        const int s = j & 1;
-        const uint32_t par = ((j >> 1) & 1) ^ 1;
-        if (!mbar_wait_bounded(&ctl->k_empty[s], par, abort_flag)) {
+      mbar_expect_tx(&ctl->q_full, kWTileBytes + nh * kQTileBytes);
+      tma_load_3d(smem + kOffWq, &tm_wq, &ctl->q_full, 0, qt * kTile, b);
+      tma_load_3d(smem + kOffWq + kWTileBytes / 2, &tm_wq, &ctl->q_full, 32, qt * kTile, b);
+      for (int x = 0; x < nh; ++x)
+        tma_load_4d(smem + kOffQ + x * kQTileBytes, &tm_q, &ctl->q_full, 0, qt * kTile, h0 + x, b);
+
+      // five independent streams, each issued as soon as its slot is free
+      int n_wk = 0, n_k[2] = {0, 0}, n_v[2] = {0, 0};
+      ProgressClock clk;
+      clk.reset();
+      for (;;) {
+        bool done = n_wk == nKT, progress = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) done = done && (x >= nh || (n_k[x] == nKT && n_v[x] == nKT));
+        if (done) break;
+        if (n_wk < nKT && mbar_try_wait(&ctl->wk_empty[n_wk & 1], ((n_wk >> 1) & 1) ^ 1)) {
+          uint8_t* dst = smem + kOffWk + (n_wk & 1) * kWTileBytes;
+          mbar_expect_tx(&ctl->wk_full[n_wk & 1], kWTileBytes);
+          tma_load_3d(dst, &tm_wk, &ctl->wk_full[n_wk & 1], 0, n_wk * kTile, b);
+          tma_load_3d(dst + kWTileBytes / 2, &tm_wk, &ctl->wk_full[n_wk & 1], 32, n_wk * kTile, b);
+          ++n_wk;
+          progress = true;
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (x >= nh) continue;
+          int j = n_k[x];
+          if (j < nKT && mbar_try_wait(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1)) {
+            mbar_expect_tx(&ctl->k_full[x][j & 1], kQTileBytes);
+            tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, j * kTile,
+                        h0 + x, b);
+            ++n_k[x];
+            progress = true;
+          }
+          j = n_v[x];
+          if (j < nKT && mbar_try_wait(&ctl->v_empty[x], (j & 1) ^ 1)) {
+            mbar_expect_tx(&ctl->v_full[x], kQTileBytes);
+            tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, j * kTile, h0 + x, b);
+            ++n_v[x];
+            progress = true;
+          }
+        }
+        if (progress) {
+          clk.reset();
+        } else if (clk.expired(abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
           break;
         }
-        mbar_expect_tx(&ctl->k_full[s], kQTileBytes);
-        tma_load_4d(sm_k + s * kQTileBytes, &tm_k, &ctl->k_full[s], 0, j * kTile, h, b);
-        if (!mbar_wait_bounded(&ctl->v_empty[s], par, abort_flag)) {
-          record_status(p.status, kDevWaitStageEmpty);
-          break;
-        }
-        mbar_expect_tx(&ctl->v_full[s], kQTileBytes);
-        tma_load_4d(sm_v + s * kQTileBytes, &tm_v, &ctl->v_full[s], 0, j * kTile, h, b);
       }
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      const uint32_t q_addr = smem_u32(sm_q);
-      const uint32_t k_addr = smem_u32(sm_k);
-      const uint32_t v_addr = smem_u32(sm_v);
+      const uint32_t wq_addr = smem_u32(smem + kOffWq);
+      const uint32_t wk_addr = smem_u32(smem + kOffWk);
+      const uint32_t q_addr = smem_u32(smem + kOffQ);
+      const uint32_t k_addr = smem_u32(smem + kOffK);
+      const uint32_t v_addr = smem_u32(smem + kOffV);
       bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
       if (!ok) record_status(p.status, kDevWaitQ);
 
-      auto issue_qk = [&](int j) -> bool {
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&ctl->k_full[s], (j >> 1) & 1, abort_flag)) {
-          record_status(p.status, kDevWaitTmaFull);
-          return false;
-        }
-        if (j > 0 && !mbar_wait_bounded(&ctl->s_free, (j - 1) & 1, abort_flag)) {
-          record_status(p.status, kDevWaitAccEmpty);
-          return false;
-        }
-        tc_fence_after();
+      int n_r = 0;                    // routing-weight tiles issued
+      int n_qk[2] = {0, 0};           // S tiles issued per head
+      int n_pv[2] = {0, 0};           // PV products issued per head
+      ProgressClock clk;
+      clk.reset();
+      while (ok) {
+        bool done = n_r == nKT, progress = false;
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          umma_f16_ss(tmem_base + kColS, smem_desc_sw128(q_addr + ks * 32),
-                      smem_desc_sw128(k_addr + s * kQTileBytes + ks * 32), kIdescQK, ks > 0);
+        for (int x = 0; x < 2; ++x) done = done && (x >= nh || n_pv[x] == nKT);
+        if (done) break;
+        // R(j): needs the indexer key tile and a free R buffer
+        if (n_r < nKT) {
+          const int j = n_r, s = j & 1;
+          if (mbar_try_wait(&ctl->wk_full[s], (j >> 1) & 1) && mbar_try_wait(&ctl->r_free[s], ((j >> 1) & 1) ^ 1)) {
+            tc_fence_after();
+            // descriptors advance in 16-byte units: +2 per 32-byte K step, +1024 for the second K half
+            const uint64_t da = smem_desc_sw128(wq_addr), db = smem_desc_sw128(wk_addr + s * kWTileBytes);
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint64_t off = (ks >> 2) * (kWTileBytes / 32) + (ks & 3) * 2;
+              umma_tf32_ss(tmem_base + kColR + s * kTile, da + off, db + off, kIdescR, ks > 0);
+            }
+            umma_commit(&ctl->wk_empty[s]);
+            umma_commit(&ctl->r_full[s]);
+            ++n_r;
+            progress = true;
+          }
         }
-        umma_commit(&ctl->k_empty[s]);
-        umma_commit(&ctl->s_full);
-        return true;
-      };
-
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; ok && j < nKT; ++j) {
-        if (j + 1 < nKT) {
-          ok = issue_qk(j + 1);
-          if (!ok) break;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (x >= nh) continue;
+          const uint32_t s_col = tmem_base + kColHead + x * kTile;
+          // S_x(j): needs K_x(j) and the head's S region free (PV of tile j-1 folded)
+          if (n_qk[x] < nKT && n_qk[x] == n_pv[x]) {
+            const int j = n_qk[x], s = j & 1;
+            if (mbar_try_wait(&ctl->k_full[x][s], (j >> 1) & 1) &&
+                (j == 0 || mbar_try_wait(&ctl->s_free[x], (j - 1) & 1))) {
+              tc_fence_after();
+              const uint64_t da = smem_desc_sw128(q_addr + x * kQTileBytes);
+              const uint64_t db = smem_desc_sw128(k_addr + (x * 2 + s) * kQTileBytes);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, da + ks * 2, db + ks * 2, kIdescQK, ks > 0);
+              umma_commit(&ctl->k_empty[x][s]);
+              umma_commit(&ctl->s_full[x]);
+              ++n_qk[x];
+              progress = true;
+            }
+          }
+          // PV_x(j): needs P_x(j) in TMEM and V_x(j) in smem
+          if (n_pv[x] < n_qk[x]) {
+            const int j = n_pv[x];
+            if (mbar_try_wait(&ctl->p_full[x], j & 1) && mbar_try_wait(&ctl->v_full[x], j & 1)) {
+              tc_fence_after();
+              const uint64_t dv = smem_desc_sw128(v_addr + x * kQTileBytes);
+#pragma unroll
+              for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
+                umma_f16_ts(s_col + 64, s_col + ks * 8, dv + ks * 128, kIdescPV, ks > 0);
+              umma_commit(&ctl->v_empty[x]);
+              umma_commit(&ctl->pv_done[x]);
+              ++n_pv[x];
+              progress = true;
+            }
+          }
         }
-        const int s = j & 1;
-        if (!mbar_wait_bounded(&ctl->v_full[s], (j >> 1) & 1, abort_flag)) {
-          record_status(p.status, kDevWaitTmaFull);
-          break;
-        }
-        if (!mbar_wait_bounded(&ctl->p_full, j & 1, abort_flag)) {
+        if (progress) {
+          clk.reset();
+        } else if (clk.expired(abort_flag)) {
           record_status(p.status, kDevWaitPReady);
           break;
         }
-        tc_fence_after();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          // 16 keys per step: 8 packed TMEM columns of P, 16 rows (2 KiB) of the V tile
-          umma_f16_ts(tmem_base + kColO, tmem_base + kColP + ks * 8,
-                      smem_desc_sw128(v_addr + s * kQTileBytes + ks * 2048), kIdescPV, (j > 0 || ks > 0));
-        }
-        umma_commit(&ctl->v_empty[s]);
-        umma_commit(&ctl->pv_done);
       }
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int qrow = qt * kTile + row;
-    const bool row_ok = qrow < p.Tq;
-    const int64_t grow = static_cast<int64_t>(b) * p.Tq + (row_ok ? qrow : 0);
-    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const float* wrow = p.weights + grow * p.top_k;
-    const uint4* mask_tile =
-        reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
-    const float sc = p.scale_log2;
-    const float ninf = -__int_as_float(0x7f800000);
+    const int x = (warp - 2) >> 2;              // head of the pair this warp group serves
+    if (x < nh) {
+      const int h = h0 + x;
+      const int quarter = warp & 3;
+      const int row = quarter * 32 + lane;
+      const int qrow = qt * kTile + row;
+      const bool row_ok = qrow < p.Tq;
 
-    float m_true = ninf, m_used = ninf, l = 0.f;
-    int cnt = 0;
-    bool ok = true;
-    uint4 mw = __ldg(mask_tile);
+      SoftmaxRow st;
+      st.lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+      st.s_col = st.lane_base + kColHead + x * kTile;
+      st.mask_tile =
+          reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
+      st.sc = p.scale_log2;
+      st.m_true = st.m_used = -__int_as_float(0x7f800000);
+      st.l = 0.f;
+#pragma unroll
+      for (int i = 0; i < kHeadDim; ++i) st.acc[i] = 0.f;
 
-    for (int j = 0; j < nKT; ++j) {
-      uint4 mw_next = make_uint4(0, 0, 0, 0);
-      if (j + 1 < nKT) mw_next = __ldg(mask_tile + static_cast<int64_t>(j + 1) * kTile);
-      if (!mbar_wait_bounded(&ctl->s_full, j & 1, abort_flag)) {
-        record_status(p.status, kDevWaitAccFull);
-        ok = false;
-        break;
+      // Row constants from the indexer's select passes: threshold bits, how many keys equal
+      // to the threshold are selected, how many exist.  The compare-only fast path is exact when
+      // the threshold is positive and every tie is selected; any other row of the warp
+      // (ties cut by key index, zero-weight members) sends the warp to the bitmask path.
+      bool flagged = false;
+      st.thr_ge = __int_as_float(0x7f800000);   // tail rows: nothing selected
+      if (row_ok) {
+        const int64_t grow = static_cast<int64_t>(b) * p.Tq + qrow;
+        const uint32_t thr_bits = p.st_prefix[grow];
+        flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow]);
+        st.thr_ge = __uint_as_float(thr_bits);
       }
-      tc_fence_after();
-      const uint32_t words[4] = {mw.x, mw.y, mw.z, mw.w};
+      const bool exact = __any_sync(0xffffffffu, flagged);
+      const bool ok = exact ? softmax_tiles<true>(st, ctl, x, nKT, lane, p.status, abort_flag)
+                            : softmax_tiles<false>(st, ctl, x, nKT, lane, p.status, abort_flag);
 
-      // pass 1: maximum over the selected logits of this tile
-      float mt = ninf;
+      if (ok && row_ok) {
+        const float* acc = st.acc;
+        const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
+        const float inv = corr / fmaxf(st.l * corr, 1e-6f);
+        if (p.o_dtype == SWV_F32) {
+          float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColS + c * 32, r);
-        tc_wait_ld();
-        const uint32_t w = words[c];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          if (w & (1u << i)) mt = fmaxf(mt, __uint_as_float(r[i]));
-        }
-      }
-      m_true = fmaxf(m_true, mt * sc);
-      const bool need = m_true > m_used + kRescaleStep;
-      const bool any = __any_sync(0xffffffffu, need);
-      float factor = 1.f;
-      if (any) {
-        factor = (m_true == m_used) ? 1.f : ex2_approx(m_used - m_true);
-        m_used = m_true;
-        l *= factor;
-      }
-      if (j > 0) {
-        if (!mbar_wait_bounded(&ctl->pv_done, (j - 1) & 1, abort_flag)) {
-          record_status(p.status, kDevWaitPvDone);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        if (any) {
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t r[32];
-            tmem_ld32(lane_base + kColO + c * 32, r);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-            tmem_st32(lane_base + kColO + c * 32, r);
+          for (int i = 0; i < kHeadDim; i += 4) {
+            *reinterpret_cast<float4*>(orow + i) =
+                make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
           }
-          tc_wait_st();
-        }
-      }
-
-      // pass 2: probabilities of the selected keys, routing-weighted, to TMEM as bf16
+        } else {
+          uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColS + c * 32, r);
-        tc_wait_ld();
-        if (c == 3) {
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl->s_free);
-        }
-        const uint32_t w = words[c];
-        uint32_t packed[16];
+          for (int i = 0; i < kHeadDim; i += 8) {
+            uint32_t w4[4];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = 0.f, p1 = 0.f;
-          if (w & (1u << i)) {
-            const float wt = __ldg(wrow + cnt);
-            ++cnt;
-            p0 = ex2_approx(fmaf(__uint_as_float(r[i]), sc, -m_used)) * wt;
-            l += p0;
-          }
-          if (w & (2u << i)) {
-            const float wt = __ldg(wrow + cnt);
-            ++cnt;
-            p1 = ex2_approx(fmaf(__uint_as_float(r[i + 1]), sc, -m_used)) * wt;
-            l += p1;
-          }
-          packed[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st16(lane_base + kColP + c * 16, packed);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->p_full);
-      mw = mw_next;
-    }
-
-    if (ok) {
-      if (!mbar_wait_bounded(&ctl->pv_done, (nKT - 1) & 1, abort_flag)) {
-        record_status(p.status, kDevWaitPvDone);
-        ok = false;
-      }
-    }
-    if (ok) {
-      tc_fence_after();
-      const float corr = (m_used == m_true) ? 1.f : ex2_approx(m_used - m_true);
-      const float inv = corr / fmaxf(l * corr, 1e-6f);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColO + c * 32, r);
-        tc_wait_ld();
-        if (row_ok) {
-          if (p.o_dtype == SWV_F32) {
-            float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 4) {
-              float4 v4 = make_float4(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv,
-                                      __uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv);
-              *reinterpret_cast<float4*>(orow + i) = v4;
-            }
-          } else {
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 32;
-#pragma unroll
-            for (int i = 0; i < 32; i += 8) {
-              uint32_t w4[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float a0 = __uint_as_float(r[i + 2 * q]) * inv;
-                const float a1 = __uint_as_float(r[i + 2 * q + 1]) * inv;
-                if (p.o_dtype == SWV_BF16) {
-                  w4[q] = pack_bf16x2(a0, a1);
-                } else {
-                  const __half2 h2 = __floats2half2_rn(a0, a1);
-                  w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                }
+            for (int q = 0; q < 4; ++q) {
+              const float a0 = acc[i + 2 * q] * inv, a1 = acc[i + 2 * q + 1] * inv;
+              if (p.o_dtype == SWV_BF16) {
+                w4[q] = pack_bf16x2(a0, a1);
+              } else {
+                const __half2 h2 = __floats2half2_rn(a0, a1);
+                w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
               }
-              *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
+            *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
           }
         }
       }
@@ -350,133 +508,18 @@ __global__ void __launch_bounds__(192, 2)
   }
 }
 
-// ------------------------------------------------------------- gather kernel
-// One warp per (batch, head, query).  Lanes split the key slots for q.k, then the
-// head dimension for the weighted sum over V.  fp32 throughout; any index list.
-struct GatherParams {
-  const void *q, *k, *v;
-  int64_t qs[4], ks[4], vs[4];
-  const int32_t* idx;
-  const float* valid;
-  const float* rw;
-  int64_t is[3], vls[3], rs[3];
-  void* o;
-  int64_t os[4];
-  int o_dtype;
-  int B, H, Tq, Tk, D, top_k;
-  float scale;
-};
-
-template <typename T>
-__device__ __forceinline__ float ld_f32(const T* p);
-template <>
-__device__ __forceinline__ float ld_f32<float>(const float* p) { return *p; }
-template <>
-__device__ __forceinline__ float ld_f32<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <>
-__device__ __forceinline__ float ld_f32<__half>(const __half* p) { return __half2float(*p); }
-
-__device__ __forceinline__ void st_out(void* o, int dtype, int64_t off, float x) {
-  if (dtype == SWV_F32) static_cast<float*>(o)[off] = x;
-  else if (dtype == SWV_BF16) static_cast<__nv_bfloat16*>(o)[off] = __float2bfloat16_rn(x);
-  else static_cast<__half*>(o)[off] = __float2half_rn(x);
-}
-
-// DPL = head-dim elements per lane in the PV phase; handles any D <= 32*DPL.
-template <typename T, int DPL>
-__global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams p) {
-  constexpr int DMAX = 32 * DPL;
-  __shared__ float qsm[4][DMAX];
-  const int D = p.D;
-  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + wib;
-  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.Tq;
-  if (wid >= total) return;
-  const int qi = static_cast<int>(wid % p.Tq);
-  const int h = static_cast<int>((wid / p.Tq) % p.H);
-  const int b = static_cast<int>(wid / (static_cast<int64_t>(p.Tq) * p.H));
-
-  const T* qrow = static_cast<const T*>(p.q) + b * p.qs[0] + h * p.qs[1] + qi * p.qs[2];
-  for (int d = lane; d < D; d += 32) qsm[wib][d] = ld_f32<T>(qrow + d * p.qs[3]);
-  __syncwarp();
-
-  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1];
-  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
-  const int32_t* idx_row = p.idx + b * p.is[0] + qi * p.is[1];
-  const float* val_row = p.valid + b * p.vls[0] + qi * p.vls[1];
-  const float* rw_row = p.rw + b * p.rs[0] + qi * p.rs[1];
-  const float ninf = -__int_as_float(0x7f800000);
-
-  float o[DPL];
-#pragma unroll
-  for (int i = 0; i < DPL; ++i) o[i] = 0.f;
-  float m = ninf, l = 0.f;
-
-  for (int s0 = 0; s0 < p.top_k; s0 += 32) {
-    const int slot = s0 + lane;
-    const bool in = slot < p.top_k;
-    int id = 0;
-    float w = 0.f;
-    bool ok = false;
-    if (in) {
-      id = idx_row[slot * p.is[2]];
-      ok = val_row[slot * p.vls[2]] > 0.f;
-      w = rw_row[slot * p.rs[2]];
-    }
-    id = min(max(id, 0), p.Tk - 1);
-    float logit = ninf;
-    if (ok) {
-      const T* kr = kbase + static_cast<int64_t>(id) * p.ks[2];
-      float acc = 0.f;
-#pragma unroll 4
-      for (int d = 0; d < D; ++d) acc = fmaf(qsm[wib][d], ld_f32<T>(kr + d * p.ks[3]), acc);
-      logit = acc * p.scale;
-    }
-    float gm = logit;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
-    const float m_new = fmaxf(m, gm);
-    if (m_new == ninf) continue;   // no valid slot so far (uniform across the warp)
-    const float alpha = (m == m_new) ? 1.f : expf(m - m_new);
-    float pj = ok ? expf(logit - m_new) * w : 0.f;
-    float ps = pj;
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
-    l = l * alpha + ps;
-#pragma unroll
-    for (int i = 0; i < DPL; ++i) o[i] *= alpha;
-    for (int j = 0; j < 32; ++j) {
-      const float pp = __shfl_sync(0xffffffffu, pj, j);
-      const int ii = __shfl_sync(0xffffffffu, id, j);
-      if (pp != 0.f) {
-        const T* vr = vbase + static_cast<int64_t>(ii) * p.vs[2];
-#pragma unroll
-        for (int i = 0; i < DPL; ++i) {
-          const int d = lane * DPL + i;
-          if (d < D) o[i] = fmaf(pp, ld_f32<T>(vr + d * p.vs[3]), o[i]);
-        }
-      }
-    }
-    m = m_new;
-  }
-  const float inv = 1.f / fmaxf(l, 1e-6f);
-  const int64_t obase = b * p.os[0] + h * p.os[1] + qi * p.os[2];
-#pragma unroll
-  for (int i = 0; i < DPL; ++i) {
-    const int d = lane * DPL + i;
-    if (d < D) st_out(p.o, p.o_dtype, obase + d * p.os[3], o[i] * inv);
-  }
-}
-
 // ---------------------------------------------------------------------- host
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
+                         uint32_t** kth, uint32_t** neq);
+
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
-                         const int64_t* vs, const uint32_t* maskbits, const float* weights, int top_k, void* o,
+                         const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
                          cudaStream_t st) {
-  if (!q || !k || !v || !maskbits || !weights || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
-  if (B < 1 || H < 1 || Tq < 1 || Tk < 1 || top_k < 1) return SWV_ERR_SHAPE;
+  if (!q || !k || !v || !maskbits || !workspace || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
+  if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (D != kHeadDim) return SWV_ERR_UNSUPPORTED;
   if (o_dtype != SWV_F32 && o_dtype != SWV_BF16 && o_dtype != SWV_F16) return SWV_ERR_DTYPE;
   const int64_t* ss[3] = {qs, ks, vs};
@@ -489,11 +532,21 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   const int osz = o_dtype == SWV_F32 ? 4 : 2;
   if (os[3] != 1 || !aligned16(o) || (os[0] * osz) % 16 || (os[1] * osz) % 16 || (os[2] * osz) % 16)
     return SWV_ERR_ALIGN;
-  if (!aligned16(maskbits) || (reinterpret_cast<uintptr_t>(weights) & 3)) return SWV_ERR_ALIGN;
+  if (!aligned16(maskbits) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return SWV_ERR_ALIGN;
 
-  CUtensorMap tm_q, tm_k, tm_v;
-  int rc = make_tmap_4d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tq, H, B, qs[2] * 2, qs[1] * 2, qs[0] * 2,
-                        kHeadDim, kTile);
+  float *wq = nullptr, *wk = nullptr;
+  uint32_t *st_prefix = nullptr, *st_kth = nullptr, *st_neq = nullptr;
+  dsa_workspace_views(const_cast<void*>(workspace), B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq);
+
+  CUtensorMap tm_wq, tm_wk, tm_q, tm_k, tm_v;
+  int rc = make_tmap_3d(&tm_wq, wq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kIdxDim, Tq, B, kIdxDim * 4,
+                        static_cast<uint64_t>(Tq) * kIdxDim * 4, 32, kTile);
+  if (rc != SWV_OK) return rc;
+  rc = make_tmap_3d(&tm_wk, wk, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kIdxDim, Tk, B, kIdxDim * 4,
+                    static_cast<uint64_t>(Tk) * kIdxDim * 4, 32, kTile);
+  if (rc != SWV_OK) return rc;
+  rc = make_tmap_4d(&tm_q, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tq, H, B, qs[2] * 2, qs[1] * 2, qs[0] * 2,
+                    kHeadDim, kTile);
   if (rc != SWV_OK) return rc;
   rc = make_tmap_4d(&tm_k, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tk, H, B, ks[2] * 2, ks[1] * 2, ks[0] * 2,
                     kHeadDim, kTile);
@@ -503,54 +556,22 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   if (rc != SWV_OK) return rc;
 
   AttnParams p;
-  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.top_k = top_k;
+  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk;
   p.nQT = (Tq + kTile - 1) / kTile;
   p.nKT = (Tk + kTile - 1) / kTile;
-  p.maskbits = maskbits; p.weights = weights;
+  p.nHP = (H + 1) / 2;
+  p.maskbits = maskbits;
+  p.st_prefix = st_prefix; p.st_kth = st_kth; p.st_neq = st_neq;
   p.o = o; p.osb = os[0]; p.osh = os[1]; p.ost = os[2]; p.o_dtype = o_dtype;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   p.status = status;
 
   SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(attn_smem_bytes())));
-  const unsigned grid = static_cast<unsigned>(B) * p.nQT * H;
-  dsa_attn_masked_kernel<<<grid, 192, attn_smem_bytes(), st>>>(tm_q, tm_k, tm_v, p);
+  const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP;
+  dsa_attn_masked_kernel<<<grid, 320, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
-}
-
-template <typename T>
-static int launch_gather(const GatherParams& p, int D, cudaStream_t st) {
-  const int64_t total = static_cast<int64_t>(p.B) * p.H * p.Tq;
-  const unsigned grid = static_cast<unsigned>((total + 3) / 4);
-  if (D <= 32) dsa_attn_gather_kernel<T, 1><<<grid, 128, 0, st>>>(p);
-  else if (D <= 64) dsa_attn_gather_kernel<T, 2><<<grid, 128, 0, st>>>(p);
-  else if (D <= 128) dsa_attn_gather_kernel<T, 4><<<grid, 128, 0, st>>>(p);
-  else if (D <= 256) dsa_attn_gather_kernel<T, 8><<<grid, 128, 0, st>>>(p);
-  else return SWV_ERR_UNSUPPORTED;
-  return cudaGetLastError() == cudaSuccess ? SWV_OK : SWV_ERR_CUDA;
-}
-
-int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
-                         const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
-                         const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
-                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
-                         cudaStream_t st) {
-  if (!q || !k || !v || !idx || !valid || !rw || !o || !status || !qs || !ks || !vs || !is || !vls || !rs || !os)
-    return SWV_ERR_NULL;
-  if (B < 1 || H < 1 || Tq < 1 || Tk < 1 || top_k < 1) return SWV_ERR_SHAPE;
-  if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
-  if (o_dtype != SWV_F32 && o_dtype != SWV_BF16 && o_dtype != SWV_F16) return SWV_ERR_DTYPE;
-  if (D < 1 || D > 256) return SWV_ERR_UNSUPPORTED;
-  GatherParams p;
-  p.q = q; p.k = k; p.v = v; p.idx = idx; p.valid = valid; p.rw = rw; p.o = o; p.o_dtype = o_dtype;
-  for (int i = 0; i < 4; ++i) { p.qs[i] = qs[i]; p.ks[i] = ks[i]; p.vs[i] = vs[i]; p.os[i] = os[i]; }
-  for (int i = 0; i < 3; ++i) { p.is[i] = is[i]; p.vls[i] = vls[i]; p.rs[i] = rs[i]; }
-  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k;
-  p.scale = 1.0f / sqrtf(static_cast<float>(D));
-  if (dtype == SWV_F32) return launch_gather<float>(p, D, st);
-  if (dtype == SWV_BF16) return launch_gather<__nv_bfloat16>(p, D, st);
-  return launch_gather<__half>(p, D, st);
 }
 
 }  // namespace swv

@@ -69,6 +69,7 @@ struct IndexerParams {
   int pass;               // HIST: 0..3
   uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
   uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
+  uint32_t* st_neq;       // [B*Tq] after the last pass: number of keys whose score equals the threshold
   int32_t* idx;           // EMIT outputs
   float* scores;
   uint32_t* maskbits;     // may be null
@@ -267,18 +268,20 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (ok && ch == 0 && row_ok && *abort_flag == 0u) {
         uint32_t kth = pass == 0 ? static_cast<uint32_t>(min(p.top_k, p.Tk)) : p.st_kth[grow];
-        uint32_t cum = 0;
+        uint32_t cum = 0, in_bin = 0;
         int digit = 0;
         for (int bin = 255; bin >= 0; --bin) {
           const uint32_t c = hrow[bin];
           if (cum + c >= kth) {
             digit = bin;
+            in_bin = c;
             break;
           }
           cum += c;
         }
         p.st_prefix[grow] = (prefix << 8) | static_cast<uint32_t>(digit);
         p.st_kth[grow] = kth - cum;
+        if (pass == 3) p.st_neq[grow] = in_bin;
       }
     } else {
       // EMIT: one thread per query row, all 128 columns of every tile, ascending keys.
@@ -370,7 +373,7 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, total;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, total;
 };
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
@@ -383,8 +386,22 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.kth_off = off;
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+  L.neq_off = off;
+  off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.total = off;
   return L;
+}
+
+// Where the collapsed indexer queries / keys of the last indexer call live inside its workspace.
+void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
+                         uint32_t** kth, uint32_t** neq) {
+  const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  *wq = reinterpret_cast<float*>(ws + L.wq_off);
+  *wk = reinterpret_cast<float*>(ws + L.wk_off);
+  *prefix = reinterpret_cast<uint32_t*>(ws + L.prefix_off);
+  *kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
+  *neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
 }
 
 template <typename T>
@@ -457,6 +474,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   p.nKT = (Tk + kTile - 1) / kTile;
   p.st_prefix = reinterpret_cast<uint32_t*>(ws + L.prefix_off);
   p.st_kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
+  p.st_neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
   p.idx = idx; p.scores = scores; p.maskbits = maskbits; p.status = status; p.pass = 0;
 
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeHist>, cudaFuncAttributeMaxDynamicSharedMemorySize,

@@ -106,7 +106,7 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
     check(rc, "swv_dsa_indexer_topk_fwd")
     if _CHECK:
         check_status(dev, "swv_dsa_indexer_topk_fwd")
-    return (idx, valid, scores, mask) if want_mask else (idx, valid, scores)
+    return (idx, valid, scores, (mask, ws)) if want_mask else (idx, valid, scores)
 
 
 def dsa_attention_gather(q, k, v, idx, valid, rw, o):
@@ -137,22 +137,21 @@ def _tma_ok(t):
             all((s * es) % 16 == 0 for s in t.stride()[:-1]))
 
 
-def dsa_attention_masked(q, k, v, mask, weights, o):
-    """Dense tensor-core sweep with the indexer's bitmask and ascending-order weights."""
-    _require_cuda(q, k, v, mask, weights, o)
+def dsa_attention_masked(q, k, v, selection, o):
+    """Dense tensor-core sweep over all key tiles; `selection` is the (bitmask, workspace)
+    pair returned by ``dsa_indexer_topk(..., want_mask=True)`` for the same queries and keys."""
+    mask, ws = selection
+    _require_cuda(q, k, v, mask, ws, o)
     B, H, Tq, D = q.shape
     Tk = k.shape[2]
-    top_k = weights.shape[-1]
     if q.dtype != torch.bfloat16 or D != 64:
         raise SwvError("dsa_attention_masked needs bf16 q/k/v with head_dim 64")
     q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
-    if not weights.is_contiguous():
-        weights = weights.contiguous()
     dev = q.device
     st = status_word(dev)
     rc = lib.swv_dsa_attn_masked_fwd(
         q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), mask.data_ptr(),
-        weights.data_ptr(), top_k, o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D,
+        ws.data_ptr(), o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D,
         st.data_ptr(), _stream(dev))
     check(rc, "swv_dsa_attn_masked_fwd")
     if _CHECK:
@@ -175,10 +174,10 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
     o = torch.empty((B, H, Tq, D), dtype=out_dtype, device=dev)
     dense = q.dtype == torch.bfloat16 and D == 64
     if dense:
-        idx, valid, scores, mask = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True)
+        idx, valid, scores, sel = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True)
         if kv_ready is not None:
             torch.cuda.current_stream(dev).wait_event(kv_ready)
-        dsa_attention_masked(q, k, v, mask, scores, o)
+        dsa_attention_masked(q, k, v, sel, o)
     else:
         idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k)
         if kv_ready is not None:
