@@ -86,42 +86,44 @@ struct TileSmemCtl {
   uint32_t abort_flag;
 };
 
+constexpr int kStageBytes = 4 * 16 * 32 * 4;       // EMIT: per epilogue warp a [16 columns][32 lanes] word tile
 constexpr size_t tile_smem_bytes(int mode) {
-  return 1024 /*alignment slack*/ + kTileBytes * (1 + kStages) + (mode == kModeHist ? kHistBytes : 0) +
+  return 1024 /*alignment slack*/ + kTileBytes * (1 + kStages) + (mode == kModeHist ? kHistBytes : kStageBytes) +
          sizeof(TileSmemCtl) + 64;
 }
 
+// Bit pattern of max(x, 0) for a float x given as bits: as SIGNED integers the negative
+// floats (and -0) are negative, the non-negative floats keep their order.
 __device__ __forceinline__ uint32_t relu_bits(uint32_t raw) {
-  const float x = __uint_as_float(raw);
-  return x > 0.f ? raw : 0u;   // -0, negatives and NaN all map to +0
+  return static_cast<uint32_t>(max(static_cast<int>(raw), 0));
+}
+__device__ __forceinline__ void red_inc_shared(uint32_t saddr) {
+  asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(saddr) : "memory");
+}
+// w |= bit where v >= t / v == t   (one compare + one predicated OR)
+__device__ __forceinline__ void or_bit_if_ge(uint32_t& w, uint32_t v, uint32_t t, uint32_t bit) {
+  asm("{\n\t.reg .pred p;\n\tsetp.ge.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
+}
+__device__ __forceinline__ void or_bit_if_eq(uint32_t& w, uint32_t v, uint32_t t, uint32_t bit) {
+  asm("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
 }
 
-// Adds the 64 scores of one thread (two 32-column TMEM chunks) to its row histogram.
-// Pass 0 bins on the top byte; later passes only count scores whose known high
-// bits equal `prefix` and bin on the next byte.  CHECK guards the ragged last key tile.
-template <bool CHECK>
-__device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint32_t (&r1)[32], uint32_t* hrow,
-                                            int pass, int shift, uint32_t prefix, int nvalid) {
-  if (pass == 0) {
+// Adds the 64 scores of one thread (two 32-column TMEM chunks) to its row histogram
+// (`hrow` = shared-memory address of the row's 256 counters).  A score takes part iff it
+// lies in the bucket [lo, lo + span) already known to hold the threshold (pass 0: all of
+// them); its bin is the next 8 bits.  CHECK guards the ragged last key tile.
+template <bool CHECK, bool FIRST>
+__device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint32_t (&r1)[32], uint32_t hrow,
+                                            int shift, uint32_t lo, uint32_t span, int nvalid) {
 #pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (!CHECK || i < nvalid) atomicAdd(hrow + (relu_bits(r0[i]) >> 24), 1u);
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      if (!CHECK || i + 32 < nvalid) atomicAdd(hrow + (relu_bits(r1[i]) >> 24), 1u);
-    }
-  } else {
-    const int hs = shift + 8;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t u = relu_bits(r0[i]);
-      if ((!CHECK || i < nvalid) && (u >> hs) == prefix) atomicAdd(hrow + ((u >> shift) & 255u), 1u);
-    }
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-      const uint32_t u = relu_bits(r1[i]);
-      if ((!CHECK || i + 32 < nvalid) && (u >> hs) == prefix) atomicAdd(hrow + ((u >> shift) & 255u), 1u);
+  for (int i = 0; i < 64; ++i) {
+    const uint32_t u = relu_bits(i < 32 ? r0[i] : r1[i - 32]);
+    if (CHECK && i >= nvalid) continue;
+    if (FIRST) {
+      red_inc_shared(hrow + ((u >> 24) << 2));
+    } else {
+      const uint32_t t = u - lo;
+      if (t < span) red_inc_shared(hrow + ((t >> shift) << 2));
     }
   }
 }
@@ -139,7 +141,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
   uint8_t* sm_k = smem + kTileBytes;
   uint32_t* sm_hist = reinterpret_cast<uint32_t*>(smem + kTileBytes * (1 + kStages));
   TileSmemCtl* ctl = reinterpret_cast<TileSmemCtl*>(smem + kTileBytes * (1 + kStages) +
-                                                    (MODE == kModeHist ? kHistBytes : 0));
+                                                    (MODE == kModeHist ? kHistBytes : kStageBytes));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -240,6 +242,9 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
       const int shift = 24 - 8 * pass;
       const uint32_t prefix = (pass > 0 && row_ok) ? p.st_prefix[grow] : 0u;
       uint32_t* hrow = sm_hist + row * kHistStride;
+      const uint32_t hrow_s = smem_u32(hrow);
+      const uint32_t lo = pass > 0 ? prefix << (shift + 8) : 0u;     // low edge of the known bucket
+      const uint32_t span = pass > 0 ? 1u << (shift + 8) : 0u;
 
       for (int j = 0; j < nKT; ++j) {
         const int a = j & 1;
@@ -259,10 +264,12 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
         if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
 
         const int nvalid = p.Tk - (j * kTile + ch * 64);   // columns of this half that are real keys
-        if (nvalid >= 64) {
-          hist_update<false>(r0, r1, hrow, pass, shift, prefix, 64);
+        if (pass == 0) {
+          if (nvalid >= 64) hist_update<false, true>(r0, r1, hrow_s, shift, lo, span, 64);
+          else hist_update<true, true>(r0, r1, hrow_s, shift, lo, span, nvalid);
         } else {
-          hist_update<true>(r0, r1, hrow, pass, shift, prefix, nvalid);
+          if (nvalid >= 64) hist_update<false, false>(r0, r1, hrow_s, shift, lo, span, 64);
+          else hist_update<true, false>(r0, r1, hrow_s, shift, lo, span, nvalid);
         }
       }
       asm volatile("bar.sync 1, 256;" ::: "memory");
@@ -285,12 +292,19 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
       }
     } else {
       // EMIT: one thread per query row, all 128 columns of every tile, ascending keys.
+      // Per 16-column unit: (1) branch-free: relu bits to a per-warp shared tile and a
+      // 16-bit member word; (2) a loop over the set bits appends (key, score).
       const uint32_t thr = row_ok ? p.st_prefix[grow] : 0xFFFFFFFFu;
       const uint32_t take_eq = row_ok ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
+      const uint32_t n_eq = row_ok ? p.st_neq[grow] : 0u;      // how many keys == thr exist
+      const bool partial = row_ok && take_eq < n_eq;            // ties cut by key index (lowest first)
+      const bool warp_partial = __any_sync(0xffffffffu, partial);
+      const uint32_t thr_min = partial ? thr + 1u : thr;        // member iff bits >= thr_min (+ chosen ties)
       uint32_t eq_seen = 0;
       int cnt = 0;
       int32_t* idx_row = p.idx + grow * p.top_k;
       float* sc_row = p.scores + grow * p.top_k;
+      uint32_t* stage = sm_hist + ew * (16 * 32);              // the staging tiles share the histogram's slot
       uint4* mask_row = nullptr;
       if (p.maskbits != nullptr) {
         mask_row = reinterpret_cast<uint4*>(p.maskbits) +
@@ -304,39 +318,53 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
           break;
         }
         tc_fence_after();
-        uint32_t words[4];
+        uint32_t words[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t r[32];
-          tmem_ld32(lane_base + a * kTile + c * 32, r);
+        for (int u = 0; u < 8; ++u) {
+          uint32_t r[16];
+          tmem_ld16(lane_base + a * kTile + u * 16, r);
           tc_wait_ld();
-          if (c == 3) {
+          if (u == 7) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
           }
-          const int key0 = j * kTile + c * 32;
-          const int nvalid = p.Tk - key0;
-          uint32_t w = 0;
+          const int key0 = j * kTile + u * 16;
+          uint32_t w = 0, e = 0;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const uint32_t u = relu_bits(r[i]);
-            bool member = u > thr;
-            if (u == thr && i < nvalid) {
-              member = eq_seen < take_eq;
+          for (int i = 0; i < 16; ++i) {
+            const uint32_t v = relu_bits(r[i]);
+            stage[i * 32 + lane] = v;
+            or_bit_if_ge(w, v, thr_min, 1u << i);
+          }
+          if (warp_partial) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) or_bit_if_eq(e, relu_bits(r[i]), thr, 1u << i);
+          }
+          const int nvalid = p.Tk - key0;
+          if (nvalid < 16) {
+            const uint32_t vm = nvalid <= 0 ? 0u : ((1u << nvalid) - 1u);
+            w &= vm;
+            e &= vm;
+          }
+          if (partial) {
+            while (e != 0u && eq_seen < take_eq) {
+              const uint32_t low = e & (0u - e);
+              w |= low;
+              e ^= low;
               ++eq_seen;
             }
-            member = member && (i < nvalid);
-            if (member) {
-              w |= 1u << i;
-              if (row_ok && cnt < p.top_k) {
-                idx_row[cnt] = key0 + i;
-                sc_row[cnt] = __uint_as_float(u);
-              }
-              ++cnt;
-            }
           }
-          words[c] = w;
+          words[u >> 1] |= w << ((u & 1) * 16);
+          while (w != 0u) {
+            const int i = __ffs(w) - 1;
+            w &= w - 1u;
+            if (row_ok && cnt < p.top_k) {
+              idx_row[cnt] = key0 + i;
+              sc_row[cnt] = __uint_as_float(stage[i * 32 + lane]);
+            }
+            ++cnt;
+          }
         }
         if (mask_row != nullptr) {
           mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(words[0], words[1], words[2], words[3]);
