@@ -41,6 +41,7 @@ constexpr int kWTileBytes = kTile * kIdxDim * 4;      // 32 KiB fp32 indexer til
 constexpr int kAttnTmemCols = 512;
 constexpr uint32_t kColR = 0, kColHead = 256;
 constexpr float kRescaleStep = 8.0f;                  // raise the stabiliser only in steps of 2^8
+constexpr float kMaxBound = 40.0f;                    // one-pass path: largest admissible |logit| bound (log2 units)
 
 // shared memory map (bytes from the 1024-aligned base)
 constexpr int kOffWq = 0;
@@ -54,6 +55,9 @@ struct AttnParams {
   int B, H, Tq, Tk, nQT, nKT, nHP;
   const uint32_t* maskbits;
   const uint32_t *st_prefix, *st_kth, *st_neq;   // per query row, written by the indexer's select passes
+  const uint32_t* kmax2;                         // [B*H] max squared key norm, float bits
+  const __nv_bfloat16* q;
+  int64_t qsb, qsh, qst;
   void* o;
   int64_t osb, osh, ost;
   int o_dtype;
@@ -74,12 +78,19 @@ struct AttnCtl {
 
 constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
 
-// gives up (and raises the CTA's abort flag) after kWaitLimitNs without progress
+// For the polling threads: gives up (and raises the CTA's abort flag) after kWaitLimitNs
+// without progress.  The clock is read only every 1024 idle polls.
 struct ProgressClock {
   uint64_t t0;
-  __device__ void reset() { t0 = globaltimer_ns(); }
+  uint32_t idle;
+  __device__ void reset() { idle = 0; }
   __device__ bool expired(volatile uint32_t* abort_flag) {
+    if ((++idle & 1023u) != 0u) return false;
     if (*abort_flag != 0u) return true;
+    if (idle == 1024u) {
+      t0 = globaltimer_ns();
+      return false;
+    }
     if (globaltimer_ns() - t0 > kWaitLimitNs) {
       *abort_flag = 1u;
       return true;
@@ -89,11 +100,7 @@ struct ProgressClock {
 };
 
 // ------------------------------------------------------------ softmax helpers
-// m = max(m, s) where r >= thr   (one compare + one predicated max)
-__device__ __forceinline__ void max_where_ge(float& m, float s, float r, float thr) {
-  asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %2, %3;\n\t@p max.f32 %0, %0, %1;\n\t}" : "+f"(m) : "f"(s), "f"(r), "f"(thr));
-}
-// r >= thr ? v : 0
+// r >= thr ? v : 0     (one compare + one select)
 __device__ __forceinline__ float keep_where_ge(float v, float r, float thr) {
   float out;
   asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %2, %3;\n\tselp.f32 %0, %1, 0f00000000, p;\n\t}"
@@ -106,27 +113,111 @@ struct SoftmaxRow {
   float acc[kHeadDim];     // output accumulator of this query row, relative to 2^m_used
   float m_true, m_used, l;
   float thr_ge;            // fast path: a key is selected iff its raw score >= thr_ge
+  float bound;             // fast path: log2-domain upper bound of every logit of the row
   float sc;
   uint32_t lane_base, s_col;
   const uint4* mask_tile;
 };
 
-// The per-tile loop of one softmax thread (one query row of one head).
-//   kExact = false: membership by comparing the recomputed score with the row threshold.
-//   kExact = true : membership from the indexer's bitmask (ties cut by key index, members
-//                   with zero weight); routing weight relu(score).
-template <bool kExact>
-__device__ __forceinline__ bool softmax_tiles(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane, int* status,
-                                              volatile uint32_t* abort_flag) {
-  const float ninf = -__int_as_float(0x7f800000);
-  const float sc = st.sc, thr = st.thr_ge;
+// Fold the PV product of the finished tile (64 fp32 columns) into the register accumulator.
+__device__ __forceinline__ void fold_pv(SoftmaxRow& st) {
+  uint32_t oa[16], ob[16];
+  tmem_ld16(st.s_col + 64, oa);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    tc_wait_ld();
+    if (c + 1 < 4) {
+      if (c & 1) tmem_ld16(st.s_col + 64 + (c + 1) * 16, oa);
+      else tmem_ld16(st.s_col + 64 + (c + 1) * 16, ob);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) st.acc[c * 16 + i] += __uint_as_float((c & 1) ? ob[i] : oa[i]);
+  }
+}
+
+// Fast per-tile loop: one pass.  Every logit of the row is bounded by st.bound (Cauchy-Schwarz
+// on the row's q and the largest key norm of the head), so 2^(s*sc - bound) never overflows
+// and the accumulator never needs rescaling.  Membership: recomputed score >= row threshold.
+__device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
+                                                   int* status, volatile uint32_t* abort_flag) {
+  const float sc = st.sc, thr = st.thr_ge, neg_b = -st.bound;
   const uint32_t s_col = st.s_col;
-  uint4 mw = make_uint4(0, 0, 0, 0);
-  if (kExact) mw = __ldg(st.mask_tile);
+  float l0 = 0.f, l1 = 0.f;
+  for (int j = 0; j < nKT; ++j) {
+    const uint32_t r_col = st.lane_base + kColR + (j & 1) * kTile;
+    if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag) ||
+        !mbar_wait_bounded(&ctl->r_full[j & 1], (j >> 1) & 1, abort_flag)) {
+      record_status(status, kDevWaitAccFull);
+      return false;
+    }
+    tc_fence_after();
+    // 16 columns at a time; the loads of unit u+1 are in flight while unit u is computed
+    uint32_t sa[16], ra[16], sb[16], rb[16];
+    tmem_ld16(s_col, sa);
+    tmem_ld16(r_col, ra);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      tc_wait_ld();
+      if (u + 1 < 8) {
+        if (u & 1) {
+          tmem_ld16(s_col + (u + 1) * 16, sa);
+          tmem_ld16(r_col + (u + 1) * 16, ra);
+        } else {
+          tmem_ld16(s_col + (u + 1) * 16, sb);
+          tmem_ld16(r_col + (u + 1) * 16, rb);
+        }
+      } else {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
+      }
+      uint32_t packed[8];
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) {
+        const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
+        const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
+        const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
+        const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
+        const float p0 = keep_where_ge(ex2_approx(fmaf(s0, sc, neg_b)) * r0, r0, thr);
+        const float p1 = keep_where_ge(ex2_approx(fmaf(s1, sc, neg_b)) * r1, r1, thr);
+        l0 += p0;
+        l1 += p1;
+        packed[i >> 1] = pack_bf16x2(p0, p1);
+      }
+      tmem_st8(s_col + u * 8, packed);
+    }
+    tc_wait_st();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+
+    if (!mbar_wait_bounded(&ctl->pv_done[x], j & 1, abort_flag)) {
+      record_status(status, kDevWaitPvDone);
+      return false;
+    }
+    tc_fence_after();
+    fold_pv(st);
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->s_free[x]);
+  }
+  st.l = l0 + l1;
+  return true;
+}
+
+// Exact per-tile loop: two passes.  Membership from the indexer's bitmask (ties cut by key
+// index, members with zero weight), routing weight relu(score), exact maximum over the
+// selected logits tracked beside the lazily raised stabiliser.
+__device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
+                                                    int* status, volatile uint32_t* abort_flag) {
+  const float ninf = -__int_as_float(0x7f800000);
+  const float sc = st.sc;
+  const uint32_t s_col = st.s_col;
+  uint4 mw = __ldg(st.mask_tile);
 
   for (int j = 0; j < nKT; ++j) {
     uint4 mw_next = make_uint4(0, 0, 0, 0);
-    if (kExact && j + 1 < nKT) mw_next = __ldg(st.mask_tile + static_cast<int64_t>(j + 1) * kTile);
+    if (j + 1 < nKT) mw_next = __ldg(st.mask_tile + static_cast<int64_t>(j + 1) * kTile);
     const uint32_t words[4] = {mw.x, mw.y, mw.z, mw.w};
     const uint32_t r_col = st.lane_base + kColR + (j & 1) * kTile;
 
@@ -137,32 +228,21 @@ __device__ __forceinline__ bool softmax_tiles(SoftmaxRow& st, AttnCtl* ctl, int 
     }
     tc_fence_after();
 
-    // pass 1: maximum over the selected logits of this tile (four independent chains)
-    float mt0 = ninf, mt1 = ninf, mt2 = ninf, mt3 = ninf;
-#pragma unroll
+    // pass 1: maximum over the selected logits of this tile
+    float mt0 = ninf, mt1 = ninf;
+#pragma unroll 1
     for (int u = 0; u < 8; ++u) {
-      uint32_t s[16], r[16];
+      uint32_t s[16];
       tmem_ld16(s_col + u * 16, s);
-      if (!kExact) tmem_ld16(r_col + u * 16, r);
       tc_wait_ld();
       const uint32_t w = words[u >> 1] >> ((u & 1) * 16);
 #pragma unroll
-      for (int i = 0; i < 16; i += 4) {
-        if (kExact) {
-          mt0 = fmaxf(mt0, (w & (1u << i)) ? __uint_as_float(s[i]) : ninf);
-          mt1 = fmaxf(mt1, (w & (2u << i)) ? __uint_as_float(s[i + 1]) : ninf);
-          mt2 = fmaxf(mt2, (w & (4u << i)) ? __uint_as_float(s[i + 2]) : ninf);
-          mt3 = fmaxf(mt3, (w & (8u << i)) ? __uint_as_float(s[i + 3]) : ninf);
-        } else {
-          max_where_ge(mt0, __uint_as_float(s[i]), __uint_as_float(r[i]), thr);
-          max_where_ge(mt1, __uint_as_float(s[i + 1]), __uint_as_float(r[i + 1]), thr);
-          max_where_ge(mt2, __uint_as_float(s[i + 2]), __uint_as_float(r[i + 2]), thr);
-          max_where_ge(mt3, __uint_as_float(s[i + 3]), __uint_as_float(r[i + 3]), thr);
-        }
+      for (int i = 0; i < 16; i += 2) {
+        mt0 = fmaxf(mt0, (w & (1u << i)) ? __uint_as_float(s[i]) : ninf);
+        mt1 = fmaxf(mt1, (w & (2u << i)) ? __uint_as_float(s[i + 1]) : ninf);
       }
     }
-    const float mt = fmaxf(fmaxf(mt0, mt1), fmaxf(mt2, mt3));
-    st.m_true = fmaxf(st.m_true, mt * sc);
+    st.m_true = fmaxf(st.m_true, fmaxf(mt0, mt1) * sc);
     if (__any_sync(0xffffffffu, st.m_true > st.m_used + kRescaleStep)) {
       const float factor = (st.m_true == st.m_used) ? 1.f : ex2_approx(st.m_used - st.m_true);
       st.m_used = st.m_true;
@@ -172,36 +252,22 @@ __device__ __forceinline__ bool softmax_tiles(SoftmaxRow& st, AttnCtl* ctl, int 
     }
     const float neg_m = -st.m_used;
 
-    // pass 2: routing-weighted probabilities of the selected keys -> TMEM (bf16),
-    // 16 columns at a time to keep the live register set small
+    // pass 2: routing-weighted probabilities of the selected keys -> TMEM (bf16)
     float l0 = 0.f, l1 = 0.f;
-#pragma unroll
+#pragma unroll 1
     for (int u = 0; u < 8; ++u) {
       uint32_t s[16], r[16];
       tmem_ld16(s_col + u * 16, s);
       tmem_ld16(r_col + u * 16, r);
       tc_wait_ld();
-      if (u == 7) {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
-      }
       const uint32_t w = words[u >> 1] >> ((u & 1) * 16);
       uint32_t packed[8];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
-        const float e0 = ex2_approx(fmaf(__uint_as_float(s[i]), sc, neg_m));
-        const float e1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sc, neg_m));
-        float p0, p1;
-        if (kExact) {
-          p0 = e0 * fmaxf(__uint_as_float(r[i]), 0.f);
-          p1 = e1 * fmaxf(__uint_as_float(r[i + 1]), 0.f);
-          p0 = (w & (1u << i)) ? p0 : 0.f;
-          p1 = (w & (2u << i)) ? p1 : 0.f;
-        } else {
-          p0 = keep_where_ge(e0 * __uint_as_float(r[i]), __uint_as_float(r[i]), thr);
-          p1 = keep_where_ge(e1 * __uint_as_float(r[i + 1]), __uint_as_float(r[i + 1]), thr);
-        }
+        float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sc, neg_m)) * fmaxf(__uint_as_float(r[i]), 0.f);
+        float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sc, neg_m)) * fmaxf(__uint_as_float(r[i + 1]), 0.f);
+        p0 = (w & (1u << i)) ? p0 : 0.f;
+        p1 = (w & (2u << i)) ? p1 : 0.f;
         l0 += p0;
         l1 += p1;
         packed[i >> 1] = pack_bf16x2(p0, p1);
@@ -209,31 +275,60 @@ __device__ __forceinline__ bool softmax_tiles(SoftmaxRow& st, AttnCtl* ctl, int 
       tmem_st8(s_col + u * 8, packed);
     }
     st.l += l0 + l1;
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
     tc_wait_st();
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->p_full[x]);
 
-    // fold the PV product of this tile into the register accumulator
     if (!mbar_wait_bounded(&ctl->pv_done[x], j & 1, abort_flag)) {
       record_status(status, kDevWaitPvDone);
       return false;
     }
     tc_fence_after();
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t o[16];
-      tmem_ld16(s_col + 64 + c * 16, o);
-      tc_wait_ld();
-#pragma unroll
-      for (int i = 0; i < 16; ++i) st.acc[c * 16 + i] += __uint_as_float(o[i]);
-    }
+    fold_pv(st);
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->s_free[x]);
     mw = mw_next;
   }
   return true;
+}
+
+// max over keys of |K[b,h,k,:]|^2, as float bits (non-negative floats order like unsigned ints)
+__global__ void key_norm_max_kernel(const __nv_bfloat16* __restrict__ k, int64_t sb, int64_t sh, int64_t st_,
+                                    int B, int H, int Tk, uint32_t* __restrict__ out) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(B) * H * Tk;
+  float n2 = 0.f;
+  int bh = 0;
+  if (gid < total) {
+    const int t = static_cast<int>(gid % Tk);
+    bh = static_cast<int>(gid / Tk);
+    const int h = bh % H, b = bh / H;
+    const uint4* row = reinterpret_cast<const uint4*>(k + b * sb + h * sh + t * st_);
+#pragma unroll
+    for (int i = 0; i < kHeadDim / 8; ++i) {
+      const uint4 v = __ldg(row + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
+        n2 = fmaf(lo, lo, fmaf(hi, hi, n2));
+      }
+    }
+  }
+  // keys of one (b,h) are contiguous in gid: reduce inside the warp when it does not straddle
+  const int bh0 = __shfl_sync(0xffffffffu, bh, 0);
+  if (__all_sync(0xffffffffu, bh == bh0)) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) n2 = fmaxf(n2, __shfl_xor_sync(0xffffffffu, n2, off));
+    if ((threadIdx.x & 31) == 0 && gid < total) atomicMax(out + bh, __float_as_uint(n2));
+  } else if (gid < total) {
+    atomicMax(out + bh, __float_as_uint(n2));
+  }
 }
 
 __global__ void __launch_bounds__(320, 1)
@@ -311,7 +406,7 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
         for (int x = 0; x < 2; ++x) done = done && (x >= nh || (n_k[x] == nKT && n_v[x] == nKT));
         if (done) break;
-        if (n_wk < nKT && mbar_try_wait(&ctl->wk_empty[n_wk & 1], ((n_wk >> 1) & 1) ^ 1)) {
+        if (n_wk < nKT && mbar_test_wait(&ctl->wk_empty[n_wk & 1], ((n_wk >> 1) & 1) ^ 1)) {
           uint8_t* dst = smem + kOffWk + (n_wk & 1) * kWTileBytes;
           mbar_expect_tx(&ctl->wk_full[n_wk & 1], kWTileBytes);
           tma_load_3d(dst, &tm_wk, &ctl->wk_full[n_wk & 1], 0, n_wk * kTile, b);
@@ -323,7 +418,7 @@ __global__ void __launch_bounds__(320, 1)
         for (int x = 0; x < 2; ++x) {
           if (x >= nh) continue;
           int j = n_k[x];
-          if (j < nKT && mbar_try_wait(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1)) {
+          if (j < nKT && mbar_test_wait(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1)) {
             mbar_expect_tx(&ctl->k_full[x][j & 1], kQTileBytes);
             tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, j * kTile,
                         h0 + x, b);
@@ -331,7 +426,7 @@ __global__ void __launch_bounds__(320, 1)
             progress = true;
           }
           j = n_v[x];
-          if (j < nKT && mbar_try_wait(&ctl->v_empty[x], (j & 1) ^ 1)) {
+          if (j < nKT && mbar_test_wait(&ctl->v_empty[x], (j & 1) ^ 1)) {
             mbar_expect_tx(&ctl->v_full[x], kQTileBytes);
             tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, j * kTile, h0 + x, b);
             ++n_v[x];
@@ -370,7 +465,7 @@ __global__ void __launch_bounds__(320, 1)
         // R(j): needs the indexer key tile and a free R buffer
         if (n_r < nKT) {
           const int j = n_r, s = j & 1;
-          if (mbar_try_wait(&ctl->wk_full[s], (j >> 1) & 1) && mbar_try_wait(&ctl->r_free[s], ((j >> 1) & 1) ^ 1)) {
+          if (mbar_test_wait(&ctl->wk_full[s], (j >> 1) & 1) && mbar_test_wait(&ctl->r_free[s], ((j >> 1) & 1) ^ 1)) {
             tc_fence_after();
             // descriptors advance in 16-byte units: +2 per 32-byte K step, +1024 for the second K half
             const uint64_t da = smem_desc_sw128(wq_addr), db = smem_desc_sw128(wk_addr + s * kWTileBytes);
@@ -392,8 +487,8 @@ __global__ void __launch_bounds__(320, 1)
           // S_x(j): needs K_x(j) and the head's S region free (PV of tile j-1 folded)
           if (n_qk[x] < nKT && n_qk[x] == n_pv[x]) {
             const int j = n_qk[x], s = j & 1;
-            if (mbar_try_wait(&ctl->k_full[x][s], (j >> 1) & 1) &&
-                (j == 0 || mbar_try_wait(&ctl->s_free[x], (j - 1) & 1))) {
+            if (mbar_test_wait(&ctl->k_full[x][s], (j >> 1) & 1) &&
+                (j == 0 || mbar_test_wait(&ctl->s_free[x], (j - 1) & 1))) {
               tc_fence_after();
               const uint64_t da = smem_desc_sw128(q_addr + x * kQTileBytes);
               const uint64_t db = smem_desc_sw128(k_addr + (x * 2 + s) * kQTileBytes);
@@ -408,7 +503,7 @@ __global__ void __launch_bounds__(320, 1)
           // PV_x(j): needs P_x(j) in TMEM and V_x(j) in smem
           if (n_pv[x] < n_qk[x]) {
             const int j = n_pv[x];
-            if (mbar_try_wait(&ctl->p_full[x], j & 1) && mbar_try_wait(&ctl->v_full[x], j & 1)) {
+            if (mbar_test_wait(&ctl->p_full[x], j & 1) && mbar_test_wait(&ctl->v_full[x], j & 1)) {
               tc_fence_after();
               const uint64_t dv = smem_desc_sw128(v_addr + x * kQTileBytes);
 #pragma unroll
@@ -451,25 +546,45 @@ __global__ void __launch_bounds__(320, 1)
       for (int i = 0; i < kHeadDim; ++i) st.acc[i] = 0.f;
 
       // Row constants from the indexer's select passes: threshold bits, how many keys equal
-      // to the threshold are selected, how many exist.  The compare-only fast path is exact when
-      // the threshold is positive and every tie is selected; any other row of the warp
-      // (ties cut by key index, zero-weight members) sends the warp to the bitmask path.
+      // to the threshold are selected, how many exist.  The one-pass path is exact when
+      //   - the threshold is positive and every tie is selected (membership = score >= thr),
+      //   - every weight exceeds the 1e-6 clamp on the denominator (the clamp cannot bind),
+      //   - the logits of the row are provably small (|s*sc| <= bound <= kMaxBound).
+      // Any other row sends its warp to the two-pass bitmask path.
       bool flagged = false;
       st.thr_ge = __int_as_float(0x7f800000);   // tail rows: nothing selected
+      st.bound = 0.f;
       if (row_ok) {
         const int64_t grow = static_cast<int64_t>(b) * p.Tq + qrow;
         const uint32_t thr_bits = p.st_prefix[grow];
-        flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow]);
         st.thr_ge = __uint_as_float(thr_bits);
+        const uint4* qv = reinterpret_cast<const uint4*>(p.q + b * p.qsb + h * p.qsh + qrow * p.qst);
+        float q2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < kHeadDim / 8; ++i) {
+          const uint4 v = __ldg(qv + i);
+          const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float lo = __uint_as_float(w[q] << 16), hi = __uint_as_float(w[q] & 0xffff0000u);
+            q2 = fmaf(lo, lo, fmaf(hi, hi, q2));
+          }
+        }
+        const float k2 = __uint_as_float(p.kmax2[b * p.H + h]);
+        st.bound = sqrtf(q2 * k2) * st.sc * 1.001f + 1e-3f;
+        flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow] && st.thr_ge >= 4e-6f &&
+                    st.bound <= kMaxBound);
       }
       const bool exact = __any_sync(0xffffffffu, flagged);
-      const bool ok = exact ? softmax_tiles<true>(st, ctl, x, nKT, lane, p.status, abort_flag)
-                            : softmax_tiles<false>(st, ctl, x, nKT, lane, p.status, abort_flag);
+      const bool ok = exact ? softmax_tiles_exact(st, ctl, x, nKT, lane, p.status, abort_flag)
+                            : softmax_tiles_fast(st, ctl, x, nKT, lane, p.status, abort_flag);
 
       if (ok && row_ok) {
         const float* acc = st.acc;
+        // exact path: the reference's clamp, out = O c / max(l c, 1e-6), c = 2^(m_used - m_true);
+        // one-pass path: the clamp cannot bind, out = O / l.
         const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
-        const float inv = corr / fmaxf(st.l * corr, 1e-6f);
+        const float inv = exact ? corr / fmaxf(st.l * corr, 1e-6f) : 1.f / st.l;
         if (p.o_dtype == SWV_F32) {
           float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost;
 #pragma unroll
@@ -512,7 +627,7 @@ __global__ void __launch_bounds__(320, 1)
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
-                         uint32_t** kth, uint32_t** neq);
+                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2);
 
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
@@ -535,8 +650,9 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   if (!aligned16(maskbits) || (reinterpret_cast<uintptr_t>(workspace) & 255)) return SWV_ERR_ALIGN;
 
   float *wq = nullptr, *wk = nullptr;
-  uint32_t *st_prefix = nullptr, *st_kth = nullptr, *st_neq = nullptr;
-  dsa_workspace_views(const_cast<void*>(workspace), B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq);
+  uint32_t *st_prefix = nullptr, *st_kth = nullptr, *st_neq = nullptr, *kmax2 = nullptr;
+  dsa_workspace_views(const_cast<void*>(workspace), B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq, &kmax2);
+  if (static_cast<int64_t>(B) * H > 1024) return SWV_ERR_UNSUPPORTED;
 
   CUtensorMap tm_wq, tm_wk, tm_q, tm_k, tm_v;
   int rc = make_tmap_3d(&tm_wq, wq, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, kIdxDim, Tq, B, kIdxDim * 4,
@@ -562,10 +678,18 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   p.nHP = (H + 1) / 2;
   p.maskbits = maskbits;
   p.st_prefix = st_prefix; p.st_kth = st_kth; p.st_neq = st_neq;
+  p.kmax2 = kmax2;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.qsb = qs[0]; p.qsh = qs[1]; p.qst = qs[2];
   p.o = o; p.osb = os[0]; p.osh = os[1]; p.ost = os[2]; p.o_dtype = o_dtype;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   p.status = status;
 
+  SWV_CUDA_OK(cudaMemsetAsync(kmax2, 0, static_cast<size_t>(B) * H * 4, st));
+  {
+    const int64_t total = static_cast<int64_t>(B) * H * Tk;
+    key_norm_max_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(k), ks[0], ks[1], ks[2], B, H, Tk, kmax2);
+  }
   SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(attn_smem_bytes())));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP;

@@ -100,6 +100,12 @@ __device__ __forceinline__ uint32_t relu_bits(uint32_t raw) {
 __device__ __forceinline__ void red_inc_shared(uint32_t saddr) {
   asm volatile("red.shared.add.u32 [%0], 1;" ::"r"(saddr) : "memory");
 }
+// if (t < span) ++*saddr, as one compare and one predicated reduction (no branch)
+__device__ __forceinline__ void red_inc_shared_if_lt(uint32_t saddr, uint32_t t, uint32_t span) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(saddr), "r"(t),
+               "r"(span)
+               : "memory");
+}
 // w |= bit where v >= t / v == t   (one compare + one predicated OR)
 __device__ __forceinline__ void or_bit_if_ge(uint32_t& w, uint32_t v, uint32_t t, uint32_t bit) {
   asm("{\n\t.reg .pred p;\n\tsetp.ge.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
@@ -114,16 +120,18 @@ __device__ __forceinline__ void or_bit_if_eq(uint32_t& w, uint32_t v, uint32_t t
 // them); its bin is the next 8 bits.  CHECK guards the ragged last key tile.
 template <bool CHECK, bool FIRST>
 __device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint32_t (&r1)[32], uint32_t hrow,
-                                            int shift, uint32_t lo, uint32_t span, int nvalid) {
+                                            int shift, uint32_t lo, uint32_t span, int nvalid, uint32_t& zeros) {
 #pragma unroll
   for (int i = 0; i < 64; ++i) {
     const uint32_t u = relu_bits(i < 32 ? r0[i] : r1[i - 32]);
-    if (CHECK && i >= nvalid) continue;
     if (FIRST) {
-      red_inc_shared(hrow + ((u >> 24) << 2));
+      // scores that are exactly zero (half of them after the ReLU) are counted in a register
+      const uint32_t t = CHECK ? (i < nvalid ? u : 0xFFFFFFFFu) : u;
+      zeros += (t == 0u) ? 1u : 0u;
+      red_inc_shared_if_lt(hrow + ((u >> 24) << 2), t - 1u, 0xFFFFFFFEu);
     } else {
       const uint32_t t = u - lo;
-      if (t < span) red_inc_shared(hrow + ((t >> shift) << 2));
+      red_inc_shared_if_lt(hrow + ((t >> shift) << 2), CHECK ? (i < nvalid ? t : span) : t, span);
     }
   }
 }
@@ -245,6 +253,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
       const uint32_t hrow_s = smem_u32(hrow);
       const uint32_t lo = pass > 0 ? prefix << (shift + 8) : 0u;     // low edge of the known bucket
       const uint32_t span = pass > 0 ? 1u << (shift + 8) : 0u;
+      uint32_t zeros = 0;
 
       for (int j = 0; j < nKT; ++j) {
         const int a = j & 1;
@@ -265,13 +274,14 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
 
         const int nvalid = p.Tk - (j * kTile + ch * 64);   // columns of this half that are real keys
         if (pass == 0) {
-          if (nvalid >= 64) hist_update<false, true>(r0, r1, hrow_s, shift, lo, span, 64);
-          else hist_update<true, true>(r0, r1, hrow_s, shift, lo, span, nvalid);
+          if (nvalid >= 64) hist_update<false, true>(r0, r1, hrow_s, shift, lo, span, 64, zeros);
+          else hist_update<true, true>(r0, r1, hrow_s, shift, lo, span, nvalid, zeros);
         } else {
-          if (nvalid >= 64) hist_update<false, false>(r0, r1, hrow_s, shift, lo, span, 64);
-          else hist_update<true, false>(r0, r1, hrow_s, shift, lo, span, nvalid);
+          if (nvalid >= 64) hist_update<false, false>(r0, r1, hrow_s, shift, lo, span, 64, zeros);
+          else hist_update<true, false>(r0, r1, hrow_s, shift, lo, span, nvalid, zeros);
         }
       }
+      if (zeros != 0u) atomicAdd(hrow, zeros);
       asm volatile("bar.sync 1, 256;" ::: "memory");
       if (ok && ch == 0 && row_ok && *abort_flag == 0u) {
         uint32_t kth = pass == 0 ? static_cast<uint32_t>(min(p.top_k, p.Tk)) : p.st_kth[grow];
@@ -401,7 +411,7 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, total;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, total;
 };
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
@@ -416,13 +426,15 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.neq_off = off;
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+  L.kmax_off = off;     // per (batch, head) key-norm maxima of the attention kernel, up to 1024 entries
+  off += 4096;
   L.total = off;
   return L;
 }
 
 // Where the collapsed indexer queries / keys of the last indexer call live inside its workspace.
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
-                         uint32_t** kth, uint32_t** neq) {
+                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2) {
   const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   *wq = reinterpret_cast<float*>(ws + L.wq_off);
@@ -430,6 +442,7 @@ void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, flo
   *prefix = reinterpret_cast<uint32_t*>(ws + L.prefix_off);
   *kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
   *neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
+  *kmax2 = reinterpret_cast<uint32_t*>(ws + L.kmax_off);
 }
 
 template <typename T>
