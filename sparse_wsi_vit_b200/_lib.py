@@ -8,7 +8,7 @@ import os
 from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint32, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libswv_b200.so")
+LIB_PATH = os.environ.get("SWV_B200_LIB") or os.path.join(_HERE, "csrc", "libswv_b200.so")
 
 SWV_F32, SWV_BF16, SWV_F16 = 0, 1, 2
 

@@ -13,21 +13,22 @@
 //   warp 0      : TMA producer: collapsed indexer queries + Q of both heads once;
 //                 per key tile the collapsed indexer keys, K and V of both heads.
 //   warp 1      : UMMA issuer (one thread, event driven):
-//                   R   = wq wk^T        TF32, the routing-weight tile, shared by both heads;
+//                   R    = wq wk^T       TF32, the routing-weight tile, shared by both heads;
 //                                        bit-identical to the scores the indexer emitted
-//                   S_h = Q_h K_h^T      bf16
-//                   PV_h = P_h V_h       P from TMEM, V MN-major from smem
+//                   S_h  = Q_h K_h^T     bf16
+//                   O_h += P_h V_h       P from TMEM, V MN-major from smem, O stays in TMEM
 //   warps 2..5  : softmax of head 0, one thread per query row
 //   warps 6..9  : softmax of head 1
-// Per (row, tile): membership from the tile-major bitmask the indexer wrote,
-//   p = 2^(s*scale*log2e - m_used) * relu(R)   for selected keys, 0 otherwise.
-// The exact maximum over the selected logits is tracked beside the lazily
-// raised stabiliser m_used, so the reference's 1e-6 clamp on the denominator
-// is reproduced: out = O*c / max(l*c, 1e-6), c = 2^(m_used - m_true).
-// The output accumulator lives in registers (64 fp32 per row).
-// TMEM (512 columns): R double buffer [0,256) | per head 128 columns at 256 + 128*h:
-//   S fp32 [0,128); P (bf16x2) overwrites [0,64) as the row is consumed; the PV
-//   product of the tile lands in [64,128) and is folded into the registers.
+// Two softmax paths, chosen per warp from the row constants the indexer left behind:
+//   one pass  : a key is selected iff its recomputed score >= the row threshold; the
+//               stabiliser is a constant Cauchy-Schwarz bound of the row's logits, so there
+//               is no running maximum and no rescaling:  p = 2^(s*c - bound) * score.
+//   two pass  : membership from the tile-major bitmask (ties cut by key index, members of
+//               weight zero), exact maximum over the selected logits beside a lazily raised
+//               stabiliser, the reference's 1e-6 clamp on the denominator reproduced:
+//               out = O*c / max(l*c, 1e-6), c = 2^(m_used - m_true).
+// TMEM (512 columns): R [0,128) | S_h fp32 [128+128h, +128), P_h (bf16x2) overwrites the
+// first 64 columns of S_h as the row is consumed | O_h fp32 [384+64h, +64).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -39,7 +40,7 @@ constexpr int kHeadDim = 64;
 constexpr int kQTileBytes = kTile * kHeadDim * 2;     // 16 KiB bf16 tile
 constexpr int kWTileBytes = kTile * kIdxDim * 4;      // 32 KiB fp32 indexer tile (two K halves)
 constexpr int kAttnTmemCols = 512;
-constexpr uint32_t kColR = 0, kColHead = 256;
+constexpr uint32_t kColR = 0, kColS = 128, kColO = 384;
 constexpr float kRescaleStep = 8.0f;                  // raise the stabiliser only in steps of 2^8
 constexpr float kMaxBound = 40.0f;                    // one-pass path: largest admissible |logit| bound (log2 units)
 
@@ -70,8 +71,8 @@ struct AttnCtl {
   uint64_t wk_full[2], wk_empty[2];
   uint64_t k_full[2][2], k_empty[2][2];
   uint64_t v_full[2], v_empty[2];
-  uint64_t r_full[2], r_free[2];
-  uint64_t s_full[2], s_free[2], p_full[2], pv_done[2];
+  uint64_t r_full, r_free;
+  uint64_t s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -110,43 +111,26 @@ __device__ __forceinline__ float keep_where_ge(float v, float r, float thr) {
 }
 
 struct SoftmaxRow {
-  float acc[kHeadDim];     // output accumulator of this query row, relative to 2^m_used
   float m_true, m_used, l;
-  float thr_ge;            // fast path: a key is selected iff its raw score >= thr_ge
-  float bound;             // fast path: log2-domain upper bound of every logit of the row
+  float thr_ge;            // one-pass path: a key is selected iff its raw score >= thr_ge
+  float bound;             // one-pass path: log2-domain upper bound of every logit of the row
   float sc;
-  uint32_t lane_base, s_col;
+  uint32_t lane_base, s_col, o_col;
   const uint4* mask_tile;
 };
 
-// Fold the PV product of the finished tile (64 fp32 columns) into the register accumulator.
-__device__ __forceinline__ void fold_pv(SoftmaxRow& st) {
-  uint32_t oa[16], ob[16];
-  tmem_ld16(st.s_col + 64, oa);
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    tc_wait_ld();
-    if (c + 1 < 4) {
-      if (c & 1) tmem_ld16(st.s_col + 64 + (c + 1) * 16, oa);
-      else tmem_ld16(st.s_col + 64 + (c + 1) * 16, ob);
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) st.acc[c * 16 + i] += __uint_as_float((c & 1) ? ob[i] : oa[i]);
-  }
-}
-
-// Fast per-tile loop: one pass.  Every logit of the row is bounded by st.bound (Cauchy-Schwarz
-// on the row's q and the largest key norm of the head), so 2^(s*sc - bound) never overflows
-// and the accumulator never needs rescaling.  Membership: recomputed score >= row threshold.
+// One-pass per-tile loop.  Every logit of the row is bounded by st.bound (Cauchy-Schwarz on
+// the row's q and the largest key norm of the head), so 2^(s*sc - bound) never overflows and
+// the accumulator never needs rescaling.  Membership: recomputed score >= row threshold.
 __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
                                                    int* status, volatile uint32_t* abort_flag) {
   const float sc = st.sc, thr = st.thr_ge, neg_b = -st.bound;
   const uint32_t s_col = st.s_col;
+  const uint32_t r_col = st.lane_base + kColR;
   float l0 = 0.f, l1 = 0.f;
   for (int j = 0; j < nKT; ++j) {
-    const uint32_t r_col = st.lane_base + kColR + (j & 1) * kTile;
     if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag) ||
-        !mbar_wait_bounded(&ctl->r_full[j & 1], (j >> 1) & 1, abort_flag)) {
+        !mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
       record_status(status, kDevWaitAccFull);
       return false;
     }
@@ -169,7 +153,7 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
       } else {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
+        if (lane == 0) mbar_arrive(&ctl->r_free);
       }
       uint32_t packed[8];
 #pragma unroll
@@ -190,39 +174,27 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->p_full[x]);
-
-    if (!mbar_wait_bounded(&ctl->pv_done[x], j & 1, abort_flag)) {
-      record_status(status, kDevWaitPvDone);
-      return false;
-    }
-    tc_fence_after();
-    fold_pv(st);
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->s_free[x]);
   }
   st.l = l0 + l1;
   return true;
 }
 
-// Exact per-tile loop: two passes.  Membership from the indexer's bitmask (ties cut by key
-// index, members with zero weight), routing weight relu(score), exact maximum over the
-// selected logits tracked beside the lazily raised stabiliser.
+// Two-pass per-tile loop (see the file header).
 __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
                                                     int* status, volatile uint32_t* abort_flag) {
   const float ninf = -__int_as_float(0x7f800000);
   const float sc = st.sc;
   const uint32_t s_col = st.s_col;
+  const uint32_t r_col = st.lane_base + kColR;
   uint4 mw = __ldg(st.mask_tile);
 
   for (int j = 0; j < nKT; ++j) {
     uint4 mw_next = make_uint4(0, 0, 0, 0);
     if (j + 1 < nKT) mw_next = __ldg(st.mask_tile + static_cast<int64_t>(j + 1) * kTile);
     const uint32_t words[4] = {mw.x, mw.y, mw.z, mw.w};
-    const uint32_t r_col = st.lane_base + kColR + (j & 1) * kTile;
 
     if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag) ||
-        !mbar_wait_bounded(&ctl->r_full[j & 1], (j >> 1) & 1, abort_flag)) {
+        !mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
       record_status(status, kDevWaitAccFull);
       return false;
     }
@@ -247,8 +219,24 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
       const float factor = (st.m_true == st.m_used) ? 1.f : ex2_approx(st.m_used - st.m_true);
       st.m_used = st.m_true;
       st.l *= factor;
+      if (j > 0) {
+        // O of the tiles before this one is complete once PV(j-1) retired
+        if (!mbar_wait_bounded(&ctl->pv_done[x], (j - 1) & 1, abort_flag)) {
+          record_status(status, kDevWaitPvDone);
+          return false;
+        }
+        tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld16(st.o_col + c * 16, o);
+          tc_wait_ld();
 #pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) st.acc[i] *= factor;
+          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st16(st.o_col + c * 16, o);
+        }
+        tc_wait_st();
+      }
     }
     const float neg_m = -st.m_used;
 
@@ -277,21 +265,11 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
     st.l += l0 + l1;
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->r_free[j & 1]);
+    if (lane == 0) mbar_arrive(&ctl->r_free);
     tc_wait_st();
     tc_fence_before();
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->p_full[x]);
-
-    if (!mbar_wait_bounded(&ctl->pv_done[x], j & 1, abort_flag)) {
-      record_status(status, kDevWaitPvDone);
-      return false;
-    }
-    tc_fence_after();
-    fold_pv(st);
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->s_free[x]);
     mw = mw_next;
   }
   return true;
@@ -354,15 +332,14 @@ __global__ void __launch_bounds__(320, 1)
 
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
+    mbar_init(&ctl->r_full, 1);
+    mbar_init(&ctl->r_free, 4 * nh);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl->wk_full[s], 1);
       mbar_init(&ctl->wk_empty[s], 1);
-      mbar_init(&ctl->r_full[s], 1);
-      mbar_init(&ctl->r_free[s], 4 * nh);
       mbar_init(&ctl->v_full[s], 1);
       mbar_init(&ctl->v_empty[s], 1);
       mbar_init(&ctl->s_full[s], 1);
-      mbar_init(&ctl->s_free[s], 4);
       mbar_init(&ctl->p_full[s], 4);
       mbar_init(&ctl->pv_done[s], 1);
       for (int t = 0; t < 2; ++t) {
@@ -462,20 +439,21 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
         for (int x = 0; x < 2; ++x) done = done && (x >= nh || n_pv[x] == nKT);
         if (done) break;
-        // R(j): needs the indexer key tile and a free R buffer
+        // R(j): needs the indexer key tile and every softmax warp done with R(j-1)
         if (n_r < nKT) {
           const int j = n_r, s = j & 1;
-          if (mbar_test_wait(&ctl->wk_full[s], (j >> 1) & 1) && mbar_test_wait(&ctl->r_free[s], ((j >> 1) & 1) ^ 1)) {
+          if (mbar_test_wait(&ctl->wk_full[s], (j >> 1) & 1) &&
+              (j == 0 || mbar_test_wait(&ctl->r_free, (j - 1) & 1))) {
             tc_fence_after();
             // descriptors advance in 16-byte units: +2 per 32-byte K step, +1024 for the second K half
             const uint64_t da = smem_desc_sw128(wq_addr), db = smem_desc_sw128(wk_addr + s * kWTileBytes);
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
               const uint64_t off = (ks >> 2) * (kWTileBytes / 32) + (ks & 3) * 2;
-              umma_tf32_ss(tmem_base + kColR + s * kTile, da + off, db + off, kIdescR, ks > 0);
+              umma_tf32_ss(tmem_base + kColR, da + off, db + off, kIdescR, ks > 0);
             }
             umma_commit(&ctl->wk_empty[s]);
-            umma_commit(&ctl->r_full[s]);
+            umma_commit(&ctl->r_full);
             ++n_r;
             progress = true;
           }
@@ -483,23 +461,7 @@ __global__ void __launch_bounds__(320, 1)
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (x >= nh) continue;
-          const uint32_t s_col = tmem_base + kColHead + x * kTile;
-          // S_x(j): needs K_x(j) and the head's S region free (PV of tile j-1 folded)
-          if (n_qk[x] < nKT && n_qk[x] == n_pv[x]) {
-            const int j = n_qk[x], s = j & 1;
-            if (mbar_test_wait(&ctl->k_full[x][s], (j >> 1) & 1) &&
-                (j == 0 || mbar_test_wait(&ctl->s_free[x], (j - 1) & 1))) {
-              tc_fence_after();
-              const uint64_t da = smem_desc_sw128(q_addr + x * kQTileBytes);
-              const uint64_t db = smem_desc_sw128(k_addr + (x * 2 + s) * kQTileBytes);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, da + ks * 2, db + ks * 2, kIdescQK, ks > 0);
-              umma_commit(&ctl->k_empty[x][s]);
-              umma_commit(&ctl->s_full[x]);
-              ++n_qk[x];
-              progress = true;
-            }
-          }
+          const uint32_t s_col = tmem_base + kColS + x * kTile;
           // PV_x(j): needs P_x(j) in TMEM and V_x(j) in smem
           if (n_pv[x] < n_qk[x]) {
             const int j = n_pv[x];
@@ -508,10 +470,27 @@ __global__ void __launch_bounds__(320, 1)
               const uint64_t dv = smem_desc_sw128(v_addr + x * kQTileBytes);
 #pragma unroll
               for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
-                umma_f16_ts(s_col + 64, s_col + ks * 8, dv + ks * 128, kIdescPV, ks > 0);
+                umma_f16_ts(tmem_base + kColO + x * kHeadDim, s_col + ks * 8, dv + ks * 128, kIdescPV,
+                            (j > 0 || ks > 0));
               umma_commit(&ctl->v_empty[x]);
               umma_commit(&ctl->pv_done[x]);
               ++n_pv[x];
+              progress = true;
+            }
+          }
+          // S_x(j): needs K_x(j); it overwrites P_x(j-1), so it is issued behind PV_x(j-1)
+          // (the tensor pipe executes one thread's MMAs in issue order)
+          if (n_qk[x] < nKT && n_qk[x] == n_pv[x]) {
+            const int j = n_qk[x], s = j & 1;
+            if (mbar_test_wait(&ctl->k_full[x][s], (j >> 1) & 1)) {
+              tc_fence_after();
+              const uint64_t da = smem_desc_sw128(q_addr + x * kQTileBytes);
+              const uint64_t db = smem_desc_sw128(k_addr + (x * 2 + s) * kQTileBytes);
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, da + ks * 2, db + ks * 2, kIdescQK, ks > 0);
+              umma_commit(&ctl->k_empty[x][s]);
+              umma_commit(&ctl->s_full[x]);
+              ++n_qk[x];
               progress = true;
             }
           }
@@ -536,14 +515,13 @@ __global__ void __launch_bounds__(320, 1)
 
       SoftmaxRow st;
       st.lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      st.s_col = st.lane_base + kColHead + x * kTile;
+      st.s_col = st.lane_base + kColS + x * kTile;
+      st.o_col = st.lane_base + kColO + x * kHeadDim;
       st.mask_tile =
           reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
       st.sc = p.scale_log2;
       st.m_true = st.m_used = -__int_as_float(0x7f800000);
       st.l = 0.f;
-#pragma unroll
-      for (int i = 0; i < kHeadDim; ++i) st.acc[i] = 0.f;
 
       // Row constants from the indexer's select passes: threshold bits, how many keys equal
       // to the threshold are selected, how many exist.  The one-pass path is exact when
@@ -576,38 +554,49 @@ __global__ void __launch_bounds__(320, 1)
                     st.bound <= kMaxBound);
       }
       const bool exact = __any_sync(0xffffffffu, flagged);
-      const bool ok = exact ? softmax_tiles_exact(st, ctl, x, nKT, lane, p.status, abort_flag)
-                            : softmax_tiles_fast(st, ctl, x, nKT, lane, p.status, abort_flag);
-
-      if (ok && row_ok) {
-        const float* acc = st.acc;
-        // exact path: the reference's clamp, out = O c / max(l c, 1e-6), c = 2^(m_used - m_true);
+      bool ok = exact ? softmax_tiles_exact(st, ctl, x, nKT, lane, p.status, abort_flag)
+                      : softmax_tiles_fast(st, ctl, x, nKT, lane, p.status, abort_flag);
+      if (ok && !mbar_wait_bounded(&ctl->pv_done[x], (nKT - 1) & 1, abort_flag)) {
+        record_status(p.status, kDevWaitPvDone);
+        ok = false;
+      }
+      if (ok) {
+        tc_fence_after();
+        // two-pass path: the reference's clamp, out = O c / max(l c, 1e-6), c = 2^(m_used - m_true);
         // one-pass path: the clamp cannot bind, out = O / l.
         const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
         const float inv = exact ? corr / fmaxf(st.l * corr, 1e-6f) : 1.f / st.l;
-        if (p.o_dtype == SWV_F32) {
-          float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost;
 #pragma unroll
-          for (int i = 0; i < kHeadDim; i += 4) {
-            *reinterpret_cast<float4*>(orow + i) =
-                make_float4(acc[i] * inv, acc[i + 1] * inv, acc[i + 2] * inv, acc[i + 3] * inv);
-          }
-        } else {
-          uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost;
+        for (int c = 0; c < 4; ++c) {
+          uint32_t o[16];
+          tmem_ld16(st.o_col + c * 16, o);
+          tc_wait_ld();
+          if (!row_ok) continue;
+          if (p.o_dtype == SWV_F32) {
+            float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
 #pragma unroll
-          for (int i = 0; i < kHeadDim; i += 8) {
-            uint32_t w4[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const float a0 = acc[i + 2 * q] * inv, a1 = acc[i + 2 * q + 1] * inv;
-              if (p.o_dtype == SWV_BF16) {
-                w4[q] = pack_bf16x2(a0, a1);
-              } else {
-                const __half2 h2 = __floats2half2_rn(a0, a1);
-                w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
-              }
+            for (int i = 0; i < 16; i += 4) {
+              *reinterpret_cast<float4*>(orow + i) =
+                  make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
+                              __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
-            *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          } else {
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
+#pragma unroll
+            for (int i = 0; i < 16; i += 8) {
+              uint32_t w4[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float a0 = __uint_as_float(o[i + 2 * q]) * inv, a1 = __uint_as_float(o[i + 2 * q + 1]) * inv;
+                if (p.o_dtype == SWV_BF16) {
+                  w4[q] = pack_bf16x2(a0, a1);
+                } else {
+                  const __half2 h2 = __floats2half2_rn(a0, a1);
+                  w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
+                }
+              }
+              *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+            }
           }
         }
       }

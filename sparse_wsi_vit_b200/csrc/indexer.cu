@@ -114,16 +114,16 @@ __device__ __forceinline__ void or_bit_if_eq(uint32_t& w, uint32_t v, uint32_t t
   asm("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
 }
 
-// Adds the 64 scores of one thread (two 32-column TMEM chunks) to its row histogram
+// Adds the 32 scores of one thread (one 32-column TMEM chunk) to its row histogram
 // (`hrow` = shared-memory address of the row's 256 counters).  A score takes part iff it
 // lies in the bucket [lo, lo + span) already known to hold the threshold (pass 0: all of
 // them); its bin is the next 8 bits.  CHECK guards the ragged last key tile.
 template <bool CHECK, bool FIRST>
-__device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint32_t (&r1)[32], uint32_t hrow,
-                                            int shift, uint32_t lo, uint32_t span, int nvalid, uint32_t& zeros) {
+__device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], uint32_t hrow, int shift, uint32_t lo,
+                                            uint32_t span, int nvalid, uint32_t& zeros) {
 #pragma unroll
-  for (int i = 0; i < 64; ++i) {
-    const uint32_t u = relu_bits(i < 32 ? r0[i] : r1[i - 32]);
+  for (int i = 0; i < 32; ++i) {
+    const uint32_t u = relu_bits(r0[i]);
     if (FIRST) {
       // scores that are exactly zero (half of them after the ReLU) are counted in a register
       const uint32_t t = CHECK ? (i < nvalid ? u : 0xFFFFFFFFu) : u;
@@ -137,10 +137,10 @@ __device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], const uint
 }
 
 template <int MODE>
-__global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHist ? 1 : 2)
+__global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHist ? 1 : 2)
     indexer_tiles_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const IndexerParams p) {
-  constexpr int kEpiWarps = MODE == kModeHist ? 8 : 4;
+  constexpr int kEpiWarps = MODE == kModeHist ? 16 : 4;
   constexpr uint32_t kIdesc = make_idesc(/*tf32*/ 2, kTile, kTile, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -241,10 +241,10 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
     bool ok = true;
 
     if constexpr (MODE == kModeHist) {
-      const int ch = ew >> 2;                // column half 0/1
-      const int et = threadIdx.x - 64;       // 0..255
-      for (int i = et; i < kTile * kHistStride; i += 256) sm_hist[i] = 0u;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const int ch = ew >> 2;                // column quarter 0..3 (32 columns each)
+      const int et = threadIdx.x - 64;       // 0..511
+      for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
 
       const int pass = p.pass;
       const int shift = 24 - 8 * pass;
@@ -263,26 +263,24 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 320 : 192, MODE == kModeHi
           break;
         }
         tc_fence_after();
-        uint32_t r0[32], r1[32];
-        const uint32_t taddr = lane_base + a * kTile + ch * 64;
-        tmem_ld32(taddr, r0);
-        tmem_ld32(taddr + 32, r1);
+        uint32_t r0[32];
+        tmem_ld32(lane_base + a * kTile + ch * 32, r0);
         tc_wait_ld();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
 
-        const int nvalid = p.Tk - (j * kTile + ch * 64);   // columns of this half that are real keys
+        const int nvalid = p.Tk - (j * kTile + ch * 32);   // columns of this quarter that are real keys
         if (pass == 0) {
-          if (nvalid >= 64) hist_update<false, true>(r0, r1, hrow_s, shift, lo, span, 64, zeros);
-          else hist_update<true, true>(r0, r1, hrow_s, shift, lo, span, nvalid, zeros);
+          if (nvalid >= 32) hist_update<false, true>(r0, hrow_s, shift, lo, span, 32, zeros);
+          else hist_update<true, true>(r0, hrow_s, shift, lo, span, nvalid, zeros);
         } else {
-          if (nvalid >= 64) hist_update<false, false>(r0, r1, hrow_s, shift, lo, span, 64, zeros);
-          else hist_update<true, false>(r0, r1, hrow_s, shift, lo, span, nvalid, zeros);
+          if (nvalid >= 32) hist_update<false, false>(r0, hrow_s, shift, lo, span, 32, zeros);
+          else hist_update<true, false>(r0, hrow_s, shift, lo, span, nvalid, zeros);
         }
       }
       if (zeros != 0u) atomicAdd(hrow, zeros);
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, 512;" ::: "memory");
       if (ok && ch == 0 && row_ok && *abort_flag == 0u) {
         uint32_t kth = pass == 0 ? static_cast<uint32_t>(min(p.top_k, p.Tk)) : p.st_kth[grow];
         uint32_t cum = 0, in_bin = 0;
@@ -525,7 +523,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   const unsigned grid = static_cast<unsigned>(B) * p.nQT;
   for (int pass = 0; pass < 4; ++pass) {
     p.pass = pass;
-    indexer_tiles_kernel<kModeHist><<<grid, 320, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
+    indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
   }
   indexer_tiles_kernel<kModeEmit><<<grid, 192, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
 
