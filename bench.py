@@ -32,9 +32,10 @@ if ROOT not in sys.path:
 H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
 METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 
-# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch on the bench workload, from the
-# ncu capture summarised in profiles/ (scaled from the captured case); None until measured.
-ATTN_DRAM_BYTES_PER_LAUNCH = None
+# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch on the 65536-token workload: the ncu
+# capture at 16384 tokens (profiles/dsa_attn_masked_kernel_16k.md: 59.2 MB read + 4.3 MB written)
+# times 4 -- this kernel's DRAM traffic is its inputs and outputs, which grow with T, not T^2.
+ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 254e6, 16384: 63.5e6}
 
 
 def measured_peaks():
@@ -303,7 +304,7 @@ def run_ours(args):
             ach = kept / (attn_ms * 1e-3) / 1e12
             line["roofline"] = {
                 "kernel": "dsa_attn_masked_kernel", "bound": "tensor", "achieved": ach, "peak": tf_peak,
-                "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH,
+                "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH.get(T),
                 "peak_source": f"bf16_tflops_sustained of {peak_src}",
                 "kernel_ms": attn_ms, "algorithmic_flops": kept,
                 "executed_flops": executed, "executed_tflops": executed / (attn_ms * 1e-3) / 1e12,
