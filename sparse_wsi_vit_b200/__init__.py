@@ -1,7 +1,7 @@
 """B200-native sparse-attention forward path for sparse-wsi-vit.
 
 Importing this package loads ``csrc/libswv_b200.so``; it raises ImportError if
-the library has not been built (``python -m sparse_wsi_vit_b200.csrc.build``).
+the library has not been built (``python sparse_wsi_vit_b200/csrc/build.py``).
 """
 from . import _lib  # noqa: F401  (fails loudly when the CUDA library is missing)
 from .ops import (DSAAttentionFunction, LightningIndexerFunction, check_status, dsa_attention_gather,

@@ -1,6 +1,8 @@
 """Builds libswv_b200.so (sm_100a only) in-tree with nvcc.
 
-    python -m sparse_wsi_vit_b200.csrc.build [--force] [--verbose]
+    python sparse_wsi_vit_b200/csrc/build.py [--force] [--verbose]
+
+(run it by path: importing it through the package would first try to load the library)
 
 nvcc cross-compiles without a GPU; the library links only the CUDA runtime and
 loads on a machine without a driver (the TMA descriptor encoder is resolved at

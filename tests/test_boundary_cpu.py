@@ -14,8 +14,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 @pytest.fixture(scope="module")
 def swv():
-    from sparse_wsi_vit_b200.csrc import build
-    build.build()
+    import __graft_entry__
+    __graft_entry__.build()
     import sparse_wsi_vit_b200 as m
     return m
 
