@@ -40,6 +40,7 @@ extern "C" {
 #define SWV_ERR_CUDA (-6)        /* a CUDA runtime call failed                      */
 #define SWV_ERR_TENSORMAP (-7)   /* the driver rejected a TMA descriptor            */
 #define SWV_ERR_UNSUPPORTED (-8) /* valid request this build has no kernel for      */
+#define SWV_ERR_TOO_LARGE (-9)   /* size beyond the fixed capacity of an entry point */
 
 #define SWV_F32 0
 #define SWV_BF16 1
@@ -82,6 +83,33 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
                              int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
                              uint32_t* maskbits, void* workspace, size_t workspace_bytes, int* status,
                              void* stream);
+
+/* swv_dsa_indexer_topk_fwd without the workspace argument, for hosts that may not obtain
+ * device memory for it.  It has no counterpart in the reference.
+ * Who needs it: a caller that runs inside someone else's memory plan -- a serving runtime or
+ * plug-in host that sizes every device buffer up front and hands the operator only its
+ * input and output tensors, or a latency-critical loop that cannot afford the device-wide
+ * synchronisation an allocation may imply.  Such a caller cannot produce the scratch buffer
+ * the regular entry point asks for, so this one brings its own: a fixed array in the
+ * library's device data segment.
+ * Same arguments, outputs and arithmetic as swv_dsa_indexer_topk_fwd (the same kernels run).
+ * Limits and rules:
+ *   - B*Tq <= 8192 and B*Tk <= 8192; anything larger returns SWV_ERR_TOO_LARGE and launches
+ *     nothing.  The array (about 4.3 MB) is held by every GPU that loads the library, until
+ *     the process exits.
+ *   - The first call on a device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins.
+ *   - It calls no allocating or freeing routine.
+ *   - All calls on a device share the one array and it keeps the previous call's contents.
+ *     Nothing in it needs clearing: every word a call reads it has written first.  Two calls
+ *     that overlap on the GPU (different streams, no ordering) race on it -- order them.
+ *   - swv_dsa_attn_masked_fwd needs a workspace pointer and therefore cannot follow this call;
+ *     use swv_dsa_attn_gather_fwd with the idx / valid / scores written here.
+ */
+int swv_dsa_indexer_topk_static_fwd(const void* q_idx, const int64_t q_strides[4], const void* k_idx,
+                                    const int64_t k_strides[4], int idx_dtype, const float* w, int B, int Tq,
+                                    int Tk, int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
+                                    uint32_t* maskbits, int* status, void* stream);
 
 /* Routing-weighted attention over an explicit per-query key list.
  * Replaces DSAAttentionFunction.forward and its kernel (K:769-810, K:450-564):

@@ -15,6 +15,7 @@ SWV_F32, SWV_BF16, SWV_F16 = 0, 1, 2
 EXPORTS = [
     "swv_version", "swv_strerror", "swv_dsa_workspace_bytes", "swv_dsa_mask_bytes",
     "swv_dsa_indexer_topk_fwd", "swv_dsa_attn_gather_fwd", "swv_dsa_attn_masked_fwd",
+    "swv_dsa_indexer_topk_static_fwd",
 ]
 
 
@@ -25,12 +26,12 @@ class SwvError(RuntimeError):
 def _load():
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} not found: build it with `python -m sparse_wsi_vit_b200.csrc.build` "
+            f"{LIB_PATH} not found: build it with `python sparse_wsi_vit_b200/csrc/build.py` "
             "(there is no CPU or PyTorch fallback for this package)")
     lib = ctypes.CDLL(LIB_PATH)
     for name in EXPORTS:
         if not hasattr(lib, name):
-            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it")
+            raise ImportError(f"{LIB_PATH} does not export {name}; rebuild it with `python sparse_wsi_vit_b200/csrc/build.py --force`")
     i64p = POINTER(c_int64)
     lib.swv_version.restype = c_int
     lib.swv_strerror.restype = c_char_p
@@ -40,6 +41,9 @@ def _load():
     lib.swv_dsa_indexer_topk_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]
+    lib.swv_dsa_indexer_topk_static_fwd.argtypes = [
+        c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.swv_dsa_attn_gather_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, i64p, c_void_p, i64p, c_void_p, i64p,
         c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]

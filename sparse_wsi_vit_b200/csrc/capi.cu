@@ -10,6 +10,10 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
                           const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
                           float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
                           int* status, cudaStream_t st);
+int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
+                                 int dtype, const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k,
+                                 int32_t* idx, float* valid, float* scores, uint32_t* maskbits, int* status,
+                                 cudaStream_t st);
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
@@ -36,6 +40,7 @@ const char* swv_strerror(int code) {
     case SWV_ERR_CUDA: return "a CUDA runtime call failed";
     case SWV_ERR_TENSORMAP: return "the driver rejected a TMA descriptor";
     case SWV_ERR_UNSUPPORTED: return "no kernel in this build for the requested shape";
+    case SWV_ERR_TOO_LARGE: return "size beyond the fixed capacity of this entry point (8192 tokens)";
     case swv::kDevWaitTmaFull: return "device: timed out waiting for a TMA tile";
     case swv::kDevWaitStageEmpty: return "device: timed out waiting for a free shared-memory stage";
     case swv::kDevWaitAccFull: return "device: timed out waiting for an accumulator tile";
@@ -62,6 +67,16 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
   return swv::dsa_indexer_topk_impl(q_idx, q_strides, k_idx, k_strides, idx_dtype, w, B, Tq, Tk, IH, ID, top_k, idx,
                                     valid, scores, maskbits, workspace, workspace_bytes, status,
                                     static_cast<cudaStream_t>(stream));
+}
+
+// The variant for callers that cannot allocate: the scratch is a fixed device array inside the
+// library (see the header for who needs this and for its limits).
+int swv_dsa_indexer_topk_static_fwd(const void* q_idx, const int64_t q_strides[4], const void* k_idx,
+                                    const int64_t k_strides[4], int idx_dtype, const float* w, int B, int Tq,
+                                    int Tk, int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
+                                    uint32_t* maskbits, int* status, void* stream) {
+  return swv::dsa_indexer_topk_static_impl(q_idx, q_strides, k_idx, k_strides, idx_dtype, w, B, Tq, Tk, IH, ID, top_k,
+                                           idx, valid, scores, maskbits, status, static_cast<cudaStream_t>(stream));
 }
 
 int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],

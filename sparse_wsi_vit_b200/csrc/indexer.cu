@@ -534,4 +534,38 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   return SWV_OK;
 }
 
+// ------------------------------------------------- entry point without a workspace argument
+// Scratch for swv_dsa_indexer_topk_static_fwd: the same layout workspace_layout() describes,
+// sized for kStaticMaxTokens query tokens and as many key tokens (batch included).  Every GPU
+// whose context loads this library holds these bytes until the process exits.
+constexpr int kStaticMaxTokens = 8192;
+constexpr size_t kStaticScratchBytes =
+    2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + 3 * static_cast<size_t>(kStaticMaxTokens) * 4 + 4096 +
+    6 * 1024 /* per-section rounding */;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
+                                 int dtype, const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k,
+                                 int32_t* idx, float* valid, float* scores, uint32_t* maskbits, int* status,
+                                 cudaStream_t st) {
+  if (B < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
+  if (static_cast<int64_t>(B) * Tq > kStaticMaxTokens || static_cast<int64_t>(B) * Tk > kStaticMaxTokens)
+    return SWV_ERR_TOO_LARGE;
+  if (workspace_layout(B, Tq, Tk).total > kStaticScratchBytes) return SWV_ERR_TOO_LARGE;
+  // In host code `g_static_scratch` names a host-side stand-in, not device memory: the device
+  // address has to be asked for, once per device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static void* dev_ptr[kMaxDevices] = {nullptr};
+  int dev = 0;
+  SWV_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return SWV_ERR_UNSUPPORTED;
+  if (dev_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return SWV_ERR_CUDA;
+    dev_ptr[dev] = ptr;
+  }
+  return dsa_indexer_topk_impl(q_idx, qs, k_idx, ks, dtype, w, B, Tq, Tk, IH, ID, top_k, idx, valid, scores, maskbits,
+                               dev_ptr[dev], kStaticScratchBytes, status, st);
+}
+
 }  // namespace swv
