@@ -142,6 +142,41 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
                             int Tq, int Tk, int D, int* status, void* stream);
 
+/* Static block-sparse flash attention forward driven by a CSR list of key blocks per
+ * query block (shared by all batches and heads):
+ *   o[q] = softmax_j( q.k_j / sqrt(D) ) v_j   over the keys j the pattern lets q see;
+ * query rows that see no key return zeros.
+ * mode 0: every key of a listed block is seen -- the 2-D block pattern (no counterpart in
+ *         the reference; defined as dense attention under the expanded block mask).
+ * mode 1: inside the listed blocks the token pattern of the reference's
+ *         StaticSparseAttention applies (src/sparse_wsi_vit/models/static_sparse_attention.py:62-188):
+ *         query i sees key j iff i < num_cls or j < num_cls or
+ *         (|i-j| <= window*dilation and (i-j) % dilation == 0); the list must contain every
+ *         block that holds such a pair.  Replaces the three SDPA calls at :87, :93/:97, :180.
+ *   q (B,H,Tq,D), k, v (B,H,Tk,D) bf16, strides (b,h,t,d), unit inner stride, 16-byte rows.
+ *   row_ptr int32[ceil(Tq/block)+1], col_idx int32[nnz]; block in {64,128}; D in {64,128}.
+ *   Tensor-core (tcgen05) QK^T and PV, fp32 softmax statistics.
+ */
+int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                              const void* v, const int64_t v_strides[4], const int32_t* row_ptr,
+                              const int32_t* col_idx, int block, int mode, int num_cls, int window, int dilation,
+                              void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
+                              int* status, void* stream);
+
+/* 2-D rotary embedding on per-token (y, x) coordinates.
+ * Replaces VisionRotaryEmbedding.forward, dynamic branch
+ * (src/sparse_wsi_vit/models/vit_5/rope.py:72-97, rotate_half :33-37), as applied to q and k in
+ * src/sparse_wsi_vit/models/vit_5/models_vit5.py:84-90: head_dim/4 frequencies
+ * theta^(-2i/(head_dim/2)), each used for two adjacent channels; the first half of the head
+ * turns with coords[:,0]/coord_high, the second half with coords[:,1]/coord_high;
+ * (x0,x1) -> (x0 cos - x1 sin, x1 cos + x0 sin).  The first `skip_tokens` tokens (CLS) are copied.
+ *   x, y (L,H,head_dim): strides (l,h,d) with unit inner stride; dtype SWV_F32 or SWV_BF16; y may be x.
+ *   coords (L,2) f32 contiguous.
+ */
+int swv_rope2d_apply(const void* x, const int64_t x_strides[3], void* y, const int64_t y_strides[3], int dtype,
+                     const float* coords, int64_t L, int H, int head_dim, float coord_high, float theta,
+                     int skip_tokens, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

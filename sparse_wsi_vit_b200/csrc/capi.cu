@@ -23,6 +23,12 @@ int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const 
                          const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
                          int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
                          cudaStream_t st);
+int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                           const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
+                           int num_cls, int window, int dilation, void* o, const int64_t* os, int o_dtype, int B,
+                           int H, int Tq, int Tk, int D, int* status, cudaStream_t st);
+int rope2d_impl(const void* x, const int64_t* xs, void* y, const int64_t* ys, int dtype, const float* coords,
+                int64_t L, int H, int hd, float coord_high, float theta, int skip, cudaStream_t st);
 }  // namespace swv
 
 extern "C" {
@@ -96,6 +102,23 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             int Tq, int Tk, int D, int* status, void* stream) {
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, status, static_cast<cudaStream_t>(stream));
+}
+
+int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                              const void* v, const int64_t v_strides[4], const int32_t* row_ptr,
+                              const int32_t* col_idx, int block, int mode, int num_cls, int window, int dilation,
+                              void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
+                              int* status, void* stream) {
+  return swv::block_sparse_attn_impl(q, q_strides, k, k_strides, v, v_strides, row_ptr, col_idx, block, mode, num_cls,
+                                     window, dilation, o, o_strides, o_dtype, B, H, Tq, Tk, D, status,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int swv_rope2d_apply(const void* x, const int64_t x_strides[3], void* y, const int64_t y_strides[3], int dtype,
+                     const float* coords, int64_t L, int H, int head_dim, float coord_high, float theta,
+                     int skip_tokens, void* stream) {
+  return swv::rope2d_impl(x, x_strides, y, y_strides, dtype, coords, L, H, head_dim, coord_high, theta, skip_tokens,
+                          static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -220,3 +220,72 @@ class DSAAttentionFunction(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         raise NotImplementedError("sparse_wsi_vit_b200 implements the forward path only")
+
+
+# --------------------------------------------------------------------------- #
+# static block-sparse attention and 2-D RoPE
+# --------------------------------------------------------------------------- #
+def block_sparse_attention(q, k, v, row_ptr, col_idx, block, mode=0, num_cls=0, window=0, dilation=1,
+                           out_dtype=None):
+    """Flash attention restricted to a CSR list of key blocks per query block.
+
+    q (B,H,Tq,D), k, v (B,H,Tk,D) bf16 (other float dtypes are converted); row_ptr / col_idx int32
+    CUDA tensors; block in {64, 128}; D in {64, 128}.  mode 0: whole listed blocks; mode 1: the
+    reference's CLS + dilated-window token pattern inside the listed blocks
+    (static_sparse_attention.py:62-188).  Rows that see no key return zeros.
+    """
+    _require_cuda(q, k, v, row_ptr, col_idx)
+    B, H, Tq, D0 = q.shape
+    Tk = k.shape[2]
+    out_dtype = out_dtype or q.dtype
+    if D0 > 128:
+        raise SwvError("block_sparse_attention supports head_dim <= 128")
+    D = 64 if D0 <= 64 else 128
+    if D != D0:
+        # zero-pad the head dimension to a supported width; q is rescaled so that the kernel's
+        # 1/sqrt(D) equals the caller's 1/sqrt(D0); the padded output channels are zero
+        pad = (0, D - D0)
+        q = torch.nn.functional.pad(q.float() * (D / D0) ** 0.5, pad)
+        k = torch.nn.functional.pad(k, pad)
+        v = torch.nn.functional.pad(v, pad)
+    q, k, v = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (q, k, v))
+    q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+    if row_ptr.dtype != torch.int32 or col_idx.dtype != torch.int32:
+        raise SwvError("row_ptr and col_idx must be int32")
+    nqb = -(-Tq // block)
+    if row_ptr.numel() != nqb + 1:
+        raise SwvError(f"row_ptr has {row_ptr.numel()} entries, expected {nqb + 1}")
+    dev = q.device
+    o = torch.empty((B, H, Tq, D), dtype=out_dtype, device=dev)
+    st = status_word(dev)
+    rc = lib.swv_block_sparse_attn_fwd(
+        q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), row_ptr.data_ptr(),
+        col_idx.data_ptr(), block, mode, num_cls, window, dilation, o.data_ptr(), strides(o), dtype_code(o.dtype),
+        B, H, Tq, Tk, D, st.data_ptr(), _stream(dev))
+    check(rc, "swv_block_sparse_attn_fwd")
+    if _CHECK:
+        check_status(dev, "swv_block_sparse_attn_fwd")
+    return o if D == D0 else o[..., :D0]
+
+
+def rope2d(x, coords, coord_high, theta=10000.0, skip_tokens=0, out=None):
+    """2-D rotary embedding (vit_5/rope.py:72-97).  x (L,H,hd) or (1,L,H,hd), fp32 or bf16, unit inner
+    stride; coords (L,2) or (1,L,2) in the units of coord_high; the first skip_tokens tokens are copied."""
+    _require_cuda(x, coords)
+    squeeze = x.dim() == 4
+    if squeeze:
+        if x.shape[0] != 1:
+            raise SwvError("rope2d handles one slide at a time (batch 1), like the reference")
+        x = x[0]
+    c = coords.reshape(-1, 2).to(torch.float32).contiguous()
+    L, H, hd = x.shape
+    if c.shape[0] != L:
+        raise SwvError("coords must have one (y, x) pair per token")
+    if x.stride(2) != 1:
+        x = x.contiguous()
+    y = torch.empty_like(x) if out is None else out
+    s3 = lambda t: (ctypes.c_int64 * 3)(*t.stride())
+    rc = lib.swv_rope2d_apply(x.data_ptr(), s3(x), y.data_ptr(), s3(y), dtype_code(x.dtype), c.data_ptr(), L, H, hd,
+                              float(coord_high), float(theta), int(skip_tokens), _stream(x.device))
+    check(rc, "swv_rope2d_apply")
+    return y[None] if squeeze else y
