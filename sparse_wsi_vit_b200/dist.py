@@ -105,3 +105,48 @@ def sharded_dsa_attention(q_loc, k_loc, v_loc, qi_loc, ki_loc, w, top_k, plan: S
     v = v_all[:, :T].transpose(1, 2)
     return compute(q, k, v, qi_loc, ki_all[:, :T], w, top_k, out_dtype=out_dtype, return_topk=return_topk,
                    **({"kv_ready": kv_ready} if kv_ready is not None else {}))
+
+
+def sharded_encoder_forward(encoder, patches_local, plan: ShardPlan, group=None, comm_stream=None, compute=None):
+    """Forward of a ``DSAViTSlideEncoder`` with the token sequence [CLS..., patches...] sharded over
+    the ranks of `group` (weights replicated).
+
+    `plan` shards the FULL sequence of ``encoder.num_cls + n_patches`` tokens; `patches_local` holds
+    the patch embeddings of this rank's slice, (B, n_local_patches, in_features): rank 0's slice
+    starts with the CLS tokens, so it gets ``plan.local - num_cls`` patches, every other rank
+    ``plan.local``.  Token-local work (projections, LayerNorm, MLP) runs on the shard with no
+    communication; each attention layer all-gathers the indexer keys, K and V
+    (``sharded_dsa_attention``).  The CLS rows live on rank 0, which computes the logits and
+    broadcasts them.  Returns {"logits": (B, out_features)} on every rank, the same dictionary
+    ``DSAViTSlideEncoder.forward`` returns (deepseek_sparse_attention.py:267-305).
+    """
+    C = encoder.num_cls
+    if plan.world > 1 and plan.per_rank < C:
+        raise ValueError("the CLS tokens must fit into rank 0's shard")
+    if patches_local.dim() == 2:
+        patches_local = patches_local.unsqueeze(0)
+    B = patches_local.shape[0]
+    x = encoder.input_proj(patches_local)
+    if plan.rank == 0:
+        x = torch.cat([encoder.cls_tokens.expand(B, -1, -1).to(x.dtype), x], dim=1)
+    if x.shape[1] != plan.local:
+        raise ValueError(f"rank {plan.rank} holds {x.shape[1]} tokens, the plan says {plan.local}")
+    for blk in encoder.blocks:
+        attn = blk.attn
+        H, D = attn.attention_heads, attn.head_dim
+        y = blk.norm1(x)
+        qkv = attn.qkv_proj(y).view(B, -1, 3, H, D)
+        q_idx, k_idx = attn.indexer_proj(y)
+        o = sharded_dsa_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], q_idx, k_idx, attn.indexer_head_weights,
+                                  attn.top_k, plan, group=group, out_dtype=y.dtype, compute=compute,
+                                  comm_stream=comm_stream)
+        x = x + blk.drop1(attn.out_proj(o.transpose(1, 2).reshape(B, -1, H * D).to(y.dtype)))
+        x = x + blk.mlp(blk.norm2(x))
+    logits = torch.empty((B, encoder.out_features), dtype=x.dtype, device=x.device)
+    if plan.rank == 0:
+        cls = encoder.norm(x[:, :C])
+        pooled = (torch.softmax(encoder.cls_pool(cls), dim=1) * cls).sum(dim=1)
+        logits = encoder.head(pooled).contiguous()
+    if plan.world > 1:
+        dist.broadcast(logits, src=0, group=group)
+    return {"logits": logits}

@@ -84,6 +84,37 @@ def test_sharded_forward_equals_single_process(world, T):
     assert all(out.get(r, False) for r in range(world))
 
 
+def _encoder_worker(rank, world, port, n_patches, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import sparse_wsi_vit_b200 as swv
+        from sparse_wsi_vit_b200.dist import sharded_encoder_forward
+        torch.manual_seed(0)
+        enc = swv.DSAViTSlideEncoder(in_features=24, out_features=3, embed_dim=32, num_heads=2, num_layers=2,
+                                     num_cls=2, indexer_heads=2, indexer_dim=16, top_k=8).eval()
+        x = torch.randn(1, n_patches, 24, generator=torch.Generator().manual_seed(1))
+        T = n_patches + enc.num_cls
+        plan = plan_shards(T, world, rank)
+        lo, hi = max(plan.start - enc.num_cls, 0), plan.stop - enc.num_cls
+        with torch.no_grad():
+            got = sharded_encoder_forward(enc, x[:, lo:hi], plan, compute=_oracle_compute)["logits"]
+            whole = sharded_encoder_forward(enc, x, plan_shards(T, 1, 0), compute=_oracle_compute)["logits"]
+        assert torch.allclose(got, whole, atol=1e-5), (got, whole)
+        out[rank] = True
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_patches", [(2, 61), (3, 40)])
+def test_sharded_encoder_equals_unsharded(world, n_patches):
+    port = _free_port()
+    mgr = mp.Manager()
+    out = mgr.dict()
+    mp.spawn(_encoder_worker, args=(world, port, n_patches, out), nprocs=world, join=True)
+    assert all(out.get(r, False) for r in range(world))
+
+
 def test_batched_gather_layout():
     """B > 1 goes through the staged gather; with world == 1 it must be the identity + padding."""
     x = torch.arange(2 * 5 * 3, dtype=torch.float32).view(2, 5, 3)
