@@ -120,13 +120,15 @@ int swv_dsa_indexer_topk_static_fwd(const void* q_idx, const int64_t q_strides[4
  *   q (B,H,Tq,D), k, v (B,H,Tk,D): strides (b,h,t,d), last stride 1; dtype F32/BF16/F16.
  *   idx int32, valid f32, rw f32: (B,Tq,top_k), strides (b,t,k).
  *   o (B,H,Tq,D): strides (b,h,t,d); o_dtype F32/BF16/F16.  1 <= D <= 256.
+ *   kv_group: query heads per key/value head (1 for the reference's multi-head attention;
+ *   k, v then have H/kv_group heads -- grouped-query attention, used by the NSA branches).
  */
 int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], int qkv_dtype, const int32_t* idx,
                             const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3],
                             const float* rw, const int64_t rw_strides[3], void* o, const int64_t o_strides[4],
-                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
-                            void* stream);
+                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int kv_group,
+                            int* status, void* stream);
 
 /* Same arithmetic as swv_dsa_attn_gather_fwd for the key lists of the
  * swv_dsa_indexer_topk_fwd call that last wrote `maskbits` and `workspace`
@@ -155,13 +157,25 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
  *         block that holds such a pair.  Replaces the three SDPA calls at :87, :93/:97, :180.
  *   q (B,H,Tq,D), k, v (B,H,Tk,D) bf16, strides (b,h,t,d), unit inner stride, 16-byte rows.
  *   row_ptr int32[ceil(Tq/block)+1], col_idx int32[nnz]; block in {64,128}; D in {64,128}.
+ *   kv_group: query heads per key/value head (k, v have H/kv_group heads); 1 = multi-head.
+ *   lse: optional (may be NULL) f32 (B,H,Tq) contiguous, natural-log sum of exponentials of
+ *   every row (-inf for rows that see no key).
  *   Tensor-core (tcgen05) QK^T and PV, fp32 softmax statistics.
  */
 int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                               const void* v, const int64_t v_strides[4], const int32_t* row_ptr,
                               const int32_t* col_idx, int block, int mode, int num_cls, int window, int dilation,
-                              void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
-                              int* status, void* stream);
+                              int kv_group, float* lse, void* o, const int64_t o_strides[4], int o_dtype, int B,
+                              int H, int Tq, int Tk, int D, int* status, void* stream);
+
+/* Mean pooling of overlapping token windows, y[b,h,c,:] = mean_{i<window} x[b,h,c*stride+i,:],
+ * c < (T-window)/stride + 1: the compressed keys and values of the NSA compressed branch
+ * (no counterpart in the reference, which only names NSA as an intent,
+ * scripts/virchow_preprocess.py:44-53).  x (B,H,T,D) bf16, strides (b,h,t,d) even, unit inner
+ * stride; y contiguous (B,H,nC,D) bf16.
+ */
+int swv_pool_tokens(const void* x, const int64_t x_strides[4], void* y, int B, int H, int T, int D, int window,
+                    int stride, void* stream);
 
 /* 2-D rotary embedding on per-token (y, x) coordinates.
  * Replaces VisionRotaryEmbedding.forward, dynamic branch

@@ -15,7 +15,7 @@ SWV_F32, SWV_BF16, SWV_F16 = 0, 1, 2
 EXPORTS = [
     "swv_version", "swv_strerror", "swv_dsa_workspace_bytes", "swv_dsa_mask_bytes",
     "swv_dsa_indexer_topk_fwd", "swv_dsa_attn_gather_fwd", "swv_dsa_attn_masked_fwd",
-    "swv_dsa_indexer_topk_static_fwd", "swv_block_sparse_attn_fwd", "swv_rope2d_apply",
+    "swv_dsa_indexer_topk_static_fwd", "swv_block_sparse_attn_fwd", "swv_rope2d_apply", "swv_pool_tokens",
 ]
 
 
@@ -46,12 +46,13 @@ def _load():
         c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]
     lib.swv_block_sparse_attn_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-        c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        c_int, c_void_p, c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+    lib.swv_pool_tokens.argtypes = [c_void_p, i64p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
     lib.swv_rope2d_apply.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, c_int64, c_int, c_int, c_float, c_float, c_int, c_void_p]
     lib.swv_dsa_attn_gather_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_int, c_void_p, i64p, c_void_p, i64p, c_void_p, i64p,
-        c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+        c_void_p, i64p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
     lib.swv_dsa_attn_masked_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_void_p, i64p, c_int,
         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]

@@ -29,6 +29,8 @@ struct BsaParams {
   const int32_t* row_ptr;   // [nQB + 1]
   const int32_t* col_idx;   // [nnz] key block index
   int mode, num_cls, window, dilation;
+  int kv_group;             // query heads per key/value head (grouped-query attention), >= 1
+  float* lse;               // optional (B,H,Tq): natural-log sum of exponentials per row, -inf for empty rows
   void* o;
   int64_t osb, osh, ost;
   int o_dtype;
@@ -122,6 +124,7 @@ __global__ void __launch_bounds__(192, 1)
 #pragma unroll
       for (int c = 0; c < D / 64; ++c)
         tma_load_4d(smem + c * (kTile * 128), &tm_q, &ctl->q_full, c * 64, qb * BS, h, b);
+      const int hk = h / p.kv_group;
       for (int j = 0; j < nblk; ++j) {
         const int s = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
@@ -133,7 +136,7 @@ __global__ void __launch_bounds__(192, 1)
         mbar_expect_tx(&ctl->k_full[s], Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + Cfg::kOffK + s * Cfg::kKVBytes + c * (BS * 128), &tm_k, &ctl->k_full[s], c * 64, key0, h,
+          tma_load_4d(smem + Cfg::kOffK + s * Cfg::kKVBytes + c * (BS * 128), &tm_k, &ctl->k_full[s], c * 64, key0, hk,
                       b);
         if (!mbar_wait_bounded(&ctl->v_empty[s], par, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
@@ -142,7 +145,7 @@ __global__ void __launch_bounds__(192, 1)
         mbar_expect_tx(&ctl->v_full[s], Cfg::kKVBytes);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + Cfg::kOffV + s * Cfg::kKVBytes + c * (BS * 128), &tm_v, &ctl->v_full[s], c * 64, key0, h,
+          tma_load_4d(smem + Cfg::kOffV + s * Cfg::kKVBytes + c * (BS * 128), &tm_v, &ctl->v_full[s], c * 64, key0, hk,
                       b);
       }
     }
@@ -316,6 +319,10 @@ __global__ void __launch_bounds__(192, 1)
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
+      if (p.lse != nullptr && row_ok) {
+        p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Tq + qrow] =
+            l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : ninf;
+      }
 #pragma unroll 1
       for (int c = 0; c < D / 16; ++c) {
         uint32_t o[16];
@@ -414,6 +421,33 @@ __global__ void rope2d_kernel(const T* __restrict__ x, T* __restrict__ y, const 
   }
 }
 
+// Mean pooling of overlapping token windows: y[b,h,c,:] = mean_{i < win} x[b,h,c*stride + i,:]
+// (the compressed keys / values of the NSA compressed branch).  One thread per output pair of channels.
+__global__ void pool_tokens_kernel(const __nv_bfloat16* __restrict__ x, int64_t sb, int64_t sh, int64_t st_,
+                                   __nv_bfloat16* __restrict__ y, int B, int H, int T, int D, int nC, int win,
+                                   int stride) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int pairs = D / 2;
+  const int64_t total = static_cast<int64_t>(B) * H * nC * pairs;
+  if (gid >= total) return;
+  const int pr = static_cast<int>(gid % pairs);
+  const int c = static_cast<int>((gid / pairs) % nC);
+  const int h = static_cast<int>((gid / (static_cast<int64_t>(pairs) * nC)) % H);
+  const int b = static_cast<int>(gid / (static_cast<int64_t>(pairs) * nC * H));
+  const __nv_bfloat16* xp = x + b * sb + h * sh + static_cast<int64_t>(c) * stride * st_ + 2 * pr;
+  float a0 = 0.f, a1 = 0.f;
+  for (int i = 0; i < win; ++i) {
+    const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(xp + i * st_);
+    a0 += __bfloat162float(v.x);
+    a1 += __bfloat162float(v.y);
+  }
+  const float inv = 1.0f / win;
+  __nv_bfloat162 o;
+  o.x = __float2bfloat16_rn(a0 * inv);
+  o.y = __float2bfloat16_rn(a1 * inv);
+  *reinterpret_cast<__nv_bfloat162*>(y + ((static_cast<int64_t>(b) * H + h) * nC + c) * D + 2 * pr) = o;
+}
+
 // ---------------------------------------------------------------------- host
 static bool bsa_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -431,10 +465,12 @@ static int launch_bsa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                            const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
-                           int num_cls, int window, int dilation, void* o, const int64_t* os, int o_dtype, int B,
-                           int H, int Tq, int Tk, int D, int* status, cudaStream_t st) {
+                           int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
+                           const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
+                           cudaStream_t st) {
   if (!q || !k || !v || !row_ptr || !col_idx || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
+  if (kv_group < 1 || H % kv_group != 0) return SWV_ERR_SHAPE;
   if ((block != 64 && block != 128) || (D != 64 && D != 128)) return SWV_ERR_UNSUPPORTED;
   if (mode != 0 && mode != 1) return SWV_ERR_UNSUPPORTED;
   if (mode == 1 && (num_cls < 0 || window < 0 || dilation < 1)) return SWV_ERR_SHAPE;
@@ -453,9 +489,10 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   int rc = make_tmap_4d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tq, H, B, qs[2] * 2, qs[1] * 2, qs[0] * 2, 64,
                         kTile);
   if (rc != SWV_OK) return rc;
-  rc = make_tmap_4d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tk, H, B, ks[2] * 2, ks[1] * 2, ks[0] * 2, 64, block);
+  const int Hkv = H / kv_group;
+  rc = make_tmap_4d(&tk, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tk, Hkv, B, ks[2] * 2, ks[1] * 2, ks[0] * 2, 64, block);
   if (rc != SWV_OK) return rc;
-  rc = make_tmap_4d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tk, H, B, vs[2] * 2, vs[1] * 2, vs[0] * 2, 64, block);
+  rc = make_tmap_4d(&tv, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tk, Hkv, B, vs[2] * 2, vs[1] * 2, vs[0] * 2, 64, block);
   if (rc != SWV_OK) return rc;
 
   BsaParams p;
@@ -463,6 +500,7 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   p.nQB = (Tq + block - 1) / block;
   p.row_ptr = row_ptr; p.col_idx = col_idx;
   p.mode = mode; p.num_cls = num_cls; p.window = window; p.dilation = dilation;
+  p.kv_group = kv_group; p.lse = lse;
   p.o = o; p.osb = os[0]; p.osh = os[1]; p.ost = os[2]; p.o_dtype = o_dtype;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   p.status = status;
@@ -470,6 +508,20 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   if (block == 64 && D == 128) return launch_bsa<64, 128>(tq, tk, tv, p, st);
   if (block == 128 && D == 64) return launch_bsa<128, 64>(tq, tk, tv, p, st);
   return launch_bsa<128, 128>(tq, tk, tv, p, st);
+}
+
+int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, int T, int D, int win, int stride,
+                     cudaStream_t st) {
+  if (!x || !y || !xs) return SWV_ERR_NULL;
+  if (B < 1 || H < 1 || T < win || win < 1 || stride < 1 || D < 2 || (D & 1)) return SWV_ERR_SHAPE;
+  if (xs[3] != 1 || (xs[0] & 1) || (xs[1] & 1) || (xs[2] & 1) || (reinterpret_cast<uintptr_t>(x) & 3)) return SWV_ERR_ALIGN;
+  const int nC = (T - win) / stride + 1;
+  const int64_t total = static_cast<int64_t>(B) * H * nC * (D / 2);
+  pool_tokens_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), xs[0], xs[1], xs[2], static_cast<__nv_bfloat16*>(y), B, H, T, D, nC, win,
+      stride);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
 }
 
 int rope2d_impl(const void* x, const int64_t* xs, void* y, const int64_t* ys, int dtype, const float* coords,

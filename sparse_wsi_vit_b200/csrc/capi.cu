@@ -21,12 +21,15 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
                          const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
-                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
+                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int kv_group, int* status,
                          cudaStream_t st);
 int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                            const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
-                           int num_cls, int window, int dilation, void* o, const int64_t* os, int o_dtype, int B,
-                           int H, int Tq, int Tk, int D, int* status, cudaStream_t st);
+                           int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
+                           const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
+                           cudaStream_t st);
+int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, int T, int D, int win, int stride,
+                     cudaStream_t st);
 int rope2d_impl(const void* x, const int64_t* xs, void* y, const int64_t* ys, int dtype, const float* coords,
                 int64_t L, int H, int hd, float coord_high, float theta, int skip, cudaStream_t st);
 }  // namespace swv
@@ -89,11 +92,11 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
                             const void* v, const int64_t v_strides[4], int qkv_dtype, const int32_t* idx,
                             const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3],
                             const float* rw, const int64_t rw_strides[3], void* o, const int64_t o_strides[4],
-                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
-                            void* stream) {
+                            int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int kv_group,
+                            int* status, void* stream) {
   return swv::dsa_attn_gather_impl(q, q_strides, k, k_strides, v, v_strides, qkv_dtype, idx, idx_strides, valid,
                                    valid_strides, rw, rw_strides, o, o_strides, o_dtype, B, H, Tq, Tk, D, top_k,
-                                   status, static_cast<cudaStream_t>(stream));
+                                   kv_group, status, static_cast<cudaStream_t>(stream));
 }
 
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
@@ -107,11 +110,16 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
 int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                               const void* v, const int64_t v_strides[4], const int32_t* row_ptr,
                               const int32_t* col_idx, int block, int mode, int num_cls, int window, int dilation,
-                              void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
-                              int* status, void* stream) {
+                              int kv_group, float* lse, void* o, const int64_t o_strides[4], int o_dtype, int B,
+                              int H, int Tq, int Tk, int D, int* status, void* stream) {
   return swv::block_sparse_attn_impl(q, q_strides, k, k_strides, v, v_strides, row_ptr, col_idx, block, mode, num_cls,
-                                     window, dilation, o, o_strides, o_dtype, B, H, Tq, Tk, D, status,
+                                     window, dilation, kv_group, lse, o, o_strides, o_dtype, B, H, Tq, Tk, D, status,
                                      static_cast<cudaStream_t>(stream));
+}
+
+int swv_pool_tokens(const void* x, const int64_t x_strides[4], void* y, int B, int H, int T, int D, int window,
+                    int stride, void* stream) {
+  return swv::pool_tokens_impl(x, x_strides, y, B, H, T, D, window, stride, static_cast<cudaStream_t>(stream));
 }
 
 int swv_rope2d_apply(const void* x, const int64_t x_strides[3], void* y, const int64_t y_strides[3], int dtype,

@@ -27,6 +27,7 @@ struct GatherParams {
   int64_t os[4];
   int o_dtype;
   int B, H, Tq, Tk, D, top_k;
+  int kv_group;   // query heads per key/value head
   float scale;
 };
 
@@ -63,8 +64,9 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
   for (int d = lane; d < D; d += 32) qsm[wib][d] = ld_f32<T>(qrow + d * p.qs[3]);
   __syncwarp();
 
-  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + h * p.ks[1];
-  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + h * p.vs[1];
+  const int hk = h / p.kv_group;
+  const T* kbase = static_cast<const T*>(p.k) + b * p.ks[0] + hk * p.ks[1];
+  const T* vbase = static_cast<const T*>(p.v) + b * p.vs[0] + hk * p.vs[1];
   const int32_t* idx_row = p.idx + b * p.is[0] + qi * p.is[1];
   const float* val_row = p.valid + b * p.vls[0] + qi * p.vls[1];
   const float* rw_row = p.rw + b * p.rs[0] + qi * p.rs[1];
@@ -146,7 +148,7 @@ static int launch_gather(const GatherParams& p, int D, cudaStream_t st) {
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
                          const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
-                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int* status,
+                         int o_dtype, int B, int H, int Tq, int Tk, int D, int top_k, int kv_group, int* status,
                          cudaStream_t st) {
   if (!q || !k || !v || !idx || !valid || !rw || !o || !status || !qs || !ks || !vs || !is || !vls || !rs || !os)
     return SWV_ERR_NULL;
@@ -154,11 +156,12 @@ int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const 
   if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
   if (o_dtype != SWV_F32 && o_dtype != SWV_BF16 && o_dtype != SWV_F16) return SWV_ERR_DTYPE;
   if (D < 1 || D > 256) return SWV_ERR_UNSUPPORTED;
+  if (kv_group < 1 || H % kv_group != 0) return SWV_ERR_SHAPE;
   GatherParams p;
   p.q = q; p.k = k; p.v = v; p.idx = idx; p.valid = valid; p.rw = rw; p.o = o; p.o_dtype = o_dtype;
   for (int i = 0; i < 4; ++i) { p.qs[i] = qs[i]; p.ks[i] = ks[i]; p.vs[i] = vs[i]; p.os[i] = os[i]; }
   for (int i = 0; i < 3; ++i) { p.is[i] = is[i]; p.vls[i] = vls[i]; p.rs[i] = rs[i]; }
-  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k;
+  p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k; p.kv_group = kv_group;
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   if (dtype == SWV_F32) return launch_gather<float>(p, D, st);
   if (dtype == SWV_BF16) return launch_gather<__nv_bfloat16>(p, D, st);

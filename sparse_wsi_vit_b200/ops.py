@@ -109,8 +109,9 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
     return (idx, valid, scores, (mask, ws)) if want_mask else (idx, valid, scores)
 
 
-def dsa_attention_gather(q, k, v, idx, valid, rw, o):
-    """Routing-weighted attention over explicit key lists; writes ``o`` in place."""
+def dsa_attention_gather(q, k, v, idx, valid, rw, o, kv_group=1):
+    """Routing-weighted attention over explicit key lists; writes ``o`` in place.
+    kv_group > 1: k, v have H/kv_group heads (grouped-query attention)."""
     _require_cuda(q, k, v, idx, valid, rw, o)
     B, H, Tq, D = q.shape
     Tk = k.shape[2]
@@ -126,7 +127,8 @@ def dsa_attention_gather(q, k, v, idx, valid, rw, o):
     rc = lib.swv_dsa_attn_gather_fwd(
         q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), dtype_code(q.dtype),
         idx.data_ptr(), strides(idx), valid.data_ptr(), strides(valid), rw.data_ptr(), strides(rw),
-        o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D, top_k, st.data_ptr(), _stream(dev))
+        o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D, top_k, kv_group, st.data_ptr(),
+        _stream(dev))
     check(rc, "swv_dsa_attn_gather_fwd")
     return o
 
@@ -226,7 +228,7 @@ class DSAAttentionFunction(torch.autograd.Function):
 # static block-sparse attention and 2-D RoPE
 # --------------------------------------------------------------------------- #
 def block_sparse_attention(q, k, v, row_ptr, col_idx, block, mode=0, num_cls=0, window=0, dilation=1,
-                           out_dtype=None):
+                           out_dtype=None, kv_group=1, return_lse=False):
     """Flash attention restricted to a CSR list of key blocks per query block.
 
     q (B,H,Tq,D), k, v (B,H,Tk,D) bf16 (other float dtypes are converted); row_ptr / col_idx int32
@@ -257,15 +259,18 @@ def block_sparse_attention(q, k, v, row_ptr, col_idx, block, mode=0, num_cls=0, 
         raise SwvError(f"row_ptr has {row_ptr.numel()} entries, expected {nqb + 1}")
     dev = q.device
     o = torch.empty((B, H, Tq, D), dtype=out_dtype, device=dev)
+    lse = torch.empty((B, H, Tq), dtype=torch.float32, device=dev) if return_lse else None
     st = status_word(dev)
     rc = lib.swv_block_sparse_attn_fwd(
         q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), row_ptr.data_ptr(),
-        col_idx.data_ptr(), block, mode, num_cls, window, dilation, o.data_ptr(), strides(o), dtype_code(o.dtype),
+        col_idx.data_ptr(), block, mode, num_cls, window, dilation, kv_group,
+        lse.data_ptr() if return_lse else None, o.data_ptr(), strides(o), dtype_code(o.dtype),
         B, H, Tq, Tk, D, st.data_ptr(), _stream(dev))
     check(rc, "swv_block_sparse_attn_fwd")
     if _CHECK:
         check_status(dev, "swv_block_sparse_attn_fwd")
-    return o if D == D0 else o[..., :D0]
+    o = o if D == D0 else o[..., :D0]
+    return (o, lse) if return_lse else o
 
 
 def rope2d(x, coords, coord_high, theta=10000.0, skip_tokens=0, out=None):

@@ -74,10 +74,18 @@ def test_argument_validation_happens_before_any_launch(swv):
     assert rc == -2
     # gather attention
     g = lambda q, D, dt: (q, i64x4, fake, i64x4, fake, i64x4, dt, fake, i64x3, fake, i64x3, fake, i64x3, fake, i64x4,
-                          0, 1, 1, 8, 8, D, 4, fake, null)
+                          0, 1, 1, 8, 8, D, 4, 1, fake, null)
     assert L.swv_dsa_attn_gather_fwd(*g(null, 64, 0)) == -1
     assert L.swv_dsa_attn_gather_fwd(*g(fake, 0, 0)) == -8
     assert L.swv_dsa_attn_gather_fwd(*g(fake, 64, 9)) == -3
+    # block-sparse attention: block size, head dim, mode, GQA divisibility
+    bs = lambda block, D, mode, grp: (fake, ok_strides, fake, ok_strides, fake, ok_strides, fake, fake, block, mode, 0,
+                                      0, 1, grp, null, fake, ok_strides, 0, 1, 4, 8, 8, D, fake, null)
+    ok_strides = (ctypes.c_int64 * 4)(4096, 512, 64, 1)
+    assert L.swv_block_sparse_attn_fwd(*bs(32, 64, 0, 1)) == -8
+    assert L.swv_block_sparse_attn_fwd(*bs(64, 96, 0, 1)) == -8
+    assert L.swv_block_sparse_attn_fwd(*bs(64, 64, 2, 1)) == -8
+    assert L.swv_block_sparse_attn_fwd(*bs(64, 64, 0, 3)) == -4
     # dense path: only head_dim 64, unit inner stride, 16-byte aligned rows
     m = lambda D, qs: (fake, qs, fake, i64x4, fake, i64x4, fake, fake, fake, i64x4, 0, 1, 1, 8, 8, D, fake, null)
     ok_strides = (ctypes.c_int64 * 4)(4096, 512, 64, 1)
