@@ -60,13 +60,21 @@ constexpr int kModeEmit = 1;
 constexpr int kStages = 2;                         // wk ring depth
 constexpr int kTileBytes = kTile * kIdxDim * 4;    // 32 KiB fp32 tile (two 16 KiB K-halves)
 constexpr int kHistStride = 257;                   // words per histogram row (+1: bank spread)
-constexpr int kHistBytes = kTile * kHistStride * 4;
+constexpr int kListCap = 512;                      // candidate pass: low-16-bit values kept per row
+constexpr int kListStride = 513;                   // uint16 per row (+1: bank spread)
+constexpr int kListBytes = kTile * kListStride * 2;
+constexpr int kHistBytes = (kTile * kHistStride * 4 > kListBytes + kTile * 4) ? kTile * kHistStride * 4
+                                                                              : kListBytes + kTile * 4;
+constexpr int kKindFirst = 0, kKindMid = 1, kKindCand = 2;
 constexpr int kTmemCols = 256;                     // two 128-column score buffers
 
 struct IndexerParams {
   int B, Tq, Tk, top_k;
   int nQT, nKT;
   int pass;               // HIST: 0..3
+  int kind;               // HIST: first byte / later byte / candidate collection of the low 16 bits
+  int only_flagged;       // HIST: run only for query tiles whose candidate pass overflowed
+  uint32_t* ovf_flags;    // [B*nQT] written by the candidate pass
   uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
   uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
   uint32_t* st_neq;       // [B*Tq] after the last pass: number of keys whose score equals the threshold
@@ -84,6 +92,7 @@ struct TileSmemCtl {
   uint64_t acc_empty[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t overflow;
 };
 
 constexpr int kStageBytes = 4 * 16 * 32 * 4;       // EMIT: per epilogue warp a [16 columns][32 lanes] word tile
@@ -151,6 +160,8 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
   TileSmemCtl* ctl = reinterpret_cast<TileSmemCtl*>(smem + kTileBytes * (1 + kStages) +
                                                     (MODE == kModeHist ? kHistBytes : kStageBytes));
 
+  if (MODE == kModeHist && p.only_flagged != 0 && p.ovf_flags[blockIdx.x] == 0u) return;
+
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int b = blockIdx.x / p.nQT;
@@ -158,6 +169,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
   const int nKT = p.nKT;
 
   if (threadIdx.x == 0) {
+    ctl->overflow = 0;
     mbar_init(&ctl->q_full, 1);
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&ctl->k_full[s], 1);
@@ -240,7 +252,78 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
 
-    if constexpr (MODE == kModeHist) {
+    if (MODE == kModeHist && p.kind == kKindCand) {
+      // Candidate pass: the top 16 bits of every row's threshold are known.  The low 16 bits of
+      // the scores inside that bucket are collected per row (a few dozen on continuous data) and
+      // the exact threshold is selected from the list, replacing the two last histogram passes.
+      // A row with more than kListCap candidates (massive ties) marks the whole query tile for
+      // the histogram passes instead; nothing of the tile's state is written then.
+      const int ch = ew >> 2;
+      const int et = threadIdx.x - 64;
+      uint16_t* list = reinterpret_cast<uint16_t*>(sm_hist);
+      uint32_t* cnt = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(sm_hist) + kListBytes);
+      if (et < kTile) cnt[et] = 0u;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      const uint32_t prefix = row_ok ? p.st_prefix[grow] : 0xFFFFu;
+      const uint32_t lo = prefix << 16;
+      uint16_t* lrow = list + row * kListStride;
+      for (int j = 0; j < nKT; ++j) {
+        const int a = j & 1;
+        if (!mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t r0[32];
+        tmem_ld32(lane_base + a * kTile + ch * 32, r0);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
+        const int nvalid = p.Tk - (j * kTile + ch * 32);
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+          uint32_t t[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            t[q] = relu_bits(r0[i + q]) - lo;
+            if (i + q >= nvalid) t[q] = 0xFFFFFFFFu;
+          }
+          if (min(min(t[0], t[1]), min(t[2], t[3])) < 65536u) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (t[q] < 65536u) {
+                const uint32_t pos = atomicAdd(cnt + row, 1u);
+                if (pos < kListCap) lrow[pos] = static_cast<uint16_t>(t[q]);
+              }
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      const uint32_t n = cnt[row];
+      if (ch == 0 && row_ok && n > kListCap) atomicOr(&ctl->overflow, 1u);
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      const bool tile_overflow = ctl->overflow != 0u;
+      if (et == 0) p.ovf_flags[blockIdx.x] = tile_overflow ? 1u : 0u;
+      if (ok && ch == 0 && row_ok && !tile_overflow && *abort_flag == 0u) {
+        uint32_t kth = p.st_kth[grow];
+        uint32_t val = 0;
+        for (int bit = 15; bit >= 0; --bit) {
+          const uint32_t want = (val >> bit) | 1u;
+          uint32_t c = 0;
+          for (uint32_t i = 0; i < n; ++i) c += ((static_cast<uint32_t>(lrow[i]) >> bit) == want) ? 1u : 0u;
+          if (c >= kth) val |= 1u << bit;
+          else kth -= c;
+        }
+        uint32_t n_eq = 0;
+        for (uint32_t i = 0; i < n; ++i) n_eq += (lrow[i] == val) ? 1u : 0u;
+        p.st_prefix[grow] = lo | val;
+        p.st_kth[grow] = kth;
+        p.st_neq[grow] = n_eq;
+      }
+    } else if constexpr (MODE == kModeHist) {
       const int ch = ew >> 2;                // column quarter 0..3 (32 columns each)
       const int et = threadIdx.x - 64;       // 0..511
       for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
@@ -409,7 +492,7 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, total;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, total;
 };
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
@@ -426,6 +509,8 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.kmax_off = off;     // per (batch, head) key-norm maxima of the attention kernel, up to 1024 entries
   off += 4096;
+  L.flags_off = off;    // one overflow flag per 128-query tile
+  off += align_up(static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * 4, 1024);
   L.total = off;
   return L;
 }
@@ -515,16 +600,31 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   p.st_kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
   p.st_neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
   p.idx = idx; p.scores = scores; p.maskbits = maskbits; p.status = status; p.pass = 0;
+  p.kind = kKindFirst; p.only_flagged = 0;
+  p.ovf_flags = reinterpret_cast<uint32_t*>(ws + L.flags_off);
 
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeHist>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeHist))));
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeEmit))));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT;
-  for (int pass = 0; pass < 4; ++pass) {
+  // bytes 0 and 1 of the threshold by histogram passes, the low 16 bits from a candidate list;
+  // query tiles whose list overflowed (massive ties) fall back to two more histogram passes
+  for (int pass = 0; pass < 2; ++pass) {
+    p.pass = pass;
+    p.kind = pass == 0 ? kKindFirst : kKindMid;
+    indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
+  }
+  p.pass = 2;
+  p.kind = kKindCand;
+  indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
+  p.kind = kKindMid;
+  p.only_flagged = 1;
+  for (int pass = 2; pass < 4; ++pass) {
     p.pass = pass;
     indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
   }
+  p.only_flagged = 0;
   indexer_tiles_kernel<kModeEmit><<<grid, 192, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
 
   const int64_t total = static_cast<int64_t>(B) * Tq * top_k;
@@ -541,7 +641,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
 constexpr int kStaticMaxTokens = 8192;
 constexpr size_t kStaticScratchBytes =
     2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + 3 * static_cast<size_t>(kStaticMaxTokens) * 4 + 4096 +
-    6 * 1024 /* per-section rounding */;
+    1024 /* tile flags */ + 8 * 1024 /* per-section rounding */;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
