@@ -278,7 +278,16 @@ def run_ours(args):
             for i in range(3):
                 dbuf[i].copy_(pinned[i], non_blocking=True)
         o, _ = step(*dbuf, qkv_ready=qkv_ready)
-        o_host.copy_(o, non_blocking=True)
+        if world == 1:
+            # read the result back on the copy stream so the next step's uploads and top-k passes
+            # need not wait for it (the download engine is separate from the upload engine)
+            done = cur.record_event()
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(done)
+                o_host.copy_(o, non_blocking=True)
+                o.record_stream(copy_stream)
+        else:
+            o_host.copy_(o, non_blocking=True)
 
     for _ in range(2):
         e2e_step()
@@ -288,6 +297,7 @@ def run_ours(args):
     e0.record(cur)
     for _ in range(args.steps):
         e2e_step()
+    cur.wait_stream(copy_stream)     # the last download belongs to the timed region
     e1.record(cur)
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps

@@ -65,7 +65,8 @@ constexpr int kListStride = 513;                   // uint16 per row (+1: bank s
 constexpr int kListBytes = kTile * kListStride * 2;
 constexpr int kHistBytes = (kTile * kHistStride * 4 > kListBytes + kTile * 4) ? kTile * kHistStride * 4
                                                                               : kListBytes + kTile * 4;
-constexpr int kKindFirst = 0, kKindMid = 1, kKindCand = 2;
+constexpr int kKindFirst = 0, kKindMid = 1, kKindCand = 2, kKindSpec = 3;
+constexpr int kSampleTiles = 8;                    // speculative pass: key tiles sampled for the top-byte guess
 constexpr int kTmemCols = 256;                     // two 128-column score buffers
 
 struct IndexerParams {
@@ -73,8 +74,9 @@ struct IndexerParams {
   int nQT, nKT;
   int pass;               // HIST: 0..3
   int kind;               // HIST: first byte / later byte / candidate collection of the low 16 bits
-  int only_flagged;       // HIST: run only for query tiles whose candidate pass overflowed
-  uint32_t* ovf_flags;    // [B*nQT] written by the candidate pass
+  int only_flagged;       // HIST: run only for the query tiles flagged in `flags_in`
+  const uint32_t* flags_in;   // [B*nQT]
+  uint32_t* flags_out;    // [B*nQT] written by the speculative and the candidate pass (1 = redo classically)
   uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
   uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
   uint32_t* st_neq;       // [B*Tq] after the last pass: number of keys whose score equals the threshold
@@ -160,13 +162,17 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
   TileSmemCtl* ctl = reinterpret_cast<TileSmemCtl*>(smem + kTileBytes * (1 + kStages) +
                                                     (MODE == kModeHist ? kHistBytes : kStageBytes));
 
-  if (MODE == kModeHist && p.only_flagged != 0 && p.ovf_flags[blockIdx.x] == 0u) return;
+  if (MODE == kModeHist && p.only_flagged != 0 && p.flags_in[blockIdx.x] == 0u) return;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int b = blockIdx.x / p.nQT;
   const int qt = blockIdx.x % p.nQT;
   const int nKT = p.nKT;
+  // The speculative pass streams the first nPre key tiles twice: once to guess the top byte of
+  // every row's threshold from a sample, then the whole key range.
+  const int nPre = (MODE == kModeHist && p.kind == kKindSpec) ? min(nKT, kSampleTiles) : 0;
+  const int nIt = nKT + nPre;
 
   if (threadIdx.x == 0) {
     ctl->overflow = 0;
@@ -200,9 +206,10 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       mbar_expect_tx(&ctl->q_full, kTileBytes);
       tma_load_3d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, b);
       tma_load_3d(sm_q + kTileBytes / 2, &tm_q, &ctl->q_full, 32, qt * kTile, b);
-      for (int j = 0; j < nKT; ++j) {
-        const int s = j % kStages;
-        if (!mbar_wait_bounded(&ctl->k_empty[s], ((j / kStages) & 1) ^ 1, abort_flag)) {
+      for (int it = 0; it < nIt; ++it) {
+        const int j = it < nPre ? it : it - nPre;
+        const int s = it % kStages;
+        if (!mbar_wait_bounded(&ctl->k_empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
           break;
         }
@@ -218,7 +225,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
       if (!ok) record_status(p.status, kDevWaitQ);
       const uint32_t q_addr = smem_u32(sm_q);
-      for (int j = 0; ok && j < nKT; ++j) {
+      for (int j = 0; ok && j < nIt; ++j) {
         const int s = j % kStages;
         const int a = j & 1;
         if (!mbar_wait_bounded(&ctl->k_full[s], (j / kStages) & 1, abort_flag)) {
@@ -252,7 +259,101 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
 
-    if (MODE == kModeHist && p.kind == kKindCand) {
+    if (MODE == kModeHist && p.kind == kKindSpec) {
+      // Speculative fusion of the two first radix passes.  Phase 1 histograms the top byte of
+      // the scores against the first nPre key tiles and guesses, per row, the top byte d0 of the
+      // K-th largest score (rank scaled to the sample).  Phase 2 streams all keys: scores above
+      // the guessed bucket are counted, scores inside it are binned on their second byte.  The
+      // guess is then CHECKED with the exact counts (above < K <= above + inside); a tile with any
+      // row that fails is flagged and redone by the two classic passes.
+      const int ch = ew >> 2;
+      const int et = threadIdx.x - 64;
+      for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      uint32_t* hrow = sm_hist + row * kHistStride;
+      const uint32_t hrow_s = smem_u32(hrow);
+      const uint32_t k_eff = static_cast<uint32_t>(min(p.top_k, p.Tk));
+      uint32_t zeros = 0, above = 0, lo = 0;
+      for (int it = 0; it < nIt; ++it) {
+        const int j = it < nPre ? it : it - nPre;
+        const int a = it & 1;
+        if (it == nPre) {
+          // ---- end of the sample: guess d0, then clear the histogram for phase 2
+          if (zeros != 0u) atomicAdd(hrow, zeros);
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+          const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nPre * kTile));
+          uint32_t rank = static_cast<uint32_t>((static_cast<uint64_t>(k_eff) * n_s + p.Tk - 1) / p.Tk);
+          rank = max(rank, 1u);
+          uint32_t cum = 0, d0 = 0;
+          for (int bin = 255; bin >= 0; --bin) {
+            cum += hrow[bin];
+            if (cum >= rank) {
+              d0 = static_cast<uint32_t>(bin);
+              break;
+            }
+          }
+          lo = d0 << 24;
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+          for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+        }
+        if (!mbar_wait_bounded(&ctl->acc_full[a], (it >> 1) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        uint32_t r0[32];
+        tmem_ld32(lane_base + a * kTile + ch * 32, r0);
+        tc_wait_ld();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
+        const int nvalid = p.Tk - (j * kTile + ch * 32);
+        if (it < nPre) {
+          if (nvalid >= 32) hist_update<false, true>(r0, hrow_s, 24, 0u, 0u, 32, zeros);
+          else hist_update<true, true>(r0, hrow_s, 24, 0u, 0u, nvalid, zeros);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const uint32_t u = relu_bits(r0[i]);
+            const uint32_t t = (i < nvalid) ? u - lo : 0xFFFFFFFFu;
+            // t >= 2^24: either below the bucket (u < lo, wrapped around) or above it (u >= lo + 2^24)
+            above += (t >= (1u << 24) && i < nvalid && u >= lo) ? 1u : 0u;
+            red_inc_shared_if_lt(hrow_s + ((t >> 16) << 2), t, 1u << 24);
+          }
+        }
+      }
+      if (above != 0u) atomicAdd(hrow + 256, above);      // word 256 of a row is its padding slot
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      bool row_valid = true;
+      uint32_t digit = 0, cum = 0, kth = 0;
+      if (ch == 0 && row_ok) {
+        const uint32_t n_above = hrow[256];
+        row_valid = n_above < k_eff;
+        if (row_valid) {
+          kth = k_eff - n_above;
+          row_valid = false;
+          for (int bin = 255; bin >= 0; --bin) {
+            const uint32_t c = hrow[bin];
+            if (cum + c >= kth) {
+              digit = static_cast<uint32_t>(bin);
+              row_valid = true;
+              break;
+            }
+            cum += c;
+          }
+        }
+        if (!row_valid) atomicOr(&ctl->overflow, 1u);
+      }
+      asm volatile("bar.sync 1, 512;" ::: "memory");
+      const bool redo = ctl->overflow != 0u || !ok || *abort_flag != 0u;
+      if (et == 0) p.flags_out[blockIdx.x] = redo ? 1u : 0u;
+      if (!redo && ch == 0 && row_ok) {
+        p.st_prefix[grow] = ((lo >> 24) << 8) | digit;
+        p.st_kth[grow] = kth - cum;
+      }
+    } else if (MODE == kModeHist && p.kind == kKindCand) {
       // Candidate pass: the top 16 bits of every row's threshold are known.  The low 16 bits of
       // the scores inside that bucket are collected per row (a few dozen on continuous data) and
       // the exact threshold is selected from the list, replacing the two last histogram passes.
@@ -306,7 +407,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       if (ch == 0 && row_ok && n > kListCap) atomicOr(&ctl->overflow, 1u);
       asm volatile("bar.sync 1, 512;" ::: "memory");
       const bool tile_overflow = ctl->overflow != 0u;
-      if (et == 0) p.ovf_flags[blockIdx.x] = tile_overflow ? 1u : 0u;
+      if (et == 0) p.flags_out[blockIdx.x] = tile_overflow ? 1u : 0u;
       if (ok && ch == 0 && row_ok && !tile_overflow && *abort_flag == 0u) {
         uint32_t kth = p.st_kth[grow];
         uint32_t val = 0;
@@ -492,7 +593,7 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, total;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, flags2_off, total;
 };
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
@@ -509,7 +610,9 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.kmax_off = off;     // per (batch, head) key-norm maxima of the attention kernel, up to 1024 entries
   off += 4096;
-  L.flags_off = off;    // one overflow flag per 128-query tile
+  L.flags_off = off;    // per 128-query tile: redo the two first passes classically
+  off += align_up(static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * 4, 1024);
+  L.flags2_off = off;   // per 128-query tile: redo the two last passes classically
   off += align_up(static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * 4, 1024);
   L.total = off;
   return L;
@@ -601,28 +704,34 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   p.st_neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
   p.idx = idx; p.scores = scores; p.maskbits = maskbits; p.status = status; p.pass = 0;
   p.kind = kKindFirst; p.only_flagged = 0;
-  p.ovf_flags = reinterpret_cast<uint32_t*>(ws + L.flags_off);
+  uint32_t* flags_a = reinterpret_cast<uint32_t*>(ws + L.flags_off);
+  uint32_t* flags_b = reinterpret_cast<uint32_t*>(ws + L.flags2_off);
+  p.flags_in = flags_a; p.flags_out = flags_a;
 
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeHist>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeHist))));
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeEmit))));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT;
-  // bytes 0 and 1 of the threshold by histogram passes, the low 16 bits from a candidate list;
-  // query tiles whose list overflowed (massive ties) fall back to two more histogram passes
-  for (int pass = 0; pass < 2; ++pass) {
-    p.pass = pass;
-    p.kind = pass == 0 ? kKindFirst : kKindMid;
-    indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
-  }
-  p.pass = 2;
-  p.kind = kKindCand;
-  indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
-  p.kind = kKindMid;
-  p.only_flagged = 1;
+  // Radix select of every row's K-th largest score, 32 bits:
+  //   bytes 0-1: one speculative fused pass (top byte guessed from a sample, checked with exact
+  //              counts); query tiles where the check fails redo the two classic histogram passes;
+  //   bytes 2-3: one candidate-list pass; tiles whose list overflowed (massive ties) redo the two
+  //              classic histogram passes.
+  const size_t hs = tile_smem_bytes(kModeHist);
+  p.pass = 1; p.kind = kKindSpec; p.only_flagged = 0; p.flags_out = flags_a;
+  indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+  p.only_flagged = 1; p.flags_in = flags_a;
+  p.pass = 0; p.kind = kKindFirst;
+  indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+  p.pass = 1; p.kind = kKindMid;
+  indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+  p.pass = 2; p.kind = kKindCand; p.only_flagged = 0; p.flags_out = flags_b;
+  indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+  p.only_flagged = 1; p.flags_in = flags_b; p.kind = kKindMid;
   for (int pass = 2; pass < 4; ++pass) {
     p.pass = pass;
-    indexer_tiles_kernel<kModeHist><<<grid, 576, tile_smem_bytes(kModeHist), st>>>(tm_q, tm_k, p);
+    indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
   }
   p.only_flagged = 0;
   indexer_tiles_kernel<kModeEmit><<<grid, 192, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
@@ -641,7 +750,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
 constexpr int kStaticMaxTokens = 8192;
 constexpr size_t kStaticScratchBytes =
     2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + 3 * static_cast<size_t>(kStaticMaxTokens) * 4 + 4096 +
-    1024 /* tile flags */ + 8 * 1024 /* per-section rounding */;
+    2 * 1024 /* tile flags */ + 8 * 1024 /* per-section rounding */;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
