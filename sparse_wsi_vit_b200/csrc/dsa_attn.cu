@@ -22,7 +22,9 @@
 // Two softmax paths, chosen per warp from the row constants the indexer left behind:
 //   one pass  : a key is selected iff its recomputed score >= the row threshold; the
 //               stabiliser is a constant Cauchy-Schwarz bound of the row's logits, so there
-//               is no running maximum and no rescaling:  p = 2^(s*c - bound) * score.
+//               is no running maximum and no rescaling:  p = 2^(s*c - bound) * score.  The
+//               weights of a tile are first packed to bf16 in registers so that R is free
+//               for the next tile while the probabilities are computed.
 //   two pass  : membership from the tile-major bitmask (ties cut by key index, members of
 //               weight zero), exact maximum over the selected logits beside a lazily raised
 //               stabiliser, the reference's 1e-6 clamp on the denominator reproduced:
@@ -129,41 +131,61 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
   const uint32_t r_col = st.lane_base + kColR;
   float l0 = 0.f, l1 = 0.f;
   for (int j = 0; j < nKT; ++j) {
-    if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag) ||
-        !mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
+    // ---- phase A: the row's routing weights of this tile, (score >= thr ? score : 0), packed
+    // to bf16 pairs in registers.  R is released right after, so the tensor pipe computes the
+    // next routing-weight tile under the rest of this pass and the two heads stop waiting
+    // for each other.
+    if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
       record_status(status, kDevWaitAccFull);
       return false;
     }
     tc_fence_after();
-    // 16 columns at a time; the loads of unit u+1 are in flight while unit u is computed
-    uint32_t sa[16], ra[16], sb[16], rb[16];
+    uint32_t wpk[64];
+    {
+      uint32_t ra[16], rb[16];
+      tmem_ld16(r_col, ra);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        tc_wait_ld();
+        if (u + 1 < 8) {
+          if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
+          else tmem_ld16(r_col + (u + 1) * 16, rb);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
+          const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
+          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
+        }
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&ctl->r_free);
+
+    // ---- phase B: p = 2^(s*c - bound) * weight, 16 columns at a time, loads one unit ahead
+    if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
+      record_status(status, kDevWaitAccFull);
+      return false;
+    }
+    tc_fence_after();
+    uint32_t sa[16], sb[16];
     tmem_ld16(s_col, sa);
-    tmem_ld16(r_col, ra);
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       tc_wait_ld();
       if (u + 1 < 8) {
-        if (u & 1) {
-          tmem_ld16(s_col + (u + 1) * 16, sa);
-          tmem_ld16(r_col + (u + 1) * 16, ra);
-        } else {
-          tmem_ld16(s_col + (u + 1) * 16, sb);
-          tmem_ld16(r_col + (u + 1) * 16, rb);
-        }
-      } else {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->r_free);
+        if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+        else tmem_ld16(s_col + (u + 1) * 16, sb);
       }
       uint32_t packed[8];
 #pragma unroll
       for (int i = 0; i < 16; i += 2) {
         const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
         const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
-        const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
-        const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-        const float p0 = keep_where_ge(ex2_approx(fmaf(s0, sc, neg_b)) * r0, r0, thr);
-        const float p1 = keep_where_ge(ex2_approx(fmaf(s1, sc, neg_b)) * r1, r1, thr);
+        const uint32_t wp = wpk[u * 8 + (i >> 1)];
+        const float p0 = ex2_approx(fmaf(s0, sc, neg_b)) * __uint_as_float(wp << 16);
+        const float p1 = ex2_approx(fmaf(s1, sc, neg_b)) * __uint_as_float(wp & 0xffff0000u);
         l0 += p0;
         l1 += p1;
         packed[i >> 1] = pack_bf16x2(p0, p1);
