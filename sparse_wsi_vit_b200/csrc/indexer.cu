@@ -97,7 +97,8 @@ struct TileSmemCtl {
   uint32_t overflow;
 };
 
-constexpr int kStageBytes = 4 * 16 * 32 * 4;       // EMIT: per epilogue warp a [16 columns][32 lanes] word tile
+// EMIT: per epilogue warp a [32 columns][32 lanes] word tile, then the row exchange [2][128][4] x 8 B
+constexpr int kStageBytes = 16 * 32 * 32 * 4 + 2 * kTile * 4 * 8;
 constexpr size_t tile_smem_bytes(int mode) {
   return 1024 /*alignment slack*/ + kTileBytes * (1 + kStages) + (mode == kModeHist ? kHistBytes : kStageBytes) +
          sizeof(TileSmemCtl) + 64;
@@ -115,6 +116,11 @@ __device__ __forceinline__ void red_inc_shared(uint32_t saddr) {
 __device__ __forceinline__ void red_inc_shared_if_lt(uint32_t saddr, uint32_t t, uint32_t span) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(saddr), "r"(t),
                "r"(span)
+               : "memory");
+}
+// if (t >= 0) ++*saddr  (signed test)
+__device__ __forceinline__ void red_inc_shared_if_ge0(uint32_t saddr, int t) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ge.s32 p, %1, 0;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(saddr), "r"(t)
                : "memory");
 }
 // w |= bit where v >= t / v == t   (one compare + one predicated OR)
@@ -147,11 +153,24 @@ __device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], uint32_t h
   }
 }
 
+// Speculative pass, 32 scores of one thread: a score u >= lo lands in bin (u - lo) >> 16 of the
+// row's histogram; everything at or beyond lo + 2^24 shares bin 256 (the row's padding word).
+template <bool CHECK>
+__device__ __forceinline__ void window_update(const uint32_t (&r0)[32], uint32_t hrow, uint32_t lo, int nvalid) {
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    int t = static_cast<int>(relu_bits(r0[i]) - lo);          // both < 2^31: negative iff below the window
+    if (CHECK && i >= nvalid) t = -1;
+    const uint32_t bin = min(static_cast<uint32_t>(t) >> 16, 256u);
+    red_inc_shared_if_ge0(hrow + (bin << 2), t);
+  }
+}
+
 template <int MODE>
-__global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHist ? 1 : 2)
+__global__ void __launch_bounds__(576, 1)
     indexer_tiles_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                          const IndexerParams p) {
-  constexpr int kEpiWarps = MODE == kModeHist ? 16 : 4;
+  constexpr int kEpiWarps = 16;
   constexpr uint32_t kIdesc = make_idesc(/*tf32*/ 2, kTile, kTile, 0, 0);
 
   extern __shared__ uint8_t smem_raw[];
@@ -169,9 +188,10 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
   const int b = blockIdx.x / p.nQT;
   const int qt = blockIdx.x % p.nQT;
   const int nKT = p.nKT;
-  // The speculative pass streams the first nPre key tiles twice: once to guess the top byte of
-  // every row's threshold from a sample, then the whole key range.
-  const int nPre = (MODE == kModeHist && p.kind == kKindSpec) ? min(nKT, kSampleTiles) : 0;
+  // The speculative pass first streams a sample of nSample key tiles twice (top byte, then second
+  // byte of every row's estimated threshold), then the whole key range.
+  const int nSample = (MODE == kModeHist && p.kind == kKindSpec) ? min(nKT, kSampleTiles) : 0;
+  const int nPre = 2 * nSample;
   const int nIt = nKT + nPre;
 
   if (threadIdx.x == 0) {
@@ -207,7 +227,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       tma_load_3d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, b);
       tma_load_3d(sm_q + kTileBytes / 2, &tm_q, &ctl->q_full, 32, qt * kTile, b);
       for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? it : it - nPre;
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) : it - nPre;
         const int s = it % kStages;
         if (!mbar_wait_bounded(&ctl->k_empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
@@ -260,12 +280,13 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
     bool ok = true;
 
     if (MODE == kModeHist && p.kind == kKindSpec) {
-      // Speculative fusion of the two first radix passes.  Phase 1 histograms the top byte of
-      // the scores against the first nPre key tiles and guesses, per row, the top byte d0 of the
-      // K-th largest score (rank scaled to the sample).  Phase 2 streams all keys: scores above
-      // the guessed bucket are counted, scores inside it are binned on their second byte.  The
-      // guess is then CHECKED with the exact counts (above < K <= above + inside); a tile with any
-      // row that fails is flagged and redone by the two classic passes.
+      // Speculative fusion of the two first radix passes.  Phase 1 estimates, per row, the top 16
+      // bits of the K-th largest score from a sample of key tiles (rank scaled to the sample; two
+      // 8-bit histogram rounds).  Phase 2 streams all keys against a 2^24-wide window of bit
+      // patterns centred on that estimate (aligned to 2^16): scores beyond the window are counted,
+      // scores inside it are binned on 2^16-wide buckets.  The estimate is then CHECKED with the
+      // exact counts (above < K <= above + inside); a tile with any row that fails is flagged and
+      // redone by the two classic passes.
       const int ch = ew >> 2;
       const int et = threadIdx.x - 64;
       for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
@@ -273,35 +294,46 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       uint32_t* hrow = sm_hist + row * kHistStride;
       const uint32_t hrow_s = smem_u32(hrow);
       const uint32_t k_eff = static_cast<uint32_t>(min(p.top_k, p.Tk));
-      uint32_t zeros = 0, above = 0, lo = 0;
+      uint32_t zeros = 0, lo = 0, rank = 1, est_hi = 0;
       for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? it : it - nPre;
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) : it - nPre;
         const int a = it & 1;
-        if (it == nPre) {
-          // ---- end of the sample: guess d0, then clear the histogram for phase 2
-          if (zeros != 0u) atomicAdd(hrow, zeros);
+        if (it == nSample || it == nPre) {
+          // ---- end of a sample round: take the digit that holds the scaled rank, clear the histogram
+          if (it == nSample) {
+            if (zeros != 0u) atomicAdd(hrow, zeros);
+            const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nSample * kTile));
+            rank = static_cast<uint32_t>((static_cast<uint64_t>(k_eff) * n_s + p.Tk - 1) / p.Tk);
+            rank = max(rank, 1u);
+          }
           asm volatile("bar.sync 1, 512;" ::: "memory");
-          const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nPre * kTile));
-          uint32_t rank = static_cast<uint32_t>((static_cast<uint64_t>(k_eff) * n_s + p.Tk - 1) / p.Tk);
-          rank = max(rank, 1u);
-          uint32_t cum = 0, d0 = 0;
+          uint32_t cum = 0, digit = 0;
           for (int bin = 255; bin >= 0; --bin) {
-            cum += hrow[bin];
-            if (cum >= rank) {
-              d0 = static_cast<uint32_t>(bin);
+            const uint32_t c = hrow[bin];
+            if (cum + c >= rank) {
+              digit = static_cast<uint32_t>(bin);
               break;
             }
+            cum += c;
           }
-          lo = d0 << 24;
+          rank -= min(cum, rank - 1u);
+          if (it == nSample) {
+            est_hi = digit;
+            lo = digit << 24;
+          } else {
+            const uint32_t est16 = (est_hi << 8) | digit;
+            lo = (est16 > 128u ? est16 - 128u : 0u) << 16;
+          }
           asm volatile("bar.sync 1, 512;" ::: "memory");
           for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
           asm volatile("bar.sync 1, 512;" ::: "memory");
         }
-        if (!mbar_wait_bounded(&ctl->acc_full[a], (it >> 1) & 1, abort_flag)) {
+        // (a wait that gave up keeps looping without work: every thread passes the same barriers)
+        if (ok && !mbar_wait_bounded(&ctl->acc_full[a], (it >> 1) & 1, abort_flag)) {
           record_status(p.status, kDevWaitAccFull);
           ok = false;
-          break;
         }
+        if (!ok) continue;
         tc_fence_after();
         uint32_t r0[32];
         tmem_ld32(lane_base + a * kTile + ch * 32, r0);
@@ -310,26 +342,22 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
         const int nvalid = p.Tk - (j * kTile + ch * 32);
-        if (it < nPre) {
+        if (it < nSample) {
           if (nvalid >= 32) hist_update<false, true>(r0, hrow_s, 24, 0u, 0u, 32, zeros);
           else hist_update<true, true>(r0, hrow_s, 24, 0u, 0u, nvalid, zeros);
+        } else if (it < nPre) {
+          if (nvalid >= 32) hist_update<false, false>(r0, hrow_s, 16, lo, 1u << 24, 32, zeros);
+          else hist_update<true, false>(r0, hrow_s, 16, lo, 1u << 24, nvalid, zeros);
         } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const uint32_t u = relu_bits(r0[i]);
-            const uint32_t t = (i < nvalid) ? u - lo : 0xFFFFFFFFu;
-            // t >= 2^24: either below the bucket (u < lo, wrapped around) or above it (u >= lo + 2^24)
-            above += (t >= (1u << 24) && i < nvalid && u >= lo) ? 1u : 0u;
-            red_inc_shared_if_lt(hrow_s + ((t >> 16) << 2), t, 1u << 24);
-          }
+          if (nvalid >= 32) window_update<false>(r0, hrow_s, lo, 32);
+          else window_update<true>(r0, hrow_s, lo, nvalid);
         }
       }
-      if (above != 0u) atomicAdd(hrow + 256, above);      // word 256 of a row is its padding slot
       asm volatile("bar.sync 1, 512;" ::: "memory");
       bool row_valid = true;
       uint32_t digit = 0, cum = 0, kth = 0;
       if (ch == 0 && row_ok) {
-        const uint32_t n_above = hrow[256];
+        const uint32_t n_above = hrow[256];      // word 256 of a row: scores beyond the window
         row_valid = n_above < k_eff;
         if (row_valid) {
           kth = k_eff - n_above;
@@ -350,7 +378,7 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       const bool redo = ctl->overflow != 0u || !ok || *abort_flag != 0u;
       if (et == 0) p.flags_out[blockIdx.x] = redo ? 1u : 0u;
       if (!redo && ch == 0 && row_ok) {
-        p.st_prefix[grow] = ((lo >> 24) << 8) | digit;
+        p.st_prefix[grow] = (lo >> 16) + digit;
         p.st_kth[grow] = kth - cum;
       }
     } else if (MODE == kModeHist && p.kind == kKindCand) {
@@ -483,9 +511,12 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
         if (pass == 3) p.st_neq[grow] = in_bin;
       }
     } else {
-      // EMIT: one thread per query row, all 128 columns of every tile, ascending keys.
-      // Per 16-column unit: (1) branch-free: relu bits to a per-warp shared tile and a
-      // 16-bit member word; (2) a loop over the set bits appends (key, score).
+      // EMIT: four threads per query row (one per 32-column quarter of the tile), ascending keys.
+      // Per tile every thread stages its 32 relu'd scores in a per-warp shared tile, builds a
+      // 32-bit member word (and a word of exact ties where a row's ties are cut), and the four
+      // threads of a row exchange their words through shared memory (one named barrier per tile,
+      // double-buffered) so each knows its output offset.  All four keep identical running counts.
+      const int ch = ew >> 2;
       const uint32_t thr = row_ok ? p.st_prefix[grow] : 0xFFFFFFFFu;
       const uint32_t take_eq = row_ok ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
       const uint32_t n_eq = row_ok ? p.st_neq[grow] : 0u;      // how many keys == thr exist
@@ -496,7 +527,8 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       int cnt = 0;
       int32_t* idx_row = p.idx + grow * p.top_k;
       float* sc_row = p.scores + grow * p.top_k;
-      uint32_t* stage = sm_hist + ew * (16 * 32);              // the staging tiles share the histogram's slot
+      uint32_t* stage = sm_hist + ew * (32 * 32);              // the staging tiles share the histogram's slot
+      uint2* xchg = reinterpret_cast<uint2*>(sm_hist + kEpiWarps * (32 * 32));   // [2][128 rows][4 quarters]
       uint4* mask_row = nullptr;
       if (p.maskbits != nullptr) {
         mask_row = reinterpret_cast<uint4*>(p.maskbits) +
@@ -504,65 +536,81 @@ __global__ void __launch_bounds__(MODE == kModeHist ? 576 : 192, MODE == kModeHi
       }
       for (int j = 0; j < nKT; ++j) {
         const int a = j & 1;
-        if (!mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
+        // (a wait that gave up keeps looping without work: every thread passes the same barriers)
+        if (ok && !mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
           record_status(p.status, kDevWaitAccFull);
           ok = false;
-          break;
         }
-        tc_fence_after();
-        uint32_t words[4] = {0u, 0u, 0u, 0u};
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          uint32_t r[16];
-          tmem_ld16(lane_base + a * kTile + u * 16, r);
+        uint32_t w = 0, e = 0;
+        const int key0 = j * kTile + ch * 32;
+        if (ok) {
+          tc_fence_after();
+          uint32_t r[32];
+          tmem_ld32(lane_base + a * kTile + ch * 32, r);
           tc_wait_ld();
-          if (u == 7) {
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
-          }
-          const int key0 = j * kTile + u * 16;
-          uint32_t w = 0, e = 0;
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
+          for (int i = 0; i < 32; ++i) {
             const uint32_t v = relu_bits(r[i]);
             stage[i * 32 + lane] = v;
             or_bit_if_ge(w, v, thr_min, 1u << i);
           }
           if (warp_partial) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) or_bit_if_eq(e, relu_bits(r[i]), thr, 1u << i);
+            for (int i = 0; i < 32; ++i) or_bit_if_eq(e, relu_bits(r[i]), thr, 1u << i);
           }
           const int nvalid = p.Tk - key0;
-          if (nvalid < 16) {
+          if (nvalid < 32) {
             const uint32_t vm = nvalid <= 0 ? 0u : ((1u << nvalid) - 1u);
             w &= vm;
             e &= vm;
           }
-          if (partial) {
-            while (e != 0u && eq_seen < take_eq) {
-              const uint32_t low = e & (0u - e);
-              w |= low;
-              e ^= low;
+        }
+        uint2* x = xchg + (a * kTile + row) * 4;
+        x[ch] = make_uint2(w, e);
+        asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
+        const uint4 x01 = *reinterpret_cast<const uint4*>(x);
+        const uint4 x23 = *reinterpret_cast<const uint4*>(x + 2);
+        uint32_t fw[4] = {x01.x, x01.z, x23.x, x23.z};
+        if (partial) {
+          const uint32_t ee[4] = {x01.y, x01.w, x23.y, x23.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t eb = ee[c];
+            while (eb != 0u && eq_seen < take_eq) {
+              const uint32_t low = eb & (0u - eb);
+              fw[c] |= low;
+              eb ^= low;
               ++eq_seen;
             }
           }
-          words[u >> 1] |= w << ((u & 1) * 16);
-          while (w != 0u) {
-            const int i = __ffs(w) - 1;
-            w &= w - 1u;
-            if (row_ok && cnt < p.top_k) {
-              idx_row[cnt] = key0 + i;
-              sc_row[cnt] = __uint_as_float(stage[i * 32 + lane]);
-            }
-            ++cnt;
+        }
+        int off = cnt;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int n = __popc(fw[c]);
+          if (c < ch) off += n;
+          cnt += n;
+        }
+        uint32_t mine = fw[0];
+#pragma unroll
+        for (int c = 1; c < 4; ++c) mine = (ch == c) ? fw[c] : mine;
+        while (mine != 0u) {
+          const int i = __ffs(mine) - 1;
+          mine &= mine - 1u;
+          if (row_ok && off < p.top_k) {
+            idx_row[off] = key0 + i;
+            sc_row[off] = __uint_as_float(stage[i * 32 + lane]);
           }
+          ++off;
         }
-        if (mask_row != nullptr) {
-          mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(words[0], words[1], words[2], words[3]);
+        if (mask_row != nullptr && ch == (j & 3)) {
+          mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(fw[0], fw[1], fw[2], fw[3]);
         }
+        __syncwarp();   // the staging tile is rewritten by the next tile
       }
-      (void)ok;
     }
   }
 
@@ -734,7 +782,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
     indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
   }
   p.only_flagged = 0;
-  indexer_tiles_kernel<kModeEmit><<<grid, 192, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
+  indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
 
   const int64_t total = static_cast<int64_t>(B) * Tq * top_k;
   fill_valid_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(valid, idx, scores, total, top_k,
