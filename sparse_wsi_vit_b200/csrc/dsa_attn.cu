@@ -12,9 +12,10 @@
 // online softmax.  One CTA owns (batch, 128 queries, a PAIR of heads):
 //   warp 0      : TMA producer: collapsed indexer queries + Q of both heads once;
 //                 per key tile the collapsed indexer keys, K and V of both heads.
-//   warp 1      : UMMA issuer (one thread, event driven):
+//   warp 1      : UMMA issuer (one thread) of
 //                   R    = wq wk^T       TF32, the routing-weight tile, shared by both heads;
 //                                        bit-identical to the scores the indexer emitted
+//   warps 10,11 : UMMA issuer (one thread each) of head 0 / head 1:
 //                   S_h  = Q_h K_h^T     bf16
 //                   O_h += P_h V_h       P from TMEM, V MN-major from smem, O stays in TMEM
 //   warps 2..5  : softmax of head 0, one thread per query row
@@ -142,20 +143,21 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
     tc_fence_after();
     uint32_t wpk[64];
     {
-      uint32_t ra[16], rb[16];
-      tmem_ld16(r_col, ra);
+      // 32 columns per load, one load ahead: a TMEM load takes longer than converting 16 columns
+      uint32_t ra[32], rb[32];
+      tmem_ld32(r_col, ra);
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
+      for (int u = 0; u < 4; ++u) {
         tc_wait_ld();
-        if (u + 1 < 8) {
-          if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
-          else tmem_ld16(r_col + (u + 1) * 16, rb);
+        if (u + 1 < 4) {
+          if (u & 1) tmem_ld32(r_col + (u + 1) * 32, ra);
+          else tmem_ld32(r_col + (u + 1) * 32, rb);
         }
 #pragma unroll
-        for (int i = 0; i < 16; i += 2) {
+        for (int i = 0; i < 32; i += 2) {
           const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
           const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
+          wpk[u * 16 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
         }
       }
     }
@@ -331,7 +333,7 @@ __global__ void key_norm_max_kernel(const __nv_bfloat16* __restrict__ k, int64_t
   }
 }
 
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(384, 1)
     dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
                            const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -441,87 +443,76 @@ __global__ void __launch_bounds__(320, 1)
       }
     }
   } else if (warp == 1) {
-    // -------------------------------------------------------------- MMA issuer
+    // ------------------------------------------- MMA issuer of the routing-weight tiles R(j)
+    // (Three issuing threads, one per independent MMA stream: a single thread spends most of a
+    // tile period inside the issue sequences and makes the streams wait for each other.)
     if (lane == 0) {
       const uint32_t wq_addr = smem_u32(smem + kOffWq);
       const uint32_t wk_addr = smem_u32(smem + kOffWk);
-      const uint32_t q_addr = smem_u32(smem + kOffQ);
-      const uint32_t k_addr = smem_u32(smem + kOffK);
-      const uint32_t v_addr = smem_u32(smem + kOffV);
       bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
       if (!ok) record_status(p.status, kDevWaitQ);
-
-      int n_r = 0;                    // routing-weight tiles issued
-      int n_qk[2] = {0, 0};           // S tiles issued per head
-      int n_pv[2] = {0, 0};           // PV products issued per head
-      ProgressClock clk;
-      clk.reset();
-      while (ok) {
-        bool done = n_r == nKT, progress = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) done = done && (x >= nh || n_pv[x] == nKT);
-        if (done) break;
-        // R(j): needs the indexer key tile and every softmax warp done with R(j-1)
-        if (n_r < nKT) {
-          const int j = n_r, s = j & 1;
-          if (mbar_test_wait(&ctl->wk_full[s], (j >> 1) & 1) &&
-              (j == 0 || mbar_test_wait(&ctl->r_free, (j - 1) & 1))) {
-            tc_fence_after();
-            // descriptors advance in 16-byte units: +2 per 32-byte K step, +1024 for the second K half
-            const uint64_t da = smem_desc_sw128(wq_addr), db = smem_desc_sw128(wk_addr + s * kWTileBytes);
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              const uint64_t off = (ks >> 2) * (kWTileBytes / 32) + (ks & 3) * 2;
-              umma_tf32_ss(tmem_base + kColR, da + off, db + off, kIdescR, ks > 0);
-            }
-            umma_commit(&ctl->wk_empty[s]);
-            umma_commit(&ctl->r_full);
-            ++n_r;
-            progress = true;
-          }
-        }
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          if (x >= nh) continue;
-          const uint32_t s_col = tmem_base + kColS + x * kTile;
-          // PV_x(j): needs P_x(j) in TMEM and V_x(j) in smem
-          if (n_pv[x] < n_qk[x]) {
-            const int j = n_pv[x];
-            if (mbar_test_wait(&ctl->p_full[x], j & 1) && mbar_test_wait(&ctl->v_full[x], j & 1)) {
-              tc_fence_after();
-              const uint64_t dv = smem_desc_sw128(v_addr + x * kQTileBytes);
-#pragma unroll
-              for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
-                umma_f16_ts(tmem_base + kColO + x * kHeadDim, s_col + ks * 8, dv + ks * 128, kIdescPV,
-                            (j > 0 || ks > 0));
-              umma_commit(&ctl->v_empty[x]);
-              umma_commit(&ctl->pv_done[x]);
-              ++n_pv[x];
-              progress = true;
-            }
-          }
-          // S_x(j): needs K_x(j); it overwrites P_x(j-1), so it is issued behind PV_x(j-1)
-          // (the tensor pipe executes one thread's MMAs in issue order)
-          if (n_qk[x] < nKT && n_qk[x] == n_pv[x]) {
-            const int j = n_qk[x], s = j & 1;
-            if (mbar_test_wait(&ctl->k_full[x][s], (j >> 1) & 1)) {
-              tc_fence_after();
-              const uint64_t da = smem_desc_sw128(q_addr + x * kQTileBytes);
-              const uint64_t db = smem_desc_sw128(k_addr + (x * 2 + s) * kQTileBytes);
-#pragma unroll
-              for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, da + ks * 2, db + ks * 2, kIdescQK, ks > 0);
-              umma_commit(&ctl->k_empty[x][s]);
-              umma_commit(&ctl->s_full[x]);
-              ++n_qk[x];
-              progress = true;
-            }
-          }
-        }
-        if (progress) {
-          clk.reset();
-        } else if (clk.expired(abort_flag)) {
-          record_status(p.status, kDevWaitPReady);
+      for (int j = 0; ok && j < nKT; ++j) {
+        const int s = j & 1;
+        // needs the indexer key tile and every softmax warp done with R(j-1)
+        if (!mbar_wait_bounded(&ctl->wk_full[s], (j >> 1) & 1, abort_flag) ||
+            (j > 0 && !mbar_wait_bounded(&ctl->r_free, (j - 1) & 1, abort_flag))) {
+          record_status(p.status, kDevWaitTmaFull);
           break;
+        }
+        tc_fence_after();
+        // descriptors advance in 16-byte units: +2 per 32-byte K step, +1024 for the second K half
+        const uint64_t da = smem_desc_sw128(wq_addr), db = smem_desc_sw128(wk_addr + s * kWTileBytes);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t off = (ks >> 2) * (kWTileBytes / 32) + (ks & 3) * 2;
+          umma_tf32_ss(tmem_base + kColR, da + off, db + off, kIdescR, ks > 0);
+        }
+        umma_commit(&ctl->wk_empty[s]);
+        umma_commit(&ctl->r_full);
+      }
+    }
+  } else if (warp >= 10) {
+    // ------------------------------------- MMA issuer of one head: S_x(j) and O_x += P_x(j) V_x(j)
+    const int x = warp - 10;
+    if (lane == 0 && x < nh) {
+      const uint32_t q_addr = smem_u32(smem + kOffQ + x * kQTileBytes);
+      const uint32_t k_addr = smem_u32(smem + kOffK + x * 2 * kQTileBytes);
+      const uint32_t v_addr = smem_u32(smem + kOffV + x * kQTileBytes);
+      const uint32_t s_col = tmem_base + kColS + x * kTile;
+      const uint32_t o_col = tmem_base + kColO + x * kHeadDim;
+      const uint64_t dq = smem_desc_sw128(q_addr), dv = smem_desc_sw128(v_addr);
+      bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
+      if (!ok) record_status(p.status, kDevWaitQ);
+      // S_x(j) overwrites P_x(j-1), so it is issued behind PV_x(j-1): the tensor pipe executes
+      // one thread's MMAs in issue order.
+      for (int j = 0; ok && j <= nKT; ++j) {
+        if (j > 0) {
+          // PV_x(j-1): needs P_x(j-1) in TMEM and V_x(j-1) in smem
+          const int jp = j - 1;
+          if (!mbar_wait_bounded(&ctl->p_full[x], jp & 1, abort_flag) ||
+              !mbar_wait_bounded(&ctl->v_full[x], jp & 1, abort_flag)) {
+            record_status(p.status, kDevWaitPReady);
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
+            umma_f16_ts(o_col, s_col + ks * 8, dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
+          umma_commit(&ctl->v_empty[x]);
+          umma_commit(&ctl->pv_done[x]);
+        }
+        if (j < nKT) {
+          const int s = j & 1;
+          if (!mbar_wait_bounded(&ctl->k_full[x][s], (j >> 1) & 1, abort_flag)) {
+            record_status(p.status, kDevWaitTmaFull);
+            break;
+          }
+          tc_fence_after();
+          const uint64_t dk = smem_desc_sw128(k_addr + s * kQTileBytes);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, dq + ks * 2, dk + ks * 2, kIdescQK, ks > 0);
+          umma_commit(&ctl->k_empty[x][s]);
+          umma_commit(&ctl->s_full[x]);
         }
       }
     }
@@ -704,7 +695,7 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(attn_smem_bytes())));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP;
-  dsa_attn_masked_kernel<<<grid, 320, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  dsa_attn_masked_kernel<<<grid, 384, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }
