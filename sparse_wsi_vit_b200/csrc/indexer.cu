@@ -17,6 +17,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace swv {
@@ -59,7 +61,7 @@ constexpr int kModeHist = 0;
 constexpr int kModeEmit = 1;
 constexpr int kStages = 2;                         // wk ring depth
 constexpr int kTileBytes = kTile * kIdxDim * 4;    // 32 KiB fp32 tile (two 16 KiB K-halves)
-constexpr int kHistStride = 257;                   // words per histogram row (+1: bank spread)
+constexpr int kHistStride = 259;                   // words per histogram row (256 bins + 3: odd, bank spread)
 constexpr int kListCap = 512;                      // candidate pass: low-16-bit values kept per row
 constexpr int kListStride = 513;                   // uint16 per row (+1: bank spread)
 constexpr int kListBytes = kTile * kListStride * 2;
@@ -97,8 +99,12 @@ struct TileSmemCtl {
   uint32_t overflow;
 };
 
-// EMIT: per epilogue warp a [32 columns][32 lanes] word tile, then the row exchange [2][128][4] x 8 B
-constexpr int kStageBytes = 16 * 32 * 32 * 4 + 2 * kTile * 4 * 8;
+// EMIT: per epilogue warp a [32 columns][32 lanes] word tile, then the row exchange [2][128][4] x 8 B,
+// then per row two rings (key index, score bits) of kRing entries that turn the 4-byte appends into
+// 32-byte stores
+constexpr int kRing = 32;
+constexpr int kRingStride = kRing + 1;             // words per row (+1: bank spread)
+constexpr int kStageBytes = 16 * 32 * 32 * 4 + 2 * kTile * 4 * 8 + 2 * kTile * kRingStride * 4;
 constexpr size_t tile_smem_bytes(int mode) {
   return 1024 /*alignment slack*/ + kTileBytes * (1 + kStages) + (mode == kModeHist ? kHistBytes : kStageBytes) +
          sizeof(TileSmemCtl) + 64;
@@ -116,11 +122,6 @@ __device__ __forceinline__ void red_inc_shared(uint32_t saddr) {
 __device__ __forceinline__ void red_inc_shared_if_lt(uint32_t saddr, uint32_t t, uint32_t span) {
   asm volatile("{\n\t.reg .pred p;\n\tsetp.lt.u32 p, %1, %2;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(saddr), "r"(t),
                "r"(span)
-               : "memory");
-}
-// if (t >= 0) ++*saddr  (signed test)
-__device__ __forceinline__ void red_inc_shared_if_ge0(uint32_t saddr, int t) {
-  asm volatile("{\n\t.reg .pred p;\n\tsetp.ge.s32 p, %1, 0;\n\t@p red.shared.add.u32 [%0], 1;\n\t}" ::"r"(saddr), "r"(t)
                : "memory");
 }
 // w |= bit where v >= t / v == t   (one compare + one predicated OR)
@@ -153,16 +154,18 @@ __device__ __forceinline__ void hist_update(const uint32_t (&r0)[32], uint32_t h
   }
 }
 
-// Speculative pass, 32 scores of one thread: a score u >= lo lands in bin (u - lo) >> 16 of the
-// row's histogram; everything at or beyond lo + 2^24 shares bin 256 (the row's padding word).
+// Speculative pass, 32 scores of one thread.  Row layout of this pass: word 0 takes every score
+// below the window, word 1 + b the scores of bucket b = (u - lo) >> 16 (b < 256), word 257 every
+// score at or beyond lo + 2^24.  The reduction is unconditional (a predicated one compiles to a
+// branch around it); padding columns of the ragged last key tile land in word 0.
 template <bool CHECK>
 __device__ __forceinline__ void window_update(const uint32_t (&r0)[32], uint32_t hrow, uint32_t lo, int nvalid) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) {
     int t = static_cast<int>(relu_bits(r0[i]) - lo);          // both < 2^31: negative iff below the window
     if (CHECK && i >= nvalid) t = -1;
-    const uint32_t bin = min(static_cast<uint32_t>(t) >> 16, 256u);
-    red_inc_shared_if_ge0(hrow + (bin << 2), t);
+    const int bin = min(max(t >> 16, -1), 256);               // arithmetic shift keeps the sign
+    red_inc_shared(hrow + 4u + static_cast<uint32_t>(bin << 2));
   }
 }
 
@@ -357,13 +360,13 @@ __global__ void __launch_bounds__(576, 1)
       bool row_valid = true;
       uint32_t digit = 0, cum = 0, kth = 0;
       if (ch == 0 && row_ok) {
-        const uint32_t n_above = hrow[256];      // word 256 of a row: scores beyond the window
+        const uint32_t n_above = hrow[257];      // scores beyond the window
         row_valid = n_above < k_eff;
         if (row_valid) {
           kth = k_eff - n_above;
           row_valid = false;
           for (int bin = 255; bin >= 0; --bin) {
-            const uint32_t c = hrow[bin];
+            const uint32_t c = hrow[1 + bin];
             if (cum + c >= kth) {
               digit = static_cast<uint32_t>(bin);
               row_valid = true;
@@ -411,24 +414,30 @@ __global__ void __launch_bounds__(576, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
         const int nvalid = p.Tk - (j * kTile + ch * 32);
+        // two instances of the scan: the bounds test only exists for the ragged last key tile
+        auto scan = [&](auto check) {
+          constexpr bool kCheck = decltype(check)::value;
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          uint32_t t[4];
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            t[q] = relu_bits(r0[i + q]) - lo;
-            if (i + q >= nvalid) t[q] = 0xFFFFFFFFu;
-          }
-          if (min(min(t[0], t[1]), min(t[2], t[3])) < 65536u) {
+          for (int i = 0; i < 32; i += 4) {
+            uint32_t t[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              if (t[q] < 65536u) {
-                const uint32_t pos = atomicAdd(cnt + row, 1u);
-                if (pos < kListCap) lrow[pos] = static_cast<uint16_t>(t[q]);
+              t[q] = relu_bits(r0[i + q]) - lo;
+              if (kCheck && i + q >= nvalid) t[q] = 0xFFFFFFFFu;
+            }
+            if (min(min(t[0], t[1]), min(t[2], t[3])) < 65536u) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (t[q] < 65536u) {
+                  const uint32_t pos = atomicAdd(cnt + row, 1u);
+                  if (pos < kListCap) lrow[pos] = static_cast<uint16_t>(t[q]);
+                }
               }
             }
           }
-        }
+        };
+        if (nvalid >= 32) scan(std::false_type{});
+        else scan(std::true_type{});
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
       const uint32_t n = cnt[row];
@@ -516,6 +525,9 @@ __global__ void __launch_bounds__(576, 1)
       // 32-bit member word (and a word of exact ties where a row's ties are cut), and the four
       // threads of a row exchange their words through shared memory (one named barrier per tile,
       // double-buffered) so each knows its output offset.  All four keep identical running counts.
+      // Appends go to the row's ring in shared memory; after the NEXT tile's barrier one of the four
+      // threads writes the completed groups of 8 entries as 32-byte stores (a 4-byte store per entry
+      // costs the L2 a sector write each).  A tile that would overrun the ring writes directly.
       const int ch = ew >> 2;
       const uint32_t thr = row_ok ? p.st_prefix[grow] : 0xFFFFFFFFu;
       const uint32_t take_eq = row_ok ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
@@ -529,6 +541,34 @@ __global__ void __launch_bounds__(576, 1)
       float* sc_row = p.scores + grow * p.top_k;
       uint32_t* stage = sm_hist + ew * (32 * 32);              // the staging tiles share the histogram's slot
       uint2* xchg = reinterpret_cast<uint2*>(sm_hist + kEpiWarps * (32 * 32));   // [2][128 rows][4 quarters]
+      uint32_t* ring_i = reinterpret_cast<uint32_t*>(xchg + 2 * kTile * 4) + row * kRingStride;
+      uint32_t* ring_s = ring_i + kTile * kRingStride;
+      const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.scores)) & 15) == 0 &&
+                          (p.top_k & 3) == 0;
+      int flushed = 0;                                          // entries of the row already in global memory
+      // entries [from, to) of the row leave the ring
+      auto flush = [&](int from, int to) {
+        int e = from;
+        while (e < to) {
+          if (vec_ok && (e & 7) == 0 && e + 8 <= to) {
+            uint32_t vi[8], vs[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              vi[t] = ring_i[(e + t) & (kRing - 1)];
+              vs[t] = ring_s[(e + t) & (kRing - 1)];
+            }
+            *reinterpret_cast<uint4*>(idx_row + e) = make_uint4(vi[0], vi[1], vi[2], vi[3]);
+            *reinterpret_cast<uint4*>(idx_row + e + 4) = make_uint4(vi[4], vi[5], vi[6], vi[7]);
+            *reinterpret_cast<uint4*>(sc_row + e) = make_uint4(vs[0], vs[1], vs[2], vs[3]);
+            *reinterpret_cast<uint4*>(sc_row + e + 4) = make_uint4(vs[4], vs[5], vs[6], vs[7]);
+            e += 8;
+          } else {
+            idx_row[e] = static_cast<int32_t>(ring_i[e & (kRing - 1)]);
+            sc_row[e] = __uint_as_float(ring_s[e & (kRing - 1)]);
+            ++e;
+          }
+        }
+      };
       uint4* mask_row = nullptr;
       if (p.maskbits != nullptr) {
         mask_row = reinterpret_cast<uint4*>(p.maskbits) +
@@ -587,13 +627,17 @@ __global__ void __launch_bounds__(576, 1)
             }
           }
         }
-        int off = cnt;
+        int off = cnt, cnt_new = cnt;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           const int n = __popc(fw[c]);
           if (c < ch) off += n;
-          cnt += n;
+          cnt_new += n;
         }
+        // (identical for the row's four threads) entries of earlier tiles are visible since the barrier
+        const bool ring_ok = cnt_new - flushed <= kRing;
+        const int upto = min(ring_ok ? (cnt & ~7) : cnt, p.top_k);
+        if (row_ok && ch == (j & 3) && upto > flushed) flush(flushed, upto);
         uint32_t mine = fw[0];
 #pragma unroll
         for (int c = 1; c < 4; ++c) mine = (ch == c) ? fw[c] : mine;
@@ -601,16 +645,26 @@ __global__ void __launch_bounds__(576, 1)
           const int i = __ffs(mine) - 1;
           mine &= mine - 1u;
           if (row_ok && off < p.top_k) {
-            idx_row[off] = key0 + i;
-            sc_row[off] = __uint_as_float(stage[i * 32 + lane]);
+            const uint32_t v = stage[i * 32 + lane];
+            if (ring_ok) {
+              ring_i[off & (kRing - 1)] = static_cast<uint32_t>(key0 + i);
+              ring_s[off & (kRing - 1)] = v;
+            } else {
+              idx_row[off] = key0 + i;
+              sc_row[off] = __uint_as_float(v);
+            }
           }
           ++off;
         }
+        flushed = ring_ok ? max(flushed, upto) : min(cnt_new, p.top_k);
+        cnt = cnt_new;
         if (mask_row != nullptr && ch == (j & 3)) {
           mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(fw[0], fw[1], fw[2], fw[3]);
         }
         __syncwarp();   // the staging tile is rewritten by the next tile
       }
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
+      if (row_ok && ch == 0) flush(flushed, min(cnt, p.top_k));
     }
   }
 
