@@ -185,12 +185,12 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
       for (int i = 0; i < 16; i += 2) {
         const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
         const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
-        const uint32_t wp = wpk[u * 8 + (i >> 1)];
-        const float p0 = ex2_approx(fmaf(s0, sc, neg_b)) * __uint_as_float(wp << 16);
-        const float p1 = ex2_approx(fmaf(s1, sc, neg_b)) * __uint_as_float(wp & 0xffff0000u);
-        l0 += p0;
-        l1 += p1;
-        packed[i >> 1] = pack_bf16x2(p0, p1);
+        // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
+        // the bf16 products the tensor core will see
+        const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
+                                       wpk[u * 8 + (i >> 1)]);
+        add_bf16x2_to_f32(l0, l1, pp);
+        packed[i >> 1] = pp;
       }
       tmem_st8(s_col + u * 8, packed);
     }
