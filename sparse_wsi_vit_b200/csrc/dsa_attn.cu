@@ -18,9 +18,10 @@
 //   warps 10,11 : UMMA issuer (one thread each) of head 0 / head 1:
 //                   S_h  = Q_h K_h^T     bf16
 //                   O_h += P_h V_h       P from TMEM, V MN-major from smem, O stays in TMEM
-//   warps 2..5  : softmax of head 0, one thread per query row
-//   warps 6..9  : softmax of head 1
-// Two softmax paths, chosen per warp from the row constants the indexer left behind:
+//   warps 2..9  : softmax.  One-pass path: warp (quarter, half) owns 32 query rows x 64 key
+//                 columns of every tile for both heads; two-pass path: warps 2..5 head 0,
+//                 warps 6..9 head 1, one thread per query row
+// Two softmax paths, chosen per CTA from the row constants the indexer left behind:
 //   one pass  : a key is selected iff its recomputed score >= the row threshold; the
 //               stabiliser is a constant Cauchy-Schwarz bound of the row's logits, so there
 //               is no running maximum and no rescaling:  p = 2^(s*c - bound) * score.  The
@@ -30,8 +31,8 @@
 //               weight zero), exact maximum over the selected logits beside a lazily raised
 //               stabiliser, the reference's 1e-6 clamp on the denominator reproduced:
 //               out = O*c / max(l*c, 1e-6), c = 2^(m_used - m_true).
-// TMEM (512 columns): R [0,128) | S_h fp32 [128+128h, +128), P_h (bf16x2) overwrites the
-// first 64 columns of S_h as the row is consumed | O_h fp32 [384+64h, +64).
+// TMEM (512 columns): R [0,128) | S_h fp32 [128+128h, +128), P_h (bf16x2) overwrites columns
+// [0,32) (keys 0..63) and [64,96) (keys 64..127) of S_h as they are consumed | O_h fp32 [384+64h, +64).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -78,6 +79,7 @@ struct AttnCtl {
   uint64_t s_full[2], p_full[2], pv_done[2];
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t cta_exact;          // some row of the CTA needs the two-pass path
 };
 
 constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
@@ -122,42 +124,43 @@ struct SoftmaxRow {
   const uint4* mask_tile;
 };
 
-// One-pass per-tile loop.  Every logit of the row is bounded by st.bound (Cauchy-Schwarz on
-// the row's q and the largest key norm of the head), so 2^(s*sc - bound) never overflows and
-// the accumulator never needs rescaling.  Membership: recomputed score >= row threshold.
-__device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
-                                                   int* status, volatile uint32_t* abort_flag) {
-  const float sc = st.sc, thr = st.thr_ge, neg_b = -st.bound;
-  const uint32_t s_col = st.s_col;
-  const uint32_t r_col = st.lane_base + kColR;
-  float l0 = 0.f, l1 = 0.f;
+// One-pass per-tile loop, column-split: the warp owns 32 query rows x 64 key columns
+// (`half` = which 64) of every tile, for BOTH heads of the CTA.  Every logit of a row is bounded
+// by the row's `bound` (Cauchy-Schwarz on q and the largest key norm of the head), so
+// 2^(s*sc - bound) never overflows and the accumulator never needs rescaling.  Membership:
+// recomputed score >= row threshold.  Per tile: the routing weights (score >= thr ? score : 0)
+// of the 64 columns are packed to bf16 pairs in registers ONCE for both heads and R is released;
+// then, per head, p = 2^(s*c - bound) * weight goes to TMEM as bf16.  With eight warps on one
+// head's tile at a time, a head's S -> P -> PV -> next S chain is short enough to hide behind
+// the other head's pass.
+__device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int half, int nh, int nKT,
+                                                    int lane, float thr, float sc, const float (&bound)[2],
+                                                    float (&l_out)[2], int* status,
+                                                    volatile uint32_t* abort_flag) {
+  const uint32_t r_col = lane_base + kColR + half * 64;
+  float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   for (int j = 0; j < nKT; ++j) {
-    // ---- phase A: the row's routing weights of this tile, (score >= thr ? score : 0), packed
-    // to bf16 pairs in registers.  R is released right after, so the tensor pipe computes the
-    // next routing-weight tile under the rest of this pass and the two heads stop waiting
-    // for each other.
     if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
       record_status(status, kDevWaitAccFull);
       return false;
     }
     tc_fence_after();
-    uint32_t wpk[64];
+    uint32_t wpk[32];
     {
-      // 32 columns per load, one load ahead: a TMEM load takes longer than converting 16 columns
-      uint32_t ra[32], rb[32];
-      tmem_ld32(r_col, ra);
+      uint32_t ra[16], rb[16];
+      tmem_ld16(r_col, ra);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         tc_wait_ld();
         if (u + 1 < 4) {
-          if (u & 1) tmem_ld32(r_col + (u + 1) * 32, ra);
-          else tmem_ld32(r_col + (u + 1) * 32, rb);
+          if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
+          else tmem_ld16(r_col + (u + 1) * 16, rb);
         }
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
+        for (int i = 0; i < 16; i += 2) {
           const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
           const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-          wpk[u * 16 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
+          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
         }
       }
     }
@@ -165,47 +168,57 @@ __device__ __forceinline__ bool softmax_tiles_fast(SoftmaxRow& st, AttnCtl* ctl,
     __syncwarp();
     if (lane == 0) mbar_arrive(&ctl->r_free);
 
-    // ---- phase B: p = 2^(s*c - bound) * weight, 16 columns at a time, loads one unit ahead
-    if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
-      record_status(status, kDevWaitAccFull);
-      return false;
-    }
-    tc_fence_after();
-    uint32_t sa[16], sb[16];
-    tmem_ld16(s_col, sa);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      tc_wait_ld();
-      if (u + 1 < 8) {
-        if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
-        else tmem_ld16(s_col + (u + 1) * 16, sb);
+    for (int x = 0; x < 2; ++x) {
+      if (x >= nh) continue;
+      if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
+        record_status(status, kDevWaitAccFull);
+        return false;
       }
-      uint32_t packed[8];
+      tc_fence_after();
+      // S columns [64*half, +64) of head x; their probabilities (bf16 pairs) overwrite the first
+      // 32 of those columns, always behind this thread's own reads
+      const uint32_t s_col = lane_base + kColS + x * kTile + half * 64;
+      const float neg_b = -bound[x];
+      uint32_t sa[16], sb[16];
+      tmem_ld16(s_col, sa);
 #pragma unroll
-      for (int i = 0; i < 16; i += 2) {
-        const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
-        const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
-        // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
-        // the bf16 products the tensor core will see
-        const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
-                                       wpk[u * 8 + (i >> 1)]);
-        add_bf16x2_to_f32(l0, l1, pp);
-        packed[i >> 1] = pp;
+      for (int u = 0; u < 4; ++u) {
+        tc_wait_ld();
+        if (u + 1 < 4) {
+          if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+          else tmem_ld16(s_col + (u + 1) * 16, sb);
+        }
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 16; i += 2) {
+          const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
+          const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
+          // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
+          // the bf16 products the tensor core will see
+          const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
+                                         wpk[u * 8 + (i >> 1)]);
+          add_bf16x2_to_f32(l[x][0], l[x][1], pp);
+          packed[i >> 1] = pp;
+        }
+        tmem_st8(s_col + u * 8, packed);
       }
-      tmem_st8(s_col + u * 8, packed);
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl->p_full[x]);
     }
-    tc_wait_st();
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->p_full[x]);
   }
-  st.l = l0 + l1;
+  l_out[0] = l[0][0] + l[0][1];
+  l_out[1] = l[1][0] + l[1][1];
   return true;
 }
 
 // Two-pass per-tile loop (see the file header).
+// One warp per (head, 32 rows), all 128 columns.  The barriers count eight arrivals (the
+// column-split layout): a warp arrives `r_arrivals` times on r_free and twice on p_full.
 __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
-                                                    int* status, volatile uint32_t* abort_flag) {
+                                                    int r_arrivals, int* status, volatile uint32_t* abort_flag) {
   const float ninf = -__int_as_float(0x7f800000);
   const float sc = st.sc;
   const uint32_t s_col = st.s_col;
@@ -284,16 +297,17 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
         l1 += p1;
         packed[i >> 1] = pack_bf16x2(p0, p1);
       }
-      tmem_st8(s_col + u * 8, packed);
+      // probabilities of keys 0..63 in columns [0,32), of keys 64..127 in columns [64,96)
+      tmem_st8(s_col + (u & 3) * 8 + (u >> 2) * 64, packed);
     }
     st.l += l0 + l1;
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->r_free);
+    if (lane < r_arrivals) mbar_arrive(&ctl->r_free);
     tc_wait_st();
     tc_fence_before();
     __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+    if (lane < 2) mbar_arrive(&ctl->p_full[x]);
     mw = mw_next;
   }
   return true;
@@ -357,14 +371,14 @@ __global__ void __launch_bounds__(384, 1)
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     mbar_init(&ctl->r_full, 1);
-    mbar_init(&ctl->r_free, 4 * nh);
+    mbar_init(&ctl->r_free, 8);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl->wk_full[s], 1);
       mbar_init(&ctl->wk_empty[s], 1);
       mbar_init(&ctl->v_full[s], 1);
       mbar_init(&ctl->v_empty[s], 1);
       mbar_init(&ctl->s_full[s], 1);
-      mbar_init(&ctl->p_full[s], 4);
+      mbar_init(&ctl->p_full[s], 8);
       mbar_init(&ctl->pv_done[s], 1);
       for (int t = 0; t < 2; ++t) {
         mbar_init(&ctl->k_full[s][t], 1);
@@ -372,6 +386,7 @@ __global__ void __launch_bounds__(384, 1)
       }
     }
     ctl->abort_flag = 0;
+    ctl->cta_exact = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -497,7 +512,7 @@ __global__ void __launch_bounds__(384, 1)
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
-            umma_f16_ts(o_col, s_col + ks * 8, dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
+            umma_f16_ts(o_col, s_col + (ks & 3) * 8 + (ks >> 2) * 64, dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
           umma_commit(&ctl->v_empty[x]);
           umma_commit(&ctl->pv_done[x]);
         }
@@ -518,38 +533,31 @@ __global__ void __launch_bounds__(384, 1)
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    const int x = (warp - 2) >> 2;              // head of the pair this warp group serves
-    if (x < nh) {
-      const int h = h0 + x;
-      const int quarter = warp & 3;
-      const int row = quarter * 32 + lane;
-      const int qrow = qt * kTile + row;
-      const bool row_ok = qrow < p.Tq;
+    const int half = (warp - 2) >> 2;           // one-pass layout: column half; two-pass layout: head of the pair
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int qrow = qt * kTile + row;
+    const bool row_ok = qrow < p.Tq;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
 
-      SoftmaxRow st;
-      st.lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-      st.s_col = st.lane_base + kColS + x * kTile;
-      st.o_col = st.lane_base + kColO + x * kHeadDim;
-      st.mask_tile =
-          reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
-      st.sc = p.scale_log2;
-      st.m_true = st.m_used = -__int_as_float(0x7f800000);
-      st.l = 0.f;
-
-      // Row constants from the indexer's select passes: threshold bits, how many keys equal
-      // to the threshold are selected, how many exist.  The one-pass path is exact when
-      //   - the threshold is positive and every tie is selected (membership = score >= thr),
-      //   - every weight exceeds the 1e-6 clamp on the denominator (the clamp cannot bind),
-      //   - the logits of the row are provably small (|s*sc| <= bound <= kMaxBound).
-      // Any other row sends its warp to the two-pass bitmask path.
-      bool flagged = false;
-      st.thr_ge = __int_as_float(0x7f800000);   // tail rows: nothing selected
-      st.bound = 0.f;
-      if (row_ok) {
-        const int64_t grow = static_cast<int64_t>(b) * p.Tq + qrow;
-        const uint32_t thr_bits = p.st_prefix[grow];
-        st.thr_ge = __uint_as_float(thr_bits);
-        const uint4* qv = reinterpret_cast<const uint4*>(p.q + b * p.qsb + h * p.qsh + qrow * p.qst);
+    // Row constants from the indexer's select passes: threshold bits, how many keys equal
+    // to the threshold are selected, how many exist.  The one-pass path is exact when
+    //   - the threshold is positive and every tie is selected (membership = score >= thr),
+    //   - every weight exceeds the 1e-6 clamp on the denominator (the clamp cannot bind),
+    //   - the logits of the row are provably small (|s*sc| <= bound <= kMaxBound), both heads.
+    // One row that fails sends the whole CTA to the two-pass bitmask path.
+    bool flagged = false;
+    float thr_ge = __int_as_float(0x7f800000);   // tail rows: nothing selected
+    float bound[2] = {0.f, 0.f};
+    if (row_ok) {
+      const int64_t grow = static_cast<int64_t>(b) * p.Tq + qrow;
+      const uint32_t thr_bits = p.st_prefix[grow];
+      thr_ge = __uint_as_float(thr_bits);
+      bool small = true;
+#pragma unroll
+      for (int x = 0; x < 2; ++x) {
+        if (x >= nh) continue;
+        const uint4* qv = reinterpret_cast<const uint4*>(p.q + b * p.qsb + (h0 + x) * p.qsh + qrow * p.qst);
         float q2 = 0.f;
 #pragma unroll
         for (int i = 0; i < kHeadDim / 8; ++i) {
@@ -561,28 +569,58 @@ __global__ void __launch_bounds__(384, 1)
             q2 = fmaf(lo, lo, fmaf(hi, hi, q2));
           }
         }
-        const float k2 = __uint_as_float(p.kmax2[b * p.H + h]);
-        st.bound = sqrtf(q2 * k2) * st.sc * 1.001f + 1e-3f;
-        flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow] && st.thr_ge >= 4e-6f &&
-                    st.bound <= kMaxBound);
+        const float k2 = __uint_as_float(p.kmax2[b * p.H + h0 + x]);
+        bound[x] = sqrtf(q2 * k2) * p.scale_log2 * 1.001f + 1e-3f;
+        small = small && bound[x] <= kMaxBound;
       }
-      const bool exact = __any_sync(0xffffffffu, flagged);
-      bool ok = exact ? softmax_tiles_exact(st, ctl, x, nKT, lane, p.status, abort_flag)
-                      : softmax_tiles_fast(st, ctl, x, nKT, lane, p.status, abort_flag);
+      flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow] && thr_ge >= 4e-6f && small);
+    }
+    if (__any_sync(0xffffffffu, flagged) && lane == 0) atomicOr(&ctl->cta_exact, 1u);
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    const bool exact = *reinterpret_cast<volatile uint32_t*>(&ctl->cta_exact) != 0u;
+
+    const int x = half;                           // head whose output rows this thread writes
+    const int h = h0 + x;
+    const uint32_t o_col = lane_base + kColO + x * kHeadDim;
+    bool ok = true;
+    float inv = 0.f;
+    if (!exact) {
+      float l_part[2];
+      ok = softmax_tiles_split(ctl, lane_base, half, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, p.status,
+                               abort_flag);
+      // The two column halves of a row add their partial sums through the indexer-query tile:
+      // every routing-weight MMA that read it has retired once any warp has left its loop.
+      float* lsum = reinterpret_cast<float*>(smem + kOffWq);      // [2 heads][128 rows][2 halves]
+      lsum[(0 * kTile + row) * 2 + half] = l_part[0];
+      lsum[(1 * kTile + row) * 2 + half] = l_part[1];
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      inv = 1.f / (lsum[(x * kTile + row) * 2] + lsum[(x * kTile + row) * 2 + 1]);   // the clamp cannot bind
+    } else if (x < nh) {
+      SoftmaxRow st;
+      st.lane_base = lane_base;
+      st.s_col = lane_base + kColS + x * kTile;
+      st.o_col = o_col;
+      st.mask_tile =
+          reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
+      st.sc = p.scale_log2;
+      st.m_true = st.m_used = -__int_as_float(0x7f800000);
+      st.l = 0.f;
+      ok = softmax_tiles_exact(st, ctl, x, nKT, lane, 2 / nh, p.status, abort_flag);
+      // the reference's clamp: out = O c / max(l c, 1e-6), c = 2^(m_used - m_true)
+      const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
+      inv = corr / fmaxf(st.l * corr, 1e-6f);
+    }
+    if (x < nh) {
       if (ok && !mbar_wait_bounded(&ctl->pv_done[x], (nKT - 1) & 1, abort_flag)) {
         record_status(p.status, kDevWaitPvDone);
         ok = false;
       }
       if (ok) {
         tc_fence_after();
-        // two-pass path: the reference's clamp, out = O c / max(l c, 1e-6), c = 2^(m_used - m_true);
-        // one-pass path: the clamp cannot bind, out = O / l.
-        const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
-        const float inv = exact ? corr / fmaxf(st.l * corr, 1e-6f) : 1.f / st.l;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           uint32_t o[16];
-          tmem_ld16(st.o_col + c * 16, o);
+          tmem_ld16(o_col + c * 16, o);
           tc_wait_ld();
           if (!row_ok) continue;
           if (p.o_dtype == SWV_F32) {
