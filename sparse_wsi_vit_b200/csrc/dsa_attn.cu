@@ -106,13 +106,15 @@ struct ProgressClock {
 };
 
 // ------------------------------------------------------------ softmax helpers
-// r >= thr ? v : 0     (one compare + one select)
-__device__ __forceinline__ float keep_where_ge(float v, float r, float thr) {
-  float out;
-  asm("{\n\t.reg .pred p;\n\tsetp.ge.f32 p, %2, %3;\n\tselp.f32 %0, %1, 0f00000000, p;\n\t}"
-      : "=f"(out)
-      : "f"(v), "f"(r), "f"(thr));
-  return out;
+// r >= thr ? r : 0 on the FMA pipe (compare and select run at half rate on the ALU pipe, which
+// bounds the weight conversion).  With t = the float just below thr, r >= thr <=> r - t > 0, and
+// the smallest positive r - t (one ulp of a threshold >= 4e-6) times 2^60 is far above 1:
+//   step = saturate(r * 2^60 - t * 2^60)  is exactly 0 or 1;   weight = r * step.
+// `neg_c` = -t * 2^60 (-inf for rows that select nothing).
+__device__ __forceinline__ float keep_where_ge(float r, float neg_c) {
+  float step;
+  asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(step) : "f"(r), "f"(neg_c));   // 0x5D800000 = 2^60
+  return r * step;
 }
 
 struct SoftmaxRow {
@@ -138,6 +140,8 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
                                                     float (&l_out)[2], int* status,
                                                     volatile uint32_t* abort_flag) {
   const uint32_t r_col = lane_base + kColR + half * 64;
+  // -(float just below the threshold) * 2^60; a +inf threshold (tail rows) gives -inf: nothing selected
+  const float neg_c = -__uint_as_float(__float_as_uint(thr) - 1u) * 0x1p60f;
   float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   for (int j = 0; j < nKT; ++j) {
     if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
@@ -160,7 +164,7 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
         for (int i = 0; i < 16; i += 2) {
           const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
           const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, r0, thr), keep_where_ge(r1, r1, thr));
+          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, neg_c), keep_where_ge(r1, neg_c));
         }
       }
     }
