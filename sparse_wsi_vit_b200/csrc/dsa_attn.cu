@@ -135,82 +135,103 @@ struct SoftmaxRow {
 // then, per head, p = 2^(s*c - bound) * weight goes to TMEM as bf16.  With eight warps on one
 // head's tile at a time, a head's S -> P -> PV -> next S chain is short enough to hide behind
 // the other head's pass.
+// Routing weights of tile j for the warp's 64 columns: (score >= thr ? score : 0) as bf16 pairs; R is
+// released as soon as it has been read.
+__device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, int j, int lane, float neg_c,
+                                                uint32_t (&w)[32], int* status, volatile uint32_t* abort_flag) {
+  if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
+    record_status(status, kDevWaitAccFull);
+    return false;
+  }
+  tc_fence_after();
+  uint32_t ra[16], rb[16];
+  tmem_ld16(r_col, ra);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    tc_wait_ld();
+    if (u + 1 < 4) {
+      if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
+      else tmem_ld16(r_col + (u + 1) * 16, rb);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
+      const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
+      w[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, neg_c), keep_where_ge(r1, neg_c));
+    }
+  }
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&ctl->r_free);
+  return true;
+}
+
+// One head's pass over the warp's 64 columns of tile j: p = 2^(s*c - bound) * weight -> TMEM as bf16
+// pairs over the first 32 of those columns, always behind this thread's own reads.
+__device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x, int j, int lane, float sc,
+                                             float neg_b, const uint32_t (&wpk)[32], float& l0, float& l1,
+                                             int* status, volatile uint32_t* abort_flag) {
+  if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
+    record_status(status, kDevWaitAccFull);
+    return false;
+  }
+  tc_fence_after();
+  uint32_t sa[16], sb[16];
+  tmem_ld16(s_col, sa);
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    tc_wait_ld();
+    if (u + 1 < 4) {
+      if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+      else tmem_ld16(s_col + (u + 1) * 16, sb);
+    }
+    uint32_t packed[8];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
+      const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
+      // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
+      // the bf16 products the tensor core will see
+      const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
+                                     wpk[u * 8 + (i >> 1)]);
+      add_bf16x2_to_f32(l0, l1, pp);
+      packed[i >> 1] = pp;
+    }
+    tmem_st8(s_col + u * 8, packed);
+  }
+  tc_wait_st();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+  return true;
+}
+
+// The two warps of a scheduler (column halves 0 and 1 of the same rows) run the tile in different
+// orders, so that one converts weights (FMA pipe) while the other computes exponentials (exp unit):
+//   half 0:  weights(j)  pass0(j)  pass1(j)
+//   half 1:  pass0(j)  weights(j+1)  pass1(j)
 __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int half, int nh, int nKT,
                                                     int lane, float thr, float sc, const float (&bound)[2],
                                                     float (&l_out)[2], int* status,
                                                     volatile uint32_t* abort_flag) {
   const uint32_t r_col = lane_base + kColR + half * 64;
+  const uint32_t s_col0 = lane_base + kColS + half * 64;      // S columns [64*half, +64) of head 0
   // -(float just below the threshold) * 2^60; a +inf threshold (tail rows) gives -inf: nothing selected
   const float neg_c = -__uint_as_float(__float_as_uint(thr) - 1u) * 0x1p60f;
   float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  const bool skew = half == 1;
+  uint32_t wa[32], wb[32];
+  if (skew && !convert_weights(ctl, r_col, 0, lane, neg_c, wa, status, abort_flag)) return false;
   for (int j = 0; j < nKT; ++j) {
-    if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
-      record_status(status, kDevWaitAccFull);
+    if (!skew && !convert_weights(ctl, r_col, j, lane, neg_c, wa, status, abort_flag)) return false;
+    if (!softmax_pass(ctl, s_col0, 0, j, lane, sc, -bound[0], wa, l[0][0], l[0][1], status, abort_flag)) return false;
+    if (skew && j + 1 < nKT && !convert_weights(ctl, r_col, j + 1, lane, neg_c, wb, status, abort_flag)) return false;
+    if (nh == 2 &&
+        !softmax_pass(ctl, s_col0 + kTile, 1, j, lane, sc, -bound[1], wa, l[1][0], l[1][1], status, abort_flag))
       return false;
-    }
-    tc_fence_after();
-    uint32_t wpk[32];
-    {
-      uint32_t ra[16], rb[16];
-      tmem_ld16(r_col, ra);
+    if (skew) {
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        tc_wait_ld();
-        if (u + 1 < 4) {
-          if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
-          else tmem_ld16(r_col + (u + 1) * 16, rb);
-        }
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
-          const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-          wpk[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, neg_c), keep_where_ge(r1, neg_c));
-        }
-      }
-    }
-    tc_fence_before();
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&ctl->r_free);
-
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-      if (x >= nh) continue;
-      if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
-        record_status(status, kDevWaitAccFull);
-        return false;
-      }
-      tc_fence_after();
-      // S columns [64*half, +64) of head x; their probabilities (bf16 pairs) overwrite the first
-      // 32 of those columns, always behind this thread's own reads
-      const uint32_t s_col = lane_base + kColS + x * kTile + half * 64;
-      const float neg_b = -bound[x];
-      uint32_t sa[16], sb[16];
-      tmem_ld16(s_col, sa);
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        tc_wait_ld();
-        if (u + 1 < 4) {
-          if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
-          else tmem_ld16(s_col + (u + 1) * 16, sb);
-        }
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
-          const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
-          // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
-          // the bf16 products the tensor core will see
-          const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
-                                         wpk[u * 8 + (i >> 1)]);
-          add_bf16x2_to_f32(l[x][0], l[x][1], pp);
-          packed[i >> 1] = pp;
-        }
-        tmem_st8(s_col + u * 8, packed);
-      }
-      tc_wait_st();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+      for (int i = 0; i < 32; ++i) wa[i] = wb[i];
     }
   }
   l_out[0] = l[0][0] + l[0][1];
@@ -218,7 +239,6 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   return true;
 }
 
-// Two-pass per-tile loop (see the file header).
 // One warp per (head, 32 rows), all 128 columns.  The barriers count eight arrivals (the
 // column-split layout): a warp arrives `r_arrivals` times on r_free and twice on p_full.
 __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
