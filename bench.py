@@ -1,6 +1,7 @@
 """Benchmark of the DSA sparse-attention forward (indexer + top-k + attention).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens T]
+    python bench.py --workload {block_sparse,nsa,encoder,static}     # other configurations, 1 GPU
 
 Workload ("dsa_fwd_64k"): one DSA attention layer, 65536 tokens, 8 heads x 64,
 4 x 64 indexer, top-2048, bf16, batch 1, non-causal; seeded synthetic inputs with
@@ -31,6 +32,10 @@ if ROOT not in sys.path:
 
 H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
 METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
+# kernels of this library launched per forward on one GPU: 2 head collapses, 6 radix-select tile
+# passes (4 of them return at once unless a query tile asked for the fallback), emit, valid fill,
+# key-norm maximum, attention
+KERNELS_PER_STEP = 12
 
 # DRAM bytes (read + write) of one dsa_attn_masked_kernel launch on the 65536-token workload: the ncu
 # capture at 16384 tokens (profiles/dsa_attn_masked_kernel_16k.md: 59.2 MB read + 4.3 MB written)
@@ -320,7 +325,7 @@ def run_ours(args):
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned) * world,
                     "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world},
-            "gpu_launches": args.steps * 9 * world,
+            "gpu_launches": args.steps * KERNELS_PER_STEP * world,
             "clocks": clocks,
         }
         if world == 1:
@@ -336,7 +341,10 @@ def run_ours(args):
                 "executed_flops": executed, "executed_tflops": executed / (attn_ms * 1e-3) / 1e12,
                 "executed_frac": executed / (attn_ms * 1e-3) / 1e12 / tf_peak,
                 "other_kernels_ms": ms - attn_ms,
+                # what actually bounds this kernel: one exp per (query, key, head) on the 16 exp lanes per SM
+                "exp_unit_floor_ms": T * float(T) * H / (16.0 * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3,
             }
+            line["roofline"]["exp_unit_frac"] = line["roofline"]["exp_unit_floor_ms"] / attn_ms
             line["cpu_baseline"] = cpu_baseline(T, budget_s=15.0)
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -350,7 +358,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "block_sparse", "nsa", "encoder", "static"])
     args = ap.parse_args()
+    if args.workload != "dsa_fwd":
+        from sparse_wsi_vit_b200.benchmarks import WORKLOADS
+        WORKLOADS[args.workload]()
+        return
     if args.impl == "reference":
         run_reference(args)
     else:

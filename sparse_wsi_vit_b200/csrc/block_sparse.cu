@@ -13,10 +13,15 @@
 // One CTA owns (batch, head, one query block).  The score tile is M = 128 query rows by
 // N = BS keys (BS = 64: the 64 rows behind the block are computed and dropped).
 //   warp 0     : TMA producer (Q once; K, V blocks of the list through 2-stage rings)
-//   warp 1     : UMMA issuer: S = Q K^T, then O += P V with P read from TMEM; the next S is
-//                issued right behind the PV that consumes the P it overwrites
-//   warps 2..5 : online softmax, one thread per query row, lazy rescale of O (in TMEM)
-// TMEM: S fp32 [0,128) with P (bf16x2) overwriting its first columns | O fp32 [128,128+D).
+//   warp 1     : UMMA issuer: S(j) = Q K(j)^T into one of TWO score buffers, O += P(j) V(j) with
+//                P read from TMEM; S(j+2) is issued as soon as the softmax has read S(j), so the
+//                tensor pipe works one tile ahead of the softmax
+//   warps 2..5 : online softmax, one thread per query row, ONE pass per tile: exponentials are
+//                taken against the current stabiliser while the tile's maximum is tracked; only
+//                if some row's maximum exceeds its stabiliser by more than 2^8 is the stabiliser
+//                raised, O (in TMEM) rescaled and the pass repeated (S stays intact: P has its
+//                own columns)
+// TMEM: S fp32 [0,BS) and [BS,2BS) | P (bf16x2) [2BS, 2.5BS) and [2.5BS, 3BS) | O fp32 [3BS, 3BS+D).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -41,7 +46,7 @@ struct BsaParams {
 struct BsaCtl {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
-  uint64_t s_full, p_full, pv_done;
+  uint64_t s_full[2], p_full[2], pv_done[2];   // per score / probability buffer (tile parity)
   uint32_t tmem_base;
   uint32_t abort_flag;
 };
@@ -53,12 +58,59 @@ struct BsaCfg {
   static constexpr int kOffK = kQBytes;
   static constexpr int kOffV = kOffK + 2 * kKVBytes;
   static constexpr int kOffCtl = kOffV + 2 * kKVBytes;
+  static constexpr uint32_t kColP = 2 * BS;          // two probability buffers of BS/2 columns
+  static constexpr uint32_t kColO = 3 * BS;
+  static constexpr uint32_t kTmemCols = (3 * BS + D <= 256) ? 256 : 512;
   // at least 80 KiB so that no more than two CTAs (2 x 256 TMEM columns) share an SM
   static constexpr size_t kSmemNeed = 1024 + kOffCtl + sizeof(BsaCtl) + 64;
   static constexpr size_t kSmem = kSmemNeed > 80 * 1024 ? kSmemNeed : 80 * 1024;
-  static constexpr uint32_t kColO = 128;
-  static constexpr uint32_t kTmemCols = 256;
 };
+
+// One softmax pass of a thread over its row of the score tile: p = 2^(s*sc + neg_m) for the kept
+// columns, written as bf16 pairs; returns the row's maximum raw score over the kept columns and
+// the sum of the probabilities.  Loads run one 16-column unit ahead.
+template <int BS, bool MASKED>
+__device__ __forceinline__ void bsa_pass(uint32_t s_col, uint32_t p_col, const uint32_t (&keep)[BS / 32], float sc,
+                                         float neg_m, float& mt_out, float& l_out) {
+  const float ninf = -__int_as_float(0x7f800000);
+  float mt0 = ninf, mt1 = ninf, l0 = 0.f, l1 = 0.f;
+  uint32_t sa[16], sb[16];
+  tmem_ld16(s_col, sa);
+#pragma unroll
+  for (int u = 0; u < BS / 16; ++u) {
+    tc_wait_ld();
+    if (u + 1 < BS / 16) {
+      if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+      else tmem_ld16(s_col + (u + 1) * 16, sb);
+    }
+    const uint32_t w = MASKED ? keep[u >> 1] >> ((u & 1) * 16) : 0xFFFFu;
+    uint32_t packed[8];
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
+      const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
+      float p0 = ex2_approx(fmaf(s0, sc, neg_m));
+      float p1 = ex2_approx(fmaf(s1, sc, neg_m));
+      if (MASKED) {
+        const bool k0 = (w & (1u << i)) != 0u, k1 = (w & (2u << i)) != 0u;
+        mt0 = fmaxf(mt0, k0 ? s0 : ninf);
+        mt1 = fmaxf(mt1, k1 ? s1 : ninf);
+        p0 = k0 ? p0 : 0.f;
+        p1 = k1 ? p1 : 0.f;
+      } else {
+        mt0 = fmaxf(mt0, s0);
+        mt1 = fmaxf(mt1, s1);
+      }
+      l0 += p0;
+      l1 += p1;
+      packed[i >> 1] = pack_bf16x2(p0, p1);
+    }
+    tmem_st8(p_col + u * 8, packed);
+  }
+  mt_out = fmaxf(mt0, mt1);
+  l_out = l0 + l1;
+}
+
 
 // Token-level pattern of the reference's static attention (mode 1).
 // With window 0 a patch sees the CLS keys only, not itself (static_sparse_attention.py:92-95).
@@ -98,9 +150,11 @@ __global__ void __launch_bounds__(192, 1)
       mbar_init(&ctl->v_full[s], 1);
       mbar_init(&ctl->v_empty[s], 1);
     }
-    mbar_init(&ctl->s_full, 1);
-    mbar_init(&ctl->p_full, 4);
-    mbar_init(&ctl->pv_done, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&ctl->s_full[s], 1);
+      mbar_init(&ctl->p_full[s], 4);
+      mbar_init(&ctl->pv_done[s], 1);
+    }
     ctl->abort_flag = 0;
     fence_barrier_init();
   }
@@ -172,21 +226,22 @@ __global__ void __launch_bounds__(192, 1)
           // 64-element halves of the head dimension are separate swizzled tiles
           const uint64_t offa = (ks >> 2) * (kTile * 128 / 16) + (ks & 3) * 2;
           const uint64_t offb = (ks >> 2) * (BS * 128 / 16) + (ks & 3) * 2;
-          umma_f16_ss(tmem_base, da + offa, db + offb, kIdescQK, ks > 0);
+          umma_f16_ss(tmem_base + s * BS, da + offa, db + offb, kIdescQK, ks > 0);
         }
         umma_commit(&ctl->k_empty[s]);
-        umma_commit(&ctl->s_full);
+        umma_commit(&ctl->s_full[s]);
         return true;
       };
 
       if (ok) ok = issue_qk(0);
+      if (ok && nblk > 1) ok = issue_qk(1);
       for (int j = 0; ok && j < nblk; ++j) {
         const int s = j & 1;
         if (!mbar_wait_bounded(&ctl->v_full[s], (j >> 1) & 1, abort_flag)) {
           record_status(p.status, kDevWaitTmaFull);
           break;
         }
-        if (!mbar_wait_bounded(&ctl->p_full, j & 1, abort_flag)) {
+        if (!mbar_wait_bounded(&ctl->p_full[s], (j >> 1) & 1, abort_flag)) {
           record_status(p.status, kDevWaitPReady);
           break;
         }
@@ -195,11 +250,12 @@ __global__ void __launch_bounds__(192, 1)
         const uint64_t dv = smem_desc_sw128(v_addr + s * Cfg::kKVBytes, BS * 128);
 #pragma unroll
         for (int ks = 0; ks < BS / 16; ++ks)
-          umma_f16_ts(tmem_base + Cfg::kColO, tmem_base + ks * 8, dv + ks * 128, kIdescPV, (j > 0 || ks > 0));
+          umma_f16_ts(tmem_base + Cfg::kColO, tmem_base + Cfg::kColP + s * (BS / 2) + ks * 8, dv + ks * 128, kIdescPV,
+                      (j > 0 || ks > 0));
         umma_commit(&ctl->v_empty[s]);
-        umma_commit(&ctl->pv_done);
-        // the next S overwrites this P: issued behind the PV that reads it (in-order pipe)
-        if (j + 1 < nblk) ok = issue_qk(j + 1);
+        umma_commit(&ctl->pv_done[s]);
+        // the softmax has read S(j) (it delivered P(j)): its buffer takes S(j+2)
+        if (j + 2 < nblk) ok = issue_qk(j + 2);
       }
     }
   } else {
@@ -219,100 +275,78 @@ __global__ void __launch_bounds__(192, 1)
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
       const int key0 = p.col_idx[list0 + j] * BS;
-      if (!mbar_wait_bounded(&ctl->s_full, j & 1, abort_flag)) {
+      const int sb = j & 1;
+      const uint32_t s_col = lane_base + sb * BS;
+      const uint32_t p_col = lane_base + Cfg::kColP + sb * (BS / 2);
+      // S(j) computed; P's buffer no longer read by PV(j-2)
+      if (!mbar_wait_bounded(&ctl->s_full[sb], (j >> 1) & 1, abort_flag) ||
+          (j >= 2 && !mbar_wait_bounded(&ctl->pv_done[sb], ((j >> 1) & 1) ^ 1, abort_flag))) {
         record_status(p.status, kDevWaitAccFull);
         ok = false;
         break;
       }
       tc_fence_after();
-      // which columns of this block the row attends (bit i of word c*16.. = column)
+      // which columns of this block the row attends (bit i of word c = column 32c + i)
+      const bool masked = p.mode != 0 || key0 + BS > p.Tk;
       uint32_t keep[BS / 32];
 #pragma unroll
       for (int c = 0; c < BS / 32; ++c) {
-        uint32_t w = 0;
+        uint32_t w = 0xFFFFFFFFu;
         const int base = key0 + c * 32;
-        if (p.mode == 0) {
-          const int nv = p.Tk - base;
-          w = nv >= 32 ? 0xFFFFFFFFu : (nv <= 0 ? 0u : ((1u << nv) - 1u));
-        } else {
+        if (p.mode != 0) {
+          w = 0;
 #pragma unroll 4
           for (int i = 0; i < 32; ++i) {
             const int kj = base + i;
             if (kj < p.Tk && static_pattern(qrow, kj, p.num_cls, reach, dil)) w |= 1u << i;
           }
+        } else if (masked) {
+          const int nv = p.Tk - base;
+          w = nv >= 32 ? 0xFFFFFFFFu : (nv <= 0 ? 0u : ((1u << nv) - 1u));
         }
         keep[c] = w;
       }
 
-      // pass 1: row maximum over the attended columns
-      float mt = ninf;
-#pragma unroll
-      for (int u = 0; u < BS / 16; ++u) {
-        uint32_t s[16];
-        tmem_ld16(lane_base + u * 16, s);
-        tc_wait_ld();
-        const uint32_t w = keep[u >> 1] >> ((u & 1) * 16);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) mt = fmaxf(mt, (w & (1u << i)) ? __uint_as_float(s[i]) : ninf);
-      }
+      // rows that have attended nothing yet have m_used = -inf; their stabiliser is 0 for now
+      float mt, lt;
+      if (masked) bsa_pass<BS, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+      else bsa_pass<BS, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
       const float m_new = fmaxf(m_used, mt * sc);
-      const bool raise = __any_sync(0xffffffffu, m_new > m_used + kStep);
-      float factor = 1.f;
-      if (raise) {
-        factor = (m_new == m_used) ? 1.f : ex2_approx(m_used - m_new);
-        m_used = m_new;
+      if (__any_sync(0xffffffffu, m_new > m_used + kStep)) {
+        // raise the stabiliser, rescale what has been accumulated, repeat the pass
+        const float factor = (m_new == m_used) ? 1.f : ex2_approx(m_used - m_new);
         l *= factor;
-      }
-      if (raise && j > 0) {
-        if (!mbar_wait_bounded(&ctl->pv_done, (j - 1) & 1, abort_flag)) {
-          record_status(p.status, kDevWaitPvDone);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
+        m_used = m_new;
+        if (j > 0) {
+          // O of the tiles before this one is complete once PV(j-1) retired
+          if (!mbar_wait_bounded(&ctl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) {
+            record_status(p.status, kDevWaitPvDone);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
 #pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
-          uint32_t o[16];
-          tmem_ld16(o_col + c * 16, o);
-          tc_wait_ld();
+          for (int c = 0; c < D / 16; ++c) {
+            uint32_t o[16];
+            tmem_ld16(o_col + c * 16, o);
+            tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-          tmem_st16(o_col + c * 16, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st16(o_col + c * 16, o);
+          }
+          tc_wait_st();
         }
-        tc_wait_st();
+        if (masked) bsa_pass<BS, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+        else bsa_pass<BS, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
       }
-      // rows that have attended nothing yet keep m_used = -inf; their probabilities are 0
-      const float neg_m = (m_used == ninf) ? 0.f : -m_used;
-
-      // pass 2: probabilities -> TMEM (bf16), overwriting the consumed part of S
-      float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-      for (int u = 0; u < BS / 16; ++u) {
-        uint32_t s[16];
-        tmem_ld16(lane_base + u * 16, s);
-        tc_wait_ld();
-        const uint32_t w = keep[u >> 1] >> ((u & 1) * 16);
-        uint32_t packed[8];
-#pragma unroll
-        for (int i = 0; i < 16; i += 2) {
-          float p0 = ex2_approx(fmaf(__uint_as_float(s[i]), sc, neg_m));
-          float p1 = ex2_approx(fmaf(__uint_as_float(s[i + 1]), sc, neg_m));
-          p0 = (w & (1u << i)) ? p0 : 0.f;
-          p1 = (w & (2u << i)) ? p1 : 0.f;
-          l0 += p0;
-          l1 += p1;
-          packed[i >> 1] = pack_bf16x2(p0, p1);
-        }
-        tmem_st8(lane_base + u * 8, packed);
-      }
-      l += l0 + l1;
+      l += lt;
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->p_full);
+      if (lane == 0) mbar_arrive(&ctl->p_full[sb]);
     }
 
-    if (nblk > 0 && ok && !mbar_wait_bounded(&ctl->pv_done, (nblk - 1) & 1, abort_flag)) {
+    if (nblk > 0 && ok && !mbar_wait_bounded(&ctl->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag)) {
       record_status(p.status, kDevWaitPvDone);
       ok = false;
     }
