@@ -177,6 +177,41 @@ int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const v
 int swv_pool_tokens(const void* x, const int64_t x_strides[4], void* y, int B, int H, int T, int D, int window,
                     int stride, void* stream);
 
+/* NSA-style attention, selection step (no counterpart in the reference, which only names NSA as an
+ * intent, scripts/virchow_preprocess.py:44-53).  For every (batch, kv head g, query t) the
+ * importance of selection block s is the sum, over the Hq/Hkv query heads of group g and over the
+ * compressed tokens c with (c * cmp_stride) / sel_block == s, of
+ *   exp(q_h[t] . kc_g[c] / sqrt(D) - lse[b,h,t])
+ * where lse is the log-sum-exp row statistic of the compressed branch
+ * (swv_block_sparse_attn_fwd's `lse` output).  The n_sel most important of the
+ * ceil(Tk / sel_block) blocks are written to `blocks` (B,Hkv,Tq,min(n_sel, n_blocks)) int32 in
+ * ascending order; ties go to the lower block index.
+ *   q (B,Hq,Tq,D), kc (B,Hkv,nC,D) bf16, unit inner stride, 16-byte aligned rows; D = 64 or 128;
+ *   sel_block / cmp_stride in {1,2,4,8}; Hq / Hkv <= 16.
+ *   importance: caller-owned scratch of swv_nsa_importance_bytes() bytes (the block scores, fp32).
+ */
+int swv_nsa_importance_bytes(int B, int Hkv, int Tq, int nC, int cmp_stride, int sel_block, size_t* bytes);
+int swv_nsa_select_blocks_fwd(const void* q, const int64_t q_strides[4], const void* kc, const int64_t kc_strides[4],
+                              const float* lse, int B, int Hq, int Hkv, int Tq, int Tk, int nC, int D,
+                              int cmp_stride, int sel_block, int n_sel, float* importance, size_t importance_bytes,
+                              int32_t* blocks, int* status, void* stream);
+
+/* NSA-style attention, selected branch: plain softmax attention of every query head over the keys
+ * of the blocks selected for its kv group, o (B,Hq,Tq,D) fp32 contiguous.  One pass reads every
+ * selected key / value row once for the whole group.  q, k, v bf16 as above; sel_block a multiple
+ * of 32; Hq / Hkv <= 8; `blocks` (B,Hkv,Tq,n_sel) int32, block ids < ceil(Tk / sel_block).
+ */
+int swv_nsa_selected_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                              const void* v, const int64_t v_strides[4], const int32_t* blocks, int B, int Hq,
+                              int Hkv, int Tq, int Tk, int D, int sel_block, int n_sel, float* o, void* stream);
+
+/* NSA-style attention, gate: out[b,h,t,:] = sum_j sigmoid(gate[b,t,h,j]) * o_j[b,h,t,:] for the three
+ * branches j = compressed, selected, window; branches fp32 contiguous (B,Hq,T,D), gate fp32
+ * contiguous (B,T,Hq,3), out contiguous in `out_dtype`.
+ */
+int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
+                        int out_dtype, int B, int Hq, int T, int D, void* stream);
+
 /* 2-D rotary embedding on per-token (y, x) coordinates.
  * Replaces VisionRotaryEmbedding.forward, dynamic branch
  * (src/sparse_wsi_vit/models/vit_5/rope.py:72-97, rotate_half :33-37), as applied to q and k in

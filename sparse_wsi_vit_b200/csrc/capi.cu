@@ -32,6 +32,16 @@ int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, in
                      cudaStream_t st);
 int rope2d_impl(const void* x, const int64_t* xs, void* y, const int64_t* ys, int dtype, const float* coords,
                 int64_t L, int H, int hd, float coord_high, float theta, int skip, cudaStream_t st);
+int nsa_importance_bytes_impl(int B, int Hkv, int Tq, int nC, int cmp_stride, int sel_block, size_t* bytes);
+int nsa_select_blocks_impl(const void* q, const int64_t* qs, const void* kc, const int64_t* kcs, const float* lse,
+                           int B, int Hq, int Hkv, int Tq, int Tk, int nC, int D, int cmp_stride, int sel_block,
+                           int n_sel, float* importance, size_t importance_bytes, int32_t* blocks, int* status,
+                           cudaStream_t st);
+int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                           const int64_t* vs, const int32_t* blocks, int B, int Hq, int Hkv, int Tq, int Tk, int D,
+                           int sel_block, int n_sel, float* o, cudaStream_t st);
+int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
+                     int out_dtype, int B, int Hq, int T, int D, cudaStream_t st);
 }  // namespace swv
 
 extern "C" {
@@ -127,6 +137,32 @@ int swv_rope2d_apply(const void* x, const int64_t x_strides[3], void* y, const i
                      int skip_tokens, void* stream) {
   return swv::rope2d_impl(x, x_strides, y, y_strides, dtype, coords, L, H, head_dim, coord_high, theta, skip_tokens,
                           static_cast<cudaStream_t>(stream));
+}
+
+int swv_nsa_importance_bytes(int B, int Hkv, int Tq, int nC, int cmp_stride, int sel_block, size_t* bytes) {
+  return swv::nsa_importance_bytes_impl(B, Hkv, Tq, nC, cmp_stride, sel_block, bytes);
+}
+
+int swv_nsa_select_blocks_fwd(const void* q, const int64_t q_strides[4], const void* kc, const int64_t kc_strides[4],
+                              const float* lse, int B, int Hq, int Hkv, int Tq, int Tk, int nC, int D,
+                              int cmp_stride, int sel_block, int n_sel, float* importance, size_t importance_bytes,
+                              int32_t* blocks, int* status, void* stream) {
+  return swv::nsa_select_blocks_impl(q, q_strides, kc, kc_strides, lse, B, Hq, Hkv, Tq, Tk, nC, D, cmp_stride,
+                                     sel_block, n_sel, importance, importance_bytes, blocks, status,
+                                     static_cast<cudaStream_t>(stream));
+}
+
+int swv_nsa_selected_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                              const void* v, const int64_t v_strides[4], const int32_t* blocks, int B, int Hq,
+                              int Hkv, int Tq, int Tk, int D, int sel_block, int n_sel, float* o, void* stream) {
+  return swv::nsa_selected_attn_impl(q, q_strides, k, k_strides, v, v_strides, blocks, B, Hq, Hkv, Tq, Tk, D,
+                                     sel_block, n_sel, o, static_cast<cudaStream_t>(stream));
+}
+
+int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
+                        int out_dtype, int B, int Hq, int T, int D, void* stream) {
+  return swv::nsa_combine_impl(o_cmp, o_sel, o_win, gate, out, out_dtype, B, Hq, T, D,
+                               static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -1,0 +1,565 @@
+// NSA-style attention forward for sm_100a: block importance, per-query block selection, attention
+// over the selected blocks for a whole grouped-query group, and the gated sum of the branches.
+//
+// The reference has no NSA code (it only names the idea, scripts/virchow_preprocess.py:44-53); the
+// semantics are this library's own:
+//   importance[b, g, t, s] = sum over the G query heads h of kv group g and over the compressed
+//                            tokens c whose first key lies in selection block s of
+//                            exp(q_h[t] . kc_g[c] / sqrt(D) - lse_h[t])
+//   (lse = log-sum-exp of the compressed branch), the `n_sel` largest blocks per (b, g, t) are
+//   selected, ties to the lower block index, reported in ascending order.
+// Kernels:
+//   nsa_importance_kernel : per CTA 128 queries of one kv group; for every tile of 128 compressed
+//                           keys and every head of the group S = Q_h Kc^T on the tensor cores
+//                           (TMA rings -> tcgen05 -> two TMEM accumulators), eight epilogue warps
+//                           turn scores into probabilities and add them up per selection block.
+//   nsa_select_kernel     : one warp per (b, g, t): iterative arg-max over the importance row.
+//   nsa_selected_attn_kernel : one warp per (b, g, t), all G heads at once, CUDA-core fp32: every
+//                           selected key / value row is read once for the whole group.
+//   nsa_combine_kernel    : out = sum_b sigmoid(gate_b) * O_b.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace swv {
+
+// ---------------------------------------------------------------- importance
+struct NsaImpParams {
+  int B, Hq, Hkv, G, Tq, nC, nQT, nCT, n_pad;
+  const float* lse;     // (B, Hq, Tq) natural log
+  float* imp;           // (B, Hkv, Tq, n_pad)
+  float scale_log2;
+  int* status;
+};
+
+struct NsaImpCtl {
+  uint64_t q_full[2], q_empty[2], k_full[2], k_empty[2], acc_full[2], acc_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+};
+
+constexpr int kNsaMaxGroup = 16;
+
+template <int D>
+struct NsaImpCfg {
+  static constexpr int kTileBytes = kTile * D * 2;
+  static constexpr int kOffK = 2 * kTileBytes;
+  static constexpr int kOffLse = 4 * kTileBytes;
+  static constexpr int kOffCtl = kOffLse + kNsaMaxGroup * kTile * 4;
+  static constexpr size_t kSmem = 1024 + kOffCtl + sizeof(NsaImpCtl) + 64;
+};
+
+// R = compressed tokens per selection block (selection block size / compression stride).
+template <int D, int R>
+__global__ void __launch_bounds__(320, 1)
+    nsa_importance_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                          const NsaImpParams p) {
+  using Cfg = NsaImpCfg<D>;
+  constexpr uint32_t kIdesc = make_idesc(/*bf16*/ 1, kTile, kTile, 0, 0);
+  constexpr int kAcc = 64 / R;                       // selection blocks per warp and key tile
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* lse_sm = reinterpret_cast<float*>(smem + Cfg::kOffLse);
+  NsaImpCtl* ctl = reinterpret_cast<NsaImpCtl*>(smem + Cfg::kOffCtl);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int qt = blockIdx.x % p.nQT;
+  const int g = (blockIdx.x / p.nQT) % p.Hkv;
+  const int b = blockIdx.x / (p.nQT * p.Hkv);
+  const int G = p.G;
+  const int nIt = p.nCT * G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&ctl->q_full[s], 1);
+      mbar_init(&ctl->q_empty[s], 1);
+      mbar_init(&ctl->k_full[s], 1);
+      mbar_init(&ctl->k_empty[s], 1);
+      mbar_init(&ctl->acc_full[s], 1);
+      mbar_init(&ctl->acc_empty[s], 8);
+    }
+    ctl->abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(&ctl->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile uint32_t* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      for (int it = 0; it < nIt; ++it) {
+        const int jt = it / G, hh = it - jt * G, s = it & 1;
+        if (!mbar_wait_bounded(&ctl->q_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          record_status(p.status, kDevWaitStageEmpty);
+          break;
+        }
+        mbar_expect_tx(&ctl->q_full[s], Cfg::kTileBytes);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + s * Cfg::kTileBytes + c * (kTile * 128), &tm_q, &ctl->q_full[s], c * 64, qt * kTile,
+                      g * G + hh, b);
+        if (hh == 0) {
+          const int ks = jt & 1;
+          if (!mbar_wait_bounded(&ctl->k_empty[ks], ((jt >> 1) & 1) ^ 1, abort_flag)) {
+            record_status(p.status, kDevWaitStageEmpty);
+            break;
+          }
+          mbar_expect_tx(&ctl->k_full[ks], Cfg::kTileBytes);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_4d(smem + Cfg::kOffK + ks * Cfg::kTileBytes + c * (kTile * 128), &tm_k, &ctl->k_full[ks], c * 64,
+                        jt * kTile, g, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      const uint32_t q_addr = smem_u32(smem);
+      const uint32_t k_addr = smem_u32(smem + Cfg::kOffK);
+      for (int it = 0; it < nIt; ++it) {
+        const int jt = it / G, hh = it - jt * G, s = it & 1, ks = jt & 1;
+        if (!mbar_wait_bounded(&ctl->q_full[s], (it >> 1) & 1, abort_flag) ||
+            (hh == 0 && !mbar_wait_bounded(&ctl->k_full[ks], (jt >> 1) & 1, abort_flag))) {
+          record_status(p.status, kDevWaitTmaFull);
+          break;
+        }
+        if (!mbar_wait_bounded(&ctl->acc_empty[s], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccEmpty);
+          break;
+        }
+        tc_fence_after();
+        const uint64_t da = smem_desc_sw128(q_addr + s * Cfg::kTileBytes);
+        const uint64_t db = smem_desc_sw128(k_addr + ks * Cfg::kTileBytes);
+#pragma unroll
+        for (int k16 = 0; k16 < D / 16; ++k16) {
+          // 64-element halves of the head dimension are separate swizzled tiles
+          const uint64_t off = (k16 >> 2) * (kTile * 128 / 16) + (k16 & 3) * 2;
+          umma_f16_ss(tmem_base + s * kTile, da + off, db + off, kIdesc, k16 > 0);
+        }
+        umma_commit(&ctl->q_empty[s]);
+        if (hh == G - 1) umma_commit(&ctl->k_empty[ks]);
+        umma_commit(&ctl->acc_full[s]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int ew = warp - 2;
+    const int quarter = warp & 3;
+    const int half = ew >> 2;
+    const int row = quarter * 32 + lane;
+    const int qrow = qt * kTile + row;
+    const bool row_ok = qrow < p.Tq;
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+    const int et = threadIdx.x - 64;
+    for (int i = et; i < G * kTile; i += 256) {
+      const int hh = i / kTile, r = i - hh * kTile, t = qt * kTile + r;
+      // +inf for rows behind the end: their probabilities are 0
+      lse_sm[i] = t < p.Tq ? p.lse[(static_cast<int64_t>(b) * p.Hq + g * G + hh) * p.Tq + t] * 1.4426950408889634f
+                           : __int_as_float(0x7f800000);
+    }
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    float* out_row = p.imp + ((static_cast<int64_t>(b) * p.Hkv + g) * p.Tq + qrow) * p.n_pad + half * kAcc;
+    bool ok = true;
+    for (int jt = 0; ok && jt < p.nCT; ++jt) {
+      float acc[kAcc];
+#pragma unroll
+      for (int i = 0; i < kAcc; ++i) acc[i] = 0.f;
+      const int col0 = jt * kTile + half * 64;        // first compressed token of this warp's columns
+      const int nvalid = p.nC - col0;
+      for (int hh = 0; hh < G; ++hh) {
+        const int it = jt * G + hh, s = it & 1;
+        if (!mbar_wait_bounded(&ctl->acc_full[s], (it >> 1) & 1, abort_flag)) {
+          record_status(p.status, kDevWaitAccFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float neg_l = -lse_sm[hh * kTile + row];
+        const uint32_t s_col = lane_base + s * kTile + half * 64;
+        uint32_t sa[16], sb[16];
+        tmem_ld16(s_col, sa);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          tc_wait_ld();
+          if (u + 1 < 4) {
+            if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+            else tmem_ld16(s_col + (u + 1) * 16, sb);
+          } else {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[s]);
+          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float pr = ex2_approx(fmaf(__uint_as_float((u & 1) ? sb[i] : sa[i]), p.scale_log2, neg_l));
+            if (nvalid < 64 && u * 16 + i >= nvalid) pr = 0.f;
+            acc[(u * 16 + i) / R] += pr;
+          }
+        }
+      }
+      if (ok && row_ok) {
+        float* dst = out_row + jt * (kTile / R);
+        if constexpr (kAcc % 4 == 0) {
+#pragma unroll
+          for (int i = 0; i < kAcc; i += 4)
+            *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < kAcc; ++i) dst[i] = acc[i];
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    __syncwarp();
+    tmem_dealloc(tmem_base, 256);
+  }
+}
+
+// ------------------------------------------------------------------- select
+// One warp per (b, g, t).  Importance values are >= 0; taken entries are marked -1, entries
+// behind the last selection block -2.  Ties go to the lower block index; output ascending.
+__global__ void __launch_bounds__(128) nsa_select_kernel(const float* __restrict__ imp, int n_pad, int n_s, int k_eff,
+                                                         int64_t rows, int32_t* __restrict__ blocks) {
+  extern __shared__ float sel_sm[];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t r = static_cast<int64_t>(blockIdx.x) * 4 + wib;
+  if (r >= rows) return;
+  const int n = (n_s + 31) & ~31;                     // scanned range, a multiple of 32
+  float* v = sel_sm + wib * n;
+  const float* src = imp + r * n_pad;
+  for (int i = lane; i < n; i += 32) v[i] = i < n_s ? (i < n_pad ? src[i] : 0.f) : -2.f;
+  __syncwarp();
+  for (int s = 0; s < k_eff; ++s) {
+    float best = -3.f;
+    int bi = 0x7fffffff;
+    for (int i = lane; i < n; i += 32) {
+      const float x = v[i];
+      if (x > best) {                                 // ascending scan, strict: the lowest index of equals
+        best = x;
+        bi = i;
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+      if (ob > best || (ob == best && oi < bi)) {
+        best = ob;
+        bi = oi;
+      }
+    }
+    if (lane == 0) v[bi] = -1.f;
+    __syncwarp();
+  }
+  int32_t* dst = blocks + r * k_eff;
+  int cnt = 0;
+  for (int i0 = 0; i0 < n; i0 += 32) {
+    const bool taken = v[i0 + lane] == -1.f;
+    const uint32_t m = __ballot_sync(0xffffffffu, taken);
+    if (taken) dst[cnt + __popc(m & ((1u << lane) - 1u))] = i0 + lane;
+    cnt += __popc(m);
+  }
+}
+
+// ------------------------------------------------------- selected attention
+// One warp per (b, g, t): plain softmax attention of the G query heads of kv group g over the keys
+// of the selected blocks.  Scores: every lane owns one key of a 32-key chunk and accumulates the G
+// dot products (q broadcast from shared memory); values: every lane owns D/32 channels.
+struct NsaSelParams {
+  const __nv_bfloat16 *q, *k, *v;
+  int64_t qs[4], ks[4], vs[4];
+  const int32_t* blocks;    // (B, Hkv, Tq, n_sel)
+  float* o;                 // (B, Hq, Tq, D) fp32 contiguous
+  int B, Hq, Hkv, G, Tq, Tk, n_sel, sel_block;
+  float scale_log2;
+};
+
+template <int D, int GMAX>
+__global__ void __launch_bounds__(128) nsa_selected_attn_kernel(const NsaSelParams p) {
+  constexpr int DPL = D / 32;
+  __shared__ float qsm[4][GMAX][D];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + wib;
+  const int64_t total = static_cast<int64_t>(p.B) * p.Hkv * p.Tq;
+  if (wid >= total) return;
+  const int t = static_cast<int>(wid % p.Tq);
+  const int g = static_cast<int>((wid / p.Tq) % p.Hkv);
+  const int b = static_cast<int>(wid / (static_cast<int64_t>(p.Tq) * p.Hkv));
+  const int G = p.G;
+
+  for (int i = lane; i < G * D; i += 32) {
+    const int hh = i / D, d = i - hh * D;
+    qsm[wib][hh][d] = __bfloat162float(p.q[b * p.qs[0] + (g * G + hh) * p.qs[1] + t * p.qs[2] + d]) * p.scale_log2;
+  }
+  __syncwarp();
+  const __nv_bfloat16* kbase = p.k + b * p.ks[0] + g * p.ks[1];
+  const __nv_bfloat16* vbase = p.v + b * p.vs[0] + g * p.vs[1];
+  const int32_t* blk = p.blocks + ((static_cast<int64_t>(b) * p.Hkv + g) * p.Tq + t) * p.n_sel;
+  const float ninf = -__int_as_float(0x7f800000);
+
+  float o[GMAX][DPL];
+  float m[GMAX], l[GMAX];
+#pragma unroll
+  for (int hh = 0; hh < GMAX; ++hh) {
+    m[hh] = ninf;
+    l[hh] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) o[hh][i] = 0.f;
+  }
+
+  const int chunks_per_block = p.sel_block / 32;
+  for (int s = 0; s < p.n_sel; ++s) {
+    const int key_block0 = blk[s] * p.sel_block;
+    for (int c = 0; c < chunks_per_block; ++c) {
+      const int key = key_block0 + c * 32 + lane;
+      const bool ok = key < p.Tk;
+      // ---- scores of this lane's key against the G heads (log2 domain)
+      float sc[GMAX];
+#pragma unroll
+      for (int hh = 0; hh < GMAX; ++hh) sc[hh] = 0.f;
+      if (ok) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<int64_t>(key) * p.ks[2]);
+#pragma unroll 2
+        for (int d8 = 0; d8 < D / 8; ++d8) {
+          const uint4 kv = __ldg(kr + d8);
+          const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+          float kf[8];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            kf[2 * q] = __uint_as_float(w[q] << 16);
+            kf[2 * q + 1] = __uint_as_float(w[q] & 0xffff0000u);
+          }
+#pragma unroll
+          for (int hh = 0; hh < GMAX; ++hh) {
+            if (hh < G) {
+              const float4 qa = *reinterpret_cast<const float4*>(&qsm[wib][hh][d8 * 8]);
+              const float4 qb = *reinterpret_cast<const float4*>(&qsm[wib][hh][d8 * 8 + 4]);
+              sc[hh] = fmaf(qa.x, kf[0], fmaf(qa.y, kf[1], fmaf(qa.z, kf[2], fmaf(qa.w, kf[3], sc[hh]))));
+              sc[hh] = fmaf(qb.x, kf[4], fmaf(qb.y, kf[5], fmaf(qb.z, kf[6], fmaf(qb.w, kf[7], sc[hh]))));
+            }
+          }
+        }
+      }
+      // ---- online softmax per head; probabilities stay in the lane that owns the key
+      float pr[GMAX];
+#pragma unroll
+      for (int hh = 0; hh < GMAX; ++hh) {
+        pr[hh] = 0.f;
+        if (hh < G) {
+          float gm = ok ? sc[hh] : ninf;
+#pragma unroll
+          for (int off = 16; off > 0; off >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, off));
+          const float m_new = fmaxf(m[hh], gm);
+          if (m_new != ninf) {
+            const float alpha = (m[hh] == m_new) ? 1.f : ex2_approx(m[hh] - m_new);
+            pr[hh] = ok ? ex2_approx(sc[hh] - m_new) : 0.f;
+            float ps = pr[hh];
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, off);
+            l[hh] = l[hh] * alpha + ps;
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[hh][i] *= alpha;
+            m[hh] = m_new;
+          }
+        }
+      }
+      // ---- O += P V: the chunk's value rows are read once for all heads
+      const int nk = min(32, p.Tk - (key_block0 + c * 32));
+      for (int j = 0; j < nk; ++j) {
+        const __nv_bfloat16* vr = vbase + static_cast<int64_t>(key_block0 + c * 32 + j) * p.vs[2] + lane * DPL;
+        float vf[DPL];
+        if constexpr (DPL == 4) {
+          const uint2 vv = __ldg(reinterpret_cast<const uint2*>(vr));
+          vf[0] = __uint_as_float(vv.x << 16);
+          vf[1] = __uint_as_float(vv.x & 0xffff0000u);
+          vf[2] = __uint_as_float(vv.y << 16);
+          vf[3] = __uint_as_float(vv.y & 0xffff0000u);
+        } else {
+          const uint32_t vv = __ldg(reinterpret_cast<const uint32_t*>(vr));
+          vf[0] = __uint_as_float(vv << 16);
+          vf[1] = __uint_as_float(vv & 0xffff0000u);
+        }
+#pragma unroll
+        for (int hh = 0; hh < GMAX; ++hh) {
+          if (hh < G) {
+            const float pj = __shfl_sync(0xffffffffu, pr[hh], j);
+#pragma unroll
+            for (int i = 0; i < DPL; ++i) o[hh][i] = fmaf(pj, vf[i], o[hh][i]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int hh = 0; hh < GMAX; ++hh) {
+    if (hh < G) {
+      const float inv = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
+      float* dst = p.o + ((static_cast<int64_t>(b) * p.Hq + g * G + hh) * p.Tq + t) * D + lane * DPL;
+#pragma unroll
+      for (int i = 0; i < DPL; ++i) dst[i] = o[hh][i] * inv;
+    }
+  }
+}
+
+// ------------------------------------------------------------------ combine
+// out[b,h,t,:] = sum_j sigmoid(gate[b,t,h,j]) * o_j[b,h,t,:], branches (B,Hq,T,D) fp32 contiguous.
+__global__ void nsa_combine_kernel(const float* __restrict__ o_cmp, const float* __restrict__ o_sel,
+                                   const float* __restrict__ o_win, const float* __restrict__ gate, void* out,
+                                   int out_dtype, int B, int Hq, int T, int D) {
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t total = static_cast<int64_t>(B) * Hq * T * D;
+  if (gid >= total) return;
+  const int64_t bht = gid / D;
+  const int t = static_cast<int>(bht % T);
+  const int h = static_cast<int>((bht / T) % Hq);
+  const int b = static_cast<int>(bht / (static_cast<int64_t>(T) * Hq));
+  const float* gp = gate + ((static_cast<int64_t>(b) * T + t) * Hq + h) * 3;
+  const float g0 = 1.f / (1.f + __expf(-gp[0])), g1 = 1.f / (1.f + __expf(-gp[1])), g2 = 1.f / (1.f + __expf(-gp[2]));
+  const float x = g0 * o_cmp[gid] + g1 * o_sel[gid] + g2 * o_win[gid];
+  if (out_dtype == SWV_F32) static_cast<float*>(out)[gid] = x;
+  else if (out_dtype == SWV_BF16) static_cast<__nv_bfloat16*>(out)[gid] = __float2bfloat16_rn(x);
+  else static_cast<__half*>(out)[gid] = __float2half_rn(x);
+}
+
+// --------------------------------------------------------------------- host
+static bool nsa_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <int D, int R>
+static int launch_importance(const CUtensorMap& tq, const CUtensorMap& tk, const NsaImpParams& p, cudaStream_t st) {
+  using Cfg = NsaImpCfg<D>;
+  SWV_CUDA_OK(cudaFuncSetAttribute(nsa_importance_kernel<D, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                   static_cast<int>(Cfg::kSmem)));
+  nsa_importance_kernel<D, R><<<static_cast<unsigned>(p.B) * p.Hkv * p.nQT, 320, Cfg::kSmem, st>>>(tq, tk, p);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+int nsa_importance_bytes_impl(int B, int Hkv, int Tq, int nC, int cmp_stride, int sel_block, size_t* bytes) {
+  if (!bytes) return SWV_ERR_NULL;
+  if (B < 1 || Hkv < 1 || Tq < 1 || nC < 1 || cmp_stride < 1 || sel_block < cmp_stride || sel_block % cmp_stride)
+    return SWV_ERR_SHAPE;
+  const int R = sel_block / cmp_stride;
+  const size_t n_pad = static_cast<size_t>((nC + kTile - 1) / kTile) * (kTile / R);
+  *bytes = static_cast<size_t>(B) * Hkv * Tq * n_pad * 4;
+  return SWV_OK;
+}
+
+int nsa_select_blocks_impl(const void* q, const int64_t* qs, const void* kc, const int64_t* kcs, const float* lse,
+                           int B, int Hq, int Hkv, int Tq, int Tk, int nC, int D, int cmp_stride, int sel_block,
+                           int n_sel, float* importance, size_t importance_bytes, int32_t* blocks, int* status,
+                           cudaStream_t st) {
+  if (!q || !kc || !lse || !importance || !blocks || !status || !qs || !kcs) return SWV_ERR_NULL;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv || Tq < 1 || Tk < 1 || nC < 1 || n_sel < 1) return SWV_ERR_SHAPE;
+  if (cmp_stride < 1 || sel_block < cmp_stride || sel_block % cmp_stride) return SWV_ERR_SHAPE;
+  const int G = Hq / Hkv, R = sel_block / cmp_stride;
+  if (G > kNsaMaxGroup || (D != 64 && D != 128) || (R != 1 && R != 2 && R != 4 && R != 8)) return SWV_ERR_UNSUPPORTED;
+  size_t need = 0;
+  nsa_importance_bytes_impl(B, Hkv, Tq, nC, cmp_stride, sel_block, &need);
+  if (importance_bytes < need) return SWV_ERR_WORKSPACE;
+  if (qs[3] != 1 || kcs[3] != 1 || !nsa_aligned16(q) || !nsa_aligned16(kc) || !nsa_aligned16(importance))
+    return SWV_ERR_ALIGN;
+  for (int i = 0; i < 3; ++i)
+    if ((qs[i] * 2) % 16 || (kcs[i] * 2) % 16) return SWV_ERR_ALIGN;
+  const int n_s = (Tk + sel_block - 1) / sel_block;
+  const int k_eff = n_sel < n_s ? n_sel : n_s;
+
+  CUtensorMap tq, tk;
+  int rc = make_tmap_4d(&tq, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, Tq, Hq, B, qs[2] * 2, qs[1] * 2, qs[0] * 2, 64,
+                        kTile);
+  if (rc != SWV_OK) return rc;
+  rc = make_tmap_4d(&tk, kc, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, D, nC, Hkv, B, kcs[2] * 2, kcs[1] * 2, kcs[0] * 2, 64,
+                    kTile);
+  if (rc != SWV_OK) return rc;
+
+  NsaImpParams p;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.Tq = Tq; p.nC = nC;
+  p.nQT = (Tq + kTile - 1) / kTile;
+  p.nCT = (nC + kTile - 1) / kTile;
+  p.n_pad = p.nCT * (kTile / R);
+  p.lse = lse; p.imp = importance;
+  p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
+  p.status = status;
+  if (D == 64) {
+    if (R == 1) rc = launch_importance<64, 1>(tq, tk, p, st);
+    else if (R == 2) rc = launch_importance<64, 2>(tq, tk, p, st);
+    else if (R == 4) rc = launch_importance<64, 4>(tq, tk, p, st);
+    else rc = launch_importance<64, 8>(tq, tk, p, st);
+  } else {
+    if (R == 1) rc = launch_importance<128, 1>(tq, tk, p, st);
+    else if (R == 2) rc = launch_importance<128, 2>(tq, tk, p, st);
+    else if (R == 4) rc = launch_importance<128, 4>(tq, tk, p, st);
+    else rc = launch_importance<128, 8>(tq, tk, p, st);
+  }
+  if (rc != SWV_OK) return rc;
+
+  const int64_t rows = static_cast<int64_t>(B) * Hkv * Tq;
+  const int n = (n_s + 31) & ~31;
+  const size_t sm = static_cast<size_t>(4) * n * 4;
+  if (sm > 200 * 1024) return SWV_ERR_UNSUPPORTED;
+  if (sm > 48 * 1024)
+    SWV_CUDA_OK(cudaFuncSetAttribute(nsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(sm)));
+  nsa_select_kernel<<<static_cast<unsigned>((rows + 3) / 4), 128, sm, st>>>(importance, p.n_pad, n_s, k_eff, rows,
+                                                                            blocks);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                           const int64_t* vs, const int32_t* blocks, int B, int Hq, int Hkv, int Tq, int Tk, int D,
+                           int sel_block, int n_sel, float* o, cudaStream_t st) {
+  if (!q || !k || !v || !blocks || !o || !qs || !ks || !vs) return SWV_ERR_NULL;
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv || Tq < 1 || Tk < 1 || n_sel < 1) return SWV_ERR_SHAPE;
+  if (sel_block < 32 || sel_block % 32) return SWV_ERR_UNSUPPORTED;
+  const int G = Hq / Hkv;
+  if (G > 8 || (D != 64 && D != 128)) return SWV_ERR_UNSUPPORTED;
+  if (qs[3] != 1 || ks[3] != 1 || vs[3] != 1 || !nsa_aligned16(k) || !nsa_aligned16(v)) return SWV_ERR_ALIGN;
+  for (int i = 0; i < 3; ++i)
+    if ((ks[i] * 2) % 16 || (vs[i] * 2) % 16) return SWV_ERR_ALIGN;
+  NsaSelParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q);
+  p.k = static_cast<const __nv_bfloat16*>(k);
+  p.v = static_cast<const __nv_bfloat16*>(v);
+  for (int i = 0; i < 4; ++i) { p.qs[i] = qs[i]; p.ks[i] = ks[i]; p.vs[i] = vs[i]; }
+  p.blocks = blocks; p.o = o;
+  p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.Tq = Tq; p.Tk = Tk; p.n_sel = n_sel; p.sel_block = sel_block;
+  p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
+  const int64_t total = static_cast<int64_t>(B) * Hkv * Tq;
+  const unsigned grid = static_cast<unsigned>((total + 3) / 4);
+  if (D == 64) nsa_selected_attn_kernel<64, 8><<<grid, 128, 0, st>>>(p);
+  else nsa_selected_attn_kernel<128, 8><<<grid, 128, 0, st>>>(p);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
+                     int out_dtype, int B, int Hq, int T, int D, cudaStream_t st) {
+  if (!o_cmp || !o_sel || !o_win || !gate || !out) return SWV_ERR_NULL;
+  if (B < 1 || Hq < 1 || T < 1 || D < 1) return SWV_ERR_SHAPE;
+  if (out_dtype != SWV_F32 && out_dtype != SWV_BF16 && out_dtype != SWV_F16) return SWV_ERR_DTYPE;
+  const int64_t total = static_cast<int64_t>(B) * Hq * T * D;
+  nsa_combine_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(o_cmp, o_sel, o_win, gate, out,
+                                                                                 out_dtype, B, Hq, T, D);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+}  // namespace swv

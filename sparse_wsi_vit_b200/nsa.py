@@ -4,13 +4,12 @@ are the builder-defined ones frozen in ``oracle/nsa.py`` (parity unpinned).
 
   compressed : `swv_pool_tokens` (mean pooling) + the block-sparse tensor-core kernel over ALL
                compressed tokens, grouped-query (kv_group), returning the log-sum-exp per row;
-  selection  : block importance from the compressed-branch probabilities.  This step is NOT a
-               hand-written kernel yet: it recomputes q.Kc^T with cuBLAS (torch.matmul) in query
-               chunks and uses torch.topk -- library code, stated as such in DESIGN.md;
-  selected   : the gather kernel (`swv_dsa_attn_gather_fwd`, weights 1) over the keys of the
-               selected blocks, one call per kv group (the lists are shared by the group's heads);
+  selection  : `swv_nsa_select_blocks_fwd`: block importance recomputed on the tensor cores from
+               q, the compressed keys and the log-sum-exp, then an arg-max kernel per query;
+  selected   : `swv_nsa_selected_attn_fwd`: one warp per (kv group, query) reads each selected
+               key / value row once for all heads of the group;
   window     : the block-sparse kernel in token-pattern mode (|i-j| <= window/2);
-  gate       : sigmoid-weighted sum (elementwise, PyTorch).
+  gate       : `swv_nsa_combine_fwd`, the sigmoid-weighted sum.
 """
 from __future__ import annotations
 
@@ -19,8 +18,8 @@ import ctypes
 import numpy as np
 import torch
 
-from ._lib import check, lib, strides
-from .ops import _require_cuda, _stream, block_sparse_attention, dsa_attention_gather
+from ._lib import check, dtype_code, lib, strides
+from .ops import _require_cuda, _stream, block_sparse_attention, status_word
 from .patterns import _to_csr, static_window_blocks
 
 
@@ -44,31 +43,39 @@ def _full_list(n_q_blocks, n_k_blocks, device):
     return rp, ci
 
 
-def select_blocks(q, kc, lse, T, cmp_stride, sel_block, sel_topk, kv_group, chunk=2048):
+def select_blocks(q, kc, lse, T, cmp_stride, sel_block, sel_topk, kv_group):
     """Top `sel_topk` selection blocks per (batch, kv head, query), ascending block ids, int32
-    (B, Hkv, T, k_eff).  Importance = compressed-branch probabilities summed over the group's query
-    heads and over the compressed tokens whose first key lies in the block."""
+    (B, Hkv, Tq, k_eff).  Importance = compressed-branch probabilities summed over the group's query
+    heads and over the compressed tokens whose first key lies in the block; ties -> lower block id."""
+    _require_cuda(q, kc, lse)
     B, Hq, Tq, D = q.shape
-    Hkv = Hq // kv_group
-    nC = kc.shape[2]
+    Hkv, nC = kc.shape[1], kc.shape[2]
     n_s = -(-T // sel_block)
     k_eff = min(sel_topk, n_s)
-    owner = (torch.arange(nC, device=q.device) * cmp_stride) // sel_block
-    scale = 1.0 / D ** 0.5
-    out = torch.empty((B, Hkv, Tq, k_eff), dtype=torch.int32, device=q.device)
-    qg = q.view(B, Hkv, kv_group, Tq, D)
-    lg = lse.view(B, Hkv, kv_group, Tq)
-    kcf = kc.float()
-    for t0 in range(0, Tq, chunk):
-        t1 = min(Tq, t0 + chunk)
-        s = torch.einsum("bkgtd,bkcd->bkgtc", qg[:, :, :, t0:t1].float(), kcf) * scale
-        p = torch.exp(s - lg[:, :, :, t0:t1, None]).sum(dim=2)                 # (B, Hkv, t, nC)
-        imp = torch.zeros((B, Hkv, t1 - t0, n_s), dtype=torch.float32, device=q.device)
-        imp.index_add_(3, owner, p)
-        # ties -> lower block index: stable descending sort
-        top = torch.sort(imp, dim=3, descending=True, stable=True).indices[..., :k_eff]
-        out[:, :, t0:t1] = torch.sort(top, dim=3).values.to(torch.int32)
-    return out
+    nbytes = ctypes.c_size_t()
+    check(lib.swv_nsa_importance_bytes(B, Hkv, Tq, nC, cmp_stride, sel_block, ctypes.byref(nbytes)),
+          "swv_nsa_importance_bytes")
+    imp = torch.empty(nbytes.value // 4, dtype=torch.float32, device=q.device)
+    blocks = torch.empty((B, Hkv, Tq, k_eff), dtype=torch.int32, device=q.device)
+    lse = lse.contiguous()
+    check(lib.swv_nsa_select_blocks_fwd(q.data_ptr(), strides(q), kc.data_ptr(), strides(kc), lse.data_ptr(), B, Hq, Hkv,
+                                        Tq, T, nC, D, cmp_stride, sel_block, sel_topk, imp.data_ptr(), nbytes.value,
+                                        blocks.data_ptr(), status_word(q.device).data_ptr(), _stream(q.device)),
+          "swv_nsa_select_blocks_fwd")
+    return blocks
+
+
+def selected_attention(q, k, v, blocks, sel_block):
+    """Softmax attention of every query head over the keys of its kv group's selected blocks -> fp32."""
+    _require_cuda(q, k, v, blocks)
+    B, Hq, Tq, D = q.shape
+    Hkv, Tk = k.shape[1], k.shape[2]
+    o = torch.empty((B, Hq, Tq, D), dtype=torch.float32, device=q.device)
+    blocks = blocks.contiguous()
+    check(lib.swv_nsa_selected_attn_fwd(q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v),
+                                        blocks.data_ptr(), B, Hq, Hkv, Tq, Tk, D, sel_block, blocks.shape[-1],
+                                        o.data_ptr(), _stream(q.device)), "swv_nsa_selected_attn_fwd")
+    return o
 
 
 def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_topk=16, window=512,
@@ -91,24 +98,17 @@ def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_
 
     # selected branch
     blocks = select_blocks(q, kc, lse, T, cmp_stride, sel_block, sel_topk, G)       # (B,Hkv,T,k_eff)
-    k_eff = blocks.shape[-1]
-    tok = (blocks[..., None].long() * sel_block + torch.arange(sel_block, device=dev)).reshape(B, Hkv, T, -1)
-    valid = (tok < T).to(torch.float32)
-    idx = tok.clamp_(max=T - 1).to(torch.int32)
-    ones = torch.ones_like(valid)
-    o_sel = torch.empty((B, Hq, T, D), dtype=torch.float32, device=dev)
-    for g in range(Hkv):
-        dsa_attention_gather(q[:, g * G:(g + 1) * G], k[:, g:g + 1], v[:, g:g + 1], idx[:, g].contiguous(),
-                             valid[:, g].contiguous(), ones[:, g].contiguous(), o_sel[:, g * G:(g + 1) * G],
-                             kv_group=G)
+    o_sel = selected_attention(q, k, v, blocks, sel_block)
 
     # sliding-window branch
     wrp, wci = static_window_blocks(T, 0, window // 2, 1, 128)
     o_win = block_sparse_attention(q, k, v, torch.from_numpy(wrp).to(dev), torch.from_numpy(wci).to(dev), 128, mode=1,
                                    num_cls=0, window=window // 2, dilation=1, out_dtype=torch.float32, kv_group=G)
 
-    gs = torch.sigmoid(gate.float()).permute(0, 2, 1, 3)                            # (B,Hq,T,3)
-    out = (gs[..., 0:1] * o_cmp + gs[..., 1:2] * o_sel + gs[..., 2:3] * o_win).to(out_dtype)
+    out = torch.empty((B, Hq, T, D), dtype=out_dtype, device=dev)
+    gate = gate.float().contiguous()
+    check(lib.swv_nsa_combine_fwd(o_cmp.data_ptr(), o_sel.data_ptr(), o_win.data_ptr(), gate.data_ptr(), out.data_ptr(),
+                                  dtype_code(out_dtype), B, Hq, T, D, _stream(dev)), "swv_nsa_combine_fwd")
     if return_parts:
         return out, o_cmp, o_sel, o_win, blocks
     return out
