@@ -212,6 +212,27 @@ int swv_nsa_selected_attn_fwd(const void* q, const int64_t q_strides[4], const v
 int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
                         int out_dtype, int B, int Hq, int T, int D, void* stream);
 
+/* NSA-style attention, whole forward pass in one call: mean-pooled compression (window cmp_block,
+ * stride cmp_stride), compressed branch, block selection (n_sel blocks of sel_block keys per query
+ * and kv group), selected branch, sliding-window branch (keys with |i - j| <= window / 2,
+ * non-causal) and the gated sum.  Non-causal, batch-major tensors:
+ *   q (B,Hq,T,D), k, v (B,Hkv,T,D) bf16, unit inner stride, 16-byte aligned rows; D = 64 or 128;
+ *   gate (B,T,Hq,3) fp32 contiguous, logits in the order [compressed, selected, window];
+ *   out (B,Hq,T,D) contiguous in out_dtype;
+ *   workspace: swv_nsa_workspace_bytes() bytes, 256-byte aligned (pooled keys / values, the three
+ *   branch outputs in fp32, row statistics, block scores, key-block lists);
+ *   blocks_out: optional (B,Hkv,T,min(n_sel, ceil(T/sel_block))) int32, the selected block ids.
+ * Limits as for the entry points it is built from (Hq / Hkv <= 8, sel_block a multiple of 32 and of
+ * cmp_stride with sel_block / cmp_stride in {1,2,4,8}).
+ */
+int swv_nsa_workspace_bytes(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
+                            int n_sel, int window, size_t* bytes);
+int swv_nsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                     const void* v, const int64_t v_strides[4], const float* gate, void* out, int out_dtype, int B,
+                     int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block, int n_sel,
+                     int window, void* workspace, size_t workspace_bytes, int32_t* blocks_out, int* status,
+                     void* stream);
+
 /* 2-D rotary embedding on per-token (y, x) coordinates.
  * Replaces VisionRotaryEmbedding.forward, dynamic branch
  * (src/sparse_wsi_vit/models/vit_5/rope.py:72-97, rotate_half :33-37), as applied to q and k in

@@ -17,6 +17,7 @@ EXPORTS = [
     "swv_dsa_indexer_topk_fwd", "swv_dsa_attn_gather_fwd", "swv_dsa_attn_masked_fwd",
     "swv_dsa_indexer_topk_static_fwd", "swv_block_sparse_attn_fwd", "swv_rope2d_apply", "swv_pool_tokens",
     "swv_nsa_importance_bytes", "swv_nsa_select_blocks_fwd", "swv_nsa_selected_attn_fwd", "swv_nsa_combine_fwd",
+    "swv_nsa_workspace_bytes", "swv_nsa_attn_fwd",
 ]
 
 
@@ -66,6 +67,10 @@ def _load():
         c_int, c_void_p, c_void_p]
     lib.swv_nsa_combine_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                         c_int, c_void_p]
+    lib.swv_nsa_workspace_bytes.argtypes = [c_int] * 10 + [POINTER(c_size_t)]
+    lib.swv_nsa_attn_fwd.argtypes = [
+        c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+        c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p, c_void_p]
     for name in EXPORTS[2:]:
         getattr(lib, name).restype = c_int
     return lib

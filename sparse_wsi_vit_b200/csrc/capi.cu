@@ -42,6 +42,12 @@ int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, cons
                            int sel_block, int n_sel, float* o, cudaStream_t st);
 int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
                      int out_dtype, int B, int Hq, int T, int D, cudaStream_t st);
+int nsa_workspace_bytes_impl(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
+                             int n_sel, int window, size_t* bytes);
+int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                  const int64_t* vs, const float* gate, void* out, int out_dtype, int B, int Hq, int Hkv, int T,
+                  int D, int cmp_block, int cmp_stride, int sel_block, int n_sel, int window, void* workspace,
+                  size_t workspace_bytes, int32_t* blocks_out, int* status, cudaStream_t st);
 }  // namespace swv
 
 extern "C" {
@@ -163,6 +169,21 @@ int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_w
                         int out_dtype, int B, int Hq, int T, int D, void* stream) {
   return swv::nsa_combine_impl(o_cmp, o_sel, o_win, gate, out, out_dtype, B, Hq, T, D,
                                static_cast<cudaStream_t>(stream));
+}
+
+int swv_nsa_workspace_bytes(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
+                            int n_sel, int window, size_t* bytes) {
+  return swv::nsa_workspace_bytes_impl(B, Hq, Hkv, T, D, cmp_block, cmp_stride, sel_block, n_sel, window, bytes);
+}
+
+int swv_nsa_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                     const void* v, const int64_t v_strides[4], const float* gate, void* out, int out_dtype, int B,
+                     int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block, int n_sel,
+                     int window, void* workspace, size_t workspace_bytes, int32_t* blocks_out, int* status,
+                     void* stream) {
+  return swv::nsa_attn_impl(q, q_strides, k, k_strides, v, v_strides, gate, out, out_dtype, B, Hq, Hkv, T, D,
+                            cmp_block, cmp_stride, sel_block, n_sel, window, workspace, workspace_bytes, blocks_out,
+                            status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -562,4 +562,147 @@ int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win,
   return SWV_OK;
 }
 
+
+// ------------------------------------------------------- whole forward pass
+// Key-block lists of the two tensor-core branches, built on the device (one CTA):
+//   compressed branch: every query block attends all `n_cb` blocks of compressed tokens;
+//   window branch    : the 128-token blocks that intersect [q0 - reach, q1 + reach].
+__global__ void nsa_build_lists_kernel(int n_qb, int n_cb, int T, int reach, int32_t* full_ptr, int32_t* full_col,
+                                       int32_t* win_ptr, int32_t* win_col) {
+  __shared__ int total;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < n_qb; ++i) {
+      full_ptr[i] = i * n_cb;
+      win_ptr[i] = acc;
+      const int lo = max(0, i * kTile - reach) / kTile;
+      const int hi = min(T - 1, min(T, (i + 1) * kTile) - 1 + reach) / kTile;
+      acc += hi - lo + 1;
+    }
+    full_ptr[n_qb] = n_qb * n_cb;
+    win_ptr[n_qb] = acc;
+    total = acc;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n_qb * n_cb; i += blockDim.x) full_col[i] = i % n_cb;
+  for (int i = threadIdx.x; i < n_qb; i += blockDim.x) {
+    const int lo = max(0, i * kTile - reach) / kTile;
+    const int n = win_ptr[i + 1] - win_ptr[i];
+    for (int j = 0; j < n; ++j) win_col[win_ptr[i] + j] = lo + j;
+  }
+  (void)total;
+}
+
+int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, int T, int D, int win, int stride,
+                     cudaStream_t st);
+int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                           const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
+                           int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
+                           const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
+                           cudaStream_t st);
+
+struct NsaLayout {
+  size_t kc, vc, o_cmp, o_sel, o_win, lse, imp, blocks, full_ptr, full_col, win_ptr, win_col, total;
+  int nC, n_qb, n_cb, k_eff, win_blocks;
+};
+static size_t nsa_up(size_t x) { return (x + 255) / 256 * 256; }
+static int nsa_layout(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block, int n_sel,
+                      int window, NsaLayout* L) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv || T < cmp_block || cmp_block < 1 || cmp_stride < 1 || n_sel < 1 ||
+      window < 0)
+    return SWV_ERR_SHAPE;
+  L->nC = (T - cmp_block) / cmp_stride + 1;
+  L->n_qb = (T + kTile - 1) / kTile;
+  L->n_cb = (L->nC + kTile - 1) / kTile;
+  const int n_s = (T + sel_block - 1) / sel_block;
+  L->k_eff = n_sel < n_s ? n_sel : n_s;
+  L->win_blocks = 2 * ((window / 2 + kTile - 1) / kTile) + 2;
+  size_t imp_bytes = 0;
+  const int rc = nsa_importance_bytes_impl(B, Hkv, T, L->nC, cmp_stride, sel_block, &imp_bytes);
+  if (rc != SWV_OK) return rc;
+  size_t off = 0;
+  const size_t branch = static_cast<size_t>(B) * Hq * T * D * 4;
+  L->kc = off; off += nsa_up(static_cast<size_t>(B) * Hkv * L->nC * D * 2);
+  L->vc = off; off += nsa_up(static_cast<size_t>(B) * Hkv * L->nC * D * 2);
+  L->o_cmp = off; off += nsa_up(branch);
+  L->o_sel = off; off += nsa_up(branch);
+  L->o_win = off; off += nsa_up(branch);
+  L->lse = off; off += nsa_up(static_cast<size_t>(B) * Hq * T * 4);
+  L->imp = off; off += nsa_up(imp_bytes);
+  L->blocks = off; off += nsa_up(static_cast<size_t>(B) * Hkv * T * L->k_eff * 4);
+  L->full_ptr = off; off += nsa_up((L->n_qb + 1) * 4);
+  L->full_col = off; off += nsa_up(static_cast<size_t>(L->n_qb) * L->n_cb * 4);
+  L->win_ptr = off; off += nsa_up((L->n_qb + 1) * 4);
+  L->win_col = off; off += nsa_up(static_cast<size_t>(L->n_qb) * L->win_blocks * 4);
+  L->total = off;
+  return SWV_OK;
+}
+
+int nsa_workspace_bytes_impl(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
+                             int n_sel, int window, size_t* bytes) {
+  if (!bytes) return SWV_ERR_NULL;
+  NsaLayout L;
+  const int rc = nsa_layout(B, Hq, Hkv, T, D, cmp_block, cmp_stride, sel_block, n_sel, window, &L);
+  if (rc == SWV_OK) *bytes = L.total;
+  return rc;
+}
+
+int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                  const int64_t* vs, const float* gate, void* out, int out_dtype, int B, int Hq, int Hkv, int T,
+                  int D, int cmp_block, int cmp_stride, int sel_block, int n_sel, int window, void* workspace,
+                  size_t workspace_bytes, int32_t* blocks_out, int* status, cudaStream_t st) {
+  if (!q || !k || !v || !gate || !out || !workspace || !status || !qs || !ks || !vs) return SWV_ERR_NULL;
+  NsaLayout L;
+  int rc = nsa_layout(B, Hq, Hkv, T, D, cmp_block, cmp_stride, sel_block, n_sel, window, &L);
+  if (rc != SWV_OK) return rc;
+  if (workspace_bytes < L.total) return SWV_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SWV_ERR_ALIGN;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  void* kc = ws + L.kc;
+  void* vc = ws + L.vc;
+  float* o_cmp = reinterpret_cast<float*>(ws + L.o_cmp);
+  float* o_sel = reinterpret_cast<float*>(ws + L.o_sel);
+  float* o_win = reinterpret_cast<float*>(ws + L.o_win);
+  float* lse = reinterpret_cast<float*>(ws + L.lse);
+  float* imp = reinterpret_cast<float*>(ws + L.imp);
+  int32_t* blocks = reinterpret_cast<int32_t*>(ws + L.blocks);
+  int32_t* full_ptr = reinterpret_cast<int32_t*>(ws + L.full_ptr);
+  int32_t* full_col = reinterpret_cast<int32_t*>(ws + L.full_col);
+  int32_t* win_ptr = reinterpret_cast<int32_t*>(ws + L.win_ptr);
+  int32_t* win_col = reinterpret_cast<int32_t*>(ws + L.win_col);
+  const int G = Hq / Hkv;
+  const int reach = window / 2;
+
+  nsa_build_lists_kernel<<<1, 256, 0, st>>>(L.n_qb, L.n_cb, T, reach, full_ptr, full_col, win_ptr, win_col);
+  SWV_CUDA_OK(cudaGetLastError());
+  rc = pool_tokens_impl(k, ks, kc, B, Hkv, T, D, cmp_block, cmp_stride, st);
+  if (rc != SWV_OK) return rc;
+  rc = pool_tokens_impl(v, vs, vc, B, Hkv, T, D, cmp_block, cmp_stride, st);
+  if (rc != SWV_OK) return rc;
+  const int64_t cs[4] = {static_cast<int64_t>(Hkv) * L.nC * D, static_cast<int64_t>(L.nC) * D, D, 1};
+  const int64_t os[4] = {static_cast<int64_t>(Hq) * T * D, static_cast<int64_t>(T) * D, D, 1};
+  // compressed branch (all compressed tokens, log-sum-exp kept for the selection)
+  rc = block_sparse_attn_impl(q, qs, kc, cs, vc, cs, full_ptr, full_col, kTile, 0, 0, 0, 1, G, lse, o_cmp, os,
+                              SWV_F32, B, Hq, T, L.nC, D, status, st);
+  if (rc != SWV_OK) return rc;
+  // selection + selected branch
+  size_t imp_bytes = 0;
+  nsa_importance_bytes_impl(B, Hkv, T, L.nC, cmp_stride, sel_block, &imp_bytes);
+  rc = nsa_select_blocks_impl(q, qs, kc, cs, lse, B, Hq, Hkv, T, T, L.nC, D, cmp_stride, sel_block, n_sel, imp,
+                              imp_bytes, blocks, status, st);
+  if (rc != SWV_OK) return rc;
+  rc = nsa_selected_attn_impl(q, qs, k, ks, v, vs, blocks, B, Hq, Hkv, T, T, D, sel_block, L.k_eff, o_sel, st);
+  if (rc != SWV_OK) return rc;
+  // sliding-window branch: token pattern |i - j| <= window / 2 inside the listed blocks
+  rc = block_sparse_attn_impl(q, qs, k, ks, v, vs, win_ptr, win_col, kTile, 1, 0, reach, 1, G, nullptr, o_win, os,
+                              SWV_F32, B, Hq, T, T, D, status, st);
+  if (rc != SWV_OK) return rc;
+  rc = nsa_combine_impl(o_cmp, o_sel, o_win, gate, out, out_dtype, B, Hq, T, D, st);
+  if (rc != SWV_OK) return rc;
+  if (blocks_out != nullptr)
+    SWV_CUDA_OK(cudaMemcpyAsync(blocks_out, blocks, static_cast<size_t>(B) * Hkv * T * L.k_eff * 4,
+                                cudaMemcpyDeviceToDevice, st));
+  return SWV_OK;
+}
+
 }  // namespace swv

@@ -81,7 +81,8 @@ def selected_attention(q, k, v, blocks, sel_block):
 def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_topk=16, window=512,
                   out_dtype=None, return_parts=False):
     """q (B,Hq,T,D), k, v (B,Hkv,T,D) bf16; gate (B,T,Hq,3) logits [compressed, selected, window].
-    Returns (B,Hq,T,D)."""
+    Returns (B,Hq,T,D).  One library call (`swv_nsa_attn_fwd`); with `return_parts` the same kernels
+    are run one by one and the branch outputs and selected blocks are returned as well."""
     _require_cuda(q, k, v, gate)
     B, Hq, T, D = q.shape
     Hkv = k.shape[1]
@@ -89,6 +90,19 @@ def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_
     dev = q.device
     out_dtype = out_dtype or q.dtype
     q, k, v = (t if t.dtype == torch.bfloat16 else t.to(torch.bfloat16) for t in (q, k, v))
+    gate = gate.float().contiguous()
+    out = torch.empty((B, Hq, T, D), dtype=out_dtype, device=dev)
+
+    if not return_parts:
+        nbytes = ctypes.c_size_t()
+        check(lib.swv_nsa_workspace_bytes(B, Hq, Hkv, T, D, cmp_block, cmp_stride, sel_block, sel_topk, window,
+                                          ctypes.byref(nbytes)), "swv_nsa_workspace_bytes")
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        check(lib.swv_nsa_attn_fwd(q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v),
+                                   gate.data_ptr(), out.data_ptr(), dtype_code(out_dtype), B, Hq, Hkv, T, D, cmp_block,
+                                   cmp_stride, sel_block, sel_topk, window, ws.data_ptr(), nbytes.value, None,
+                                   status_word(dev).data_ptr(), _stream(dev)), "swv_nsa_attn_fwd")
+        return out
 
     # compressed branch
     kc, vc = pool_tokens(k, cmp_block, cmp_stride), pool_tokens(v, cmp_block, cmp_stride)
@@ -105,10 +119,6 @@ def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_
     o_win = block_sparse_attention(q, k, v, torch.from_numpy(wrp).to(dev), torch.from_numpy(wci).to(dev), 128, mode=1,
                                    num_cls=0, window=window // 2, dilation=1, out_dtype=torch.float32, kv_group=G)
 
-    out = torch.empty((B, Hq, T, D), dtype=out_dtype, device=dev)
-    gate = gate.float().contiguous()
     check(lib.swv_nsa_combine_fwd(o_cmp.data_ptr(), o_sel.data_ptr(), o_win.data_ptr(), gate.data_ptr(), out.data_ptr(),
                                   dtype_code(out_dtype), B, Hq, T, D, _stream(dev)), "swv_nsa_combine_fwd")
-    if return_parts:
-        return out, o_cmp, o_sel, o_win, blocks
-    return out
+    return out, o_cmp, o_sel, o_win, blocks

@@ -34,3 +34,20 @@ def test_nsa_vs_oracle(T, Hq, Hkv, D, topk, window):
     assert (o_sel[0].cpu() - r_sel)[rows].abs().max() < 3e-2
     assert (out[0].cpu() - ref)[rows].abs().max() < 3e-2
     assert (out[0].cpu() - ref).abs().mean() < 2e-3
+
+
+def test_nsa_single_call_equals_stepwise():
+    """`swv_nsa_attn_fwd` (one call, device-built block lists, caller workspace) runs the same kernels
+    as the step-by-step composition: identical output bits."""
+    import sparse_wsi_vit_b200 as swv
+    from sparse_wsi_vit_b200.nsa import nsa_attention
+    T, Hq, Hkv, D = 1100, 8, 2, 128
+    g = torch.Generator().manual_seed(5)
+    q = torch.randn(1, Hq, T, D, generator=g).to(torch.bfloat16).to(DEV)
+    k = torch.randn(1, Hkv, T, D, generator=g).to(torch.bfloat16).to(DEV)
+    v = torch.randn(1, Hkv, T, D, generator=g).to(torch.bfloat16).to(DEV)
+    gate = torch.randn(1, T, Hq, 3, generator=g).to(DEV)
+    one = nsa_attention(q, k, v, gate, sel_topk=8, window=256, out_dtype=torch.float32)
+    parts = nsa_attention(q, k, v, gate, sel_topk=8, window=256, out_dtype=torch.float32, return_parts=True)
+    swv.check_status(DEV)
+    assert torch.equal(one, parts[0])
