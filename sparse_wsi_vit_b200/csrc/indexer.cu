@@ -128,6 +128,10 @@ __device__ __forceinline__ void red_inc_shared_if_lt(uint32_t saddr, uint32_t t,
 __device__ __forceinline__ void or_bit_if_ge(uint32_t& w, uint32_t v, uint32_t t, uint32_t bit) {
   asm("{\n\t.reg .pred p;\n\tsetp.ge.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
 }
+// signed compare on raw float bits: negative floats are negative integers
+__device__ __forceinline__ void or_bit_if_ge_s32(uint32_t& w, uint32_t v, int t, uint32_t bit) {
+  asm("{\n\t.reg .pred p;\n\tsetp.ge.s32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
+}
 __device__ __forceinline__ void or_bit_if_eq(uint32_t& w, uint32_t v, uint32_t t, uint32_t bit) {
   asm("{\n\t.reg .pred p;\n\tsetp.eq.u32 p, %1, %2;\n\t@p or.b32 %0, %0, %3;\n\t}" : "+r"(w) : "r"(v), "r"(t), "r"(bit));
 }
@@ -535,6 +539,7 @@ __global__ void __launch_bounds__(576, 1)
       const bool partial = row_ok && take_eq < n_eq;            // ties cut by key index (lowest first)
       const bool warp_partial = __any_sync(0xffffffffu, partial);
       const uint32_t thr_min = partial ? thr + 1u : thr;        // member iff bits >= thr_min (+ chosen ties)
+      const int thr_signed = thr_min == 0u ? static_cast<int>(0x80000000u) : static_cast<int>(thr_min);
       uint32_t eq_seen = 0;
       int cnt = 0;
       int32_t* idx_row = p.idx + grow * p.top_k;
@@ -591,12 +596,14 @@ __global__ void __launch_bounds__(576, 1)
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
+          // Raw scores are staged four to a 16-byte store; membership compares the raw bits as
+          // signed integers (a negative score is a negative integer, below every positive
+          // threshold; a zero threshold admits everything: max(score, 0) >= 0).
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const uint32_t v = relu_bits(r[i]);
-            stage[i * 32 + lane] = v;
-            or_bit_if_ge(w, v, thr_min, 1u << i);
-          }
+          for (int i = 0; i < 32; i += 4)
+            *reinterpret_cast<uint4*>(stage + ((i >> 2) * 32 + lane) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) or_bit_if_ge_s32(w, r[i], thr_signed, 1u << i);
           if (warp_partial) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) or_bit_if_eq(e, relu_bits(r[i]), thr, 1u << i);
@@ -645,7 +652,7 @@ __global__ void __launch_bounds__(576, 1)
           const int i = __ffs(mine) - 1;
           mine &= mine - 1u;
           if (row_ok && off < p.top_k) {
-            const uint32_t v = stage[i * 32 + lane];
+            const uint32_t v = relu_bits(stage[((i >> 2) * 32 + lane) * 4 + (i & 3)]);
             if (ring_ok) {
               ring_i[off & (kRing - 1)] = static_cast<uint32_t>(key0 + i);
               ring_s[off & (kRing - 1)] = v;
