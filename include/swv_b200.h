@@ -72,8 +72,11 @@ int swv_dsa_mask_bytes(int B, int Tq, int Tk, size_t* bytes);
  *   idx    int32  selected key indices in ASCENDING key order,
  *   valid  f32    1.0 for the first min(top_k, Tk) slots, else 0.0,
  *   scores f32    the score of each selected key (0 for unfilled slots).
- * N x N scores never reach memory: four radix passes recompute score tiles on
- * the tensor cores and keep per-row digit histograms on chip.
+ * N x N scores never reach memory: the radix select recomputes score tiles on the
+ * tensor cores in three sweeps (a sampled two-byte pass with an exact check, a
+ * candidate-list pass for the low 16 bits, the emit pass) and keeps per-row
+ * histograms / candidate lists on chip; query tiles whose check fails or whose list
+ * overflows redo the corresponding bytes with plain 8-bit histogram sweeps.
  *   q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID): strides (b,t,h,d); dtype SWV_F32/BF16/F16.
  *   w: (IH,) f32.   ID <= 64.   maskbits: optional (may be NULL) bitmask output
  *   (see swv_dsa_mask_bytes) consumed by swv_dsa_attn_masked_fwd.

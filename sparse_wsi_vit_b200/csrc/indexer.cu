@@ -5,10 +5,12 @@
 //
 // Pipeline (all on the caller's stream):
 //   1. collapse_heads_kernel : wq[t,:] = sum_h W[h] q_idx[t,h,:]  (and wk), fp32, padded to 64.
-//   2. indexer_tiles_kernel<HIST> x 4 : radix select, 8 bits per pass.  Each CTA owns 128
-//      query rows, streams all key tiles through TMA, recomputes the 128x128 score tile with
-//      tcgen05 TF32 MMAs into TMEM, and its epilogue warps keep a 256-bin histogram per row
-//      in shared memory.  After pass p each row knows 8 more bits of its K-th largest score.
+//   2. indexer_tiles_kernel<HIST> : radix select of every row's K-th largest score.  Each CTA owns
+//      128 query rows, streams all key tiles through TMA, recomputes the 128x128 score tile with
+//      tcgen05 TF32 MMAs into TMEM; 16 epilogue warps keep per-row counters in shared memory.
+//        speculative pass : top 16 bits (estimate from a sample of key tiles, exact check);
+//        candidate pass   : low 16 bits and the tie count from a per-row candidate list;
+//        classic passes   : 8 bits each, only for query tiles flagged by the two passes above.
 //   3. indexer_tiles_kernel<EMIT> : recomputes the tiles once more (bit-identical: same
 //      instruction sequence) and writes idx / scores in ascending key order plus the
 //      tile-major membership bitmask.  Ties at the threshold go to the lower key index.
