@@ -45,6 +45,17 @@ constexpr int kQTileBytes = kTile * kHeadDim * 2;     // 16 KiB bf16 tile
 constexpr int kWTileBytes = kTile * kIdxDim * 4;      // 32 KiB fp32 indexer tile (two K halves)
 constexpr int kAttnTmemCols = 512;
 constexpr uint32_t kColR = 0, kColS = 128, kColO = 384;
+constexpr int kSlices = 2;                            // one-pass path: column slices of a tile (warps per row quarter);
+                                                      // 4 (16 softmax warps) measures the same: the tile period is set by
+                                                      // the MMA streams and the exp unit, not by softmax latency
+constexpr int kSoftWarps = 4 * kSlices;               // softmax warps
+constexpr int kSliceCols = kTile / kSlices;
+constexpr int kAttnThreads = 64 + 32 * kSoftWarps + 64;   // TMA, R issuer, softmax warps, two head issuers
+// Packed probabilities of the 16 keys starting at key0 (a multiple of 16) live in 8 columns inside the
+// score columns of the slice that owns those keys, so a thread only overwrites scores it has read.
+__host__ __device__ constexpr uint32_t p_col_of_key(int key0) {
+  return static_cast<uint32_t>((key0 / kSliceCols) * kSliceCols + (key0 % kSliceCols) / 2);
+}
 constexpr float kRescaleStep = 8.0f;                  // raise the stabiliser only in steps of 2^8
 constexpr float kMaxBound = 40.0f;                    // one-pass path: largest admissible |logit| bound (log2 units)
 
@@ -138,7 +149,8 @@ struct SoftmaxRow {
 // Routing weights of tile j for the warp's 64 columns: (score >= thr ? score : 0) as bf16 pairs; R is
 // released as soon as it has been read.
 __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, int j, int lane, float neg_c,
-                                                uint32_t (&w)[32], int* status, volatile uint32_t* abort_flag) {
+                                                uint32_t (&w)[kSliceCols / 2], int* status,
+                                                volatile uint32_t* abort_flag) {
   if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
     record_status(status, kDevWaitAccFull);
     return false;
@@ -147,9 +159,9 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
   uint32_t ra[16], rb[16];
   tmem_ld16(r_col, ra);
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < kSliceCols / 16; ++u) {
     tc_wait_ld();
-    if (u + 1 < 4) {
+    if (u + 1 < kSliceCols / 16) {
       if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
       else tmem_ld16(r_col + (u + 1) * 16, rb);
     }
@@ -169,7 +181,7 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
 // One head's pass over the warp's 64 columns of tile j: p = 2^(s*c - bound) * weight -> TMEM as bf16
 // pairs over the first 32 of those columns, always behind this thread's own reads.
 __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x, int j, int lane, float sc,
-                                             float neg_b, const uint32_t (&wpk)[32], float& l0, float& l1,
+                                             float neg_b, const uint32_t (&wpk)[kSliceCols / 2], float& l0, float& l1,
                                              int* status, volatile uint32_t* abort_flag) {
   if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
     record_status(status, kDevWaitAccFull);
@@ -179,9 +191,9 @@ __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x
   uint32_t sa[16], sb[16];
   tmem_ld16(s_col, sa);
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < kSliceCols / 16; ++u) {
     tc_wait_ld();
-    if (u + 1 < 4) {
+    if (u + 1 < kSliceCols / 16) {
       if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
       else tmem_ld16(s_col + (u + 1) * 16, sb);
     }
@@ -206,21 +218,21 @@ __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x
   return true;
 }
 
-// The two warps of a scheduler (column halves 0 and 1 of the same rows) run the tile in different
-// orders, so that one converts weights (FMA pipe) while the other computes exponentials (exp unit):
-//   half 0:  weights(j)  pass0(j)  pass1(j)
-//   half 1:  pass0(j)  weights(j+1)  pass1(j)
-__device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int half, int nh, int nKT,
+// The warps of a scheduler (column slices of the same rows) run the tile in two different orders, so
+// that some convert weights (FMA pipe) while the others compute exponentials (exp unit):
+//   even slices:  weights(j)  pass0(j)  pass1(j)
+//   odd slices :  pass0(j)  weights(j+1)  pass1(j)
+__device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int slice, int nh, int nKT,
                                                     int lane, float thr, float sc, const float (&bound)[2],
                                                     float (&l_out)[2], int* status,
                                                     volatile uint32_t* abort_flag) {
-  const uint32_t r_col = lane_base + kColR + half * 64;
-  const uint32_t s_col0 = lane_base + kColS + half * 64;      // S columns [64*half, +64) of head 0
+  const uint32_t r_col = lane_base + kColR + slice * kSliceCols;
+  const uint32_t s_col0 = lane_base + kColS + slice * kSliceCols;   // this slice's score columns of head 0
   // -(float just below the threshold) * 2^60; a +inf threshold (tail rows) gives -inf: nothing selected
   const float neg_c = -__uint_as_float(__float_as_uint(thr) - 1u) * 0x1p60f;
   float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  const bool skew = half == 1;
-  uint32_t wa[32], wb[32];
+  const bool skew = (slice & 1) != 0;
+  uint32_t wa[kSliceCols / 2], wb[kSliceCols / 2];
   if (skew && !convert_weights(ctl, r_col, 0, lane, neg_c, wa, status, abort_flag)) return false;
   for (int j = 0; j < nKT; ++j) {
     if (!skew && !convert_weights(ctl, r_col, j, lane, neg_c, wa, status, abort_flag)) return false;
@@ -231,7 +243,7 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
       return false;
     if (skew) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) wa[i] = wb[i];
+      for (int i = 0; i < kSliceCols / 2; ++i) wa[i] = wb[i];
     }
   }
   l_out[0] = l[0][0] + l[0][1];
@@ -239,8 +251,8 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   return true;
 }
 
-// One warp per (head, 32 rows), all 128 columns.  The barriers count eight arrivals (the
-// column-split layout): a warp arrives `r_arrivals` times on r_free and twice on p_full.
+// One warp per (head, 32 rows), all 128 columns.  The barriers count one arrival per softmax warp
+// of the column-split layout: a warp arrives `r_arrivals` times on r_free and kSlices times on p_full.
 __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl, int x, int nKT, int lane,
                                                     int r_arrivals, int* status, volatile uint32_t* abort_flag) {
   const float ninf = -__int_as_float(0x7f800000);
@@ -321,8 +333,7 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
         l1 += p1;
         packed[i >> 1] = pack_bf16x2(p0, p1);
       }
-      // probabilities of keys 0..63 in columns [0,32), of keys 64..127 in columns [64,96)
-      tmem_st8(s_col + (u & 3) * 8 + (u >> 2) * 64, packed);
+      tmem_st8(s_col + p_col_of_key(u * 16), packed);
     }
     st.l += l0 + l1;
     tc_fence_before();
@@ -331,7 +342,7 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
     tc_wait_st();
     tc_fence_before();
     __syncwarp();
-    if (lane < 2) mbar_arrive(&ctl->p_full[x]);
+    if (lane < kSlices) mbar_arrive(&ctl->p_full[x]);
     mw = mw_next;
   }
   return true;
@@ -371,7 +382,7 @@ __global__ void key_norm_max_kernel(const __nv_bfloat16* __restrict__ k, int64_t
   }
 }
 
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(kAttnThreads, 1)
     dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
                            const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                            const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
@@ -395,14 +406,14 @@ __global__ void __launch_bounds__(384, 1)
   if (threadIdx.x == 0) {
     mbar_init(&ctl->q_full, 1);
     mbar_init(&ctl->r_full, 1);
-    mbar_init(&ctl->r_free, 8);
+    mbar_init(&ctl->r_free, kSoftWarps);
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl->wk_full[s], 1);
       mbar_init(&ctl->wk_empty[s], 1);
       mbar_init(&ctl->v_full[s], 1);
       mbar_init(&ctl->v_empty[s], 1);
       mbar_init(&ctl->s_full[s], 1);
-      mbar_init(&ctl->p_full[s], 8);
+      mbar_init(&ctl->p_full[s], kSoftWarps);
       mbar_init(&ctl->pv_done[s], 1);
       for (int t = 0; t < 2; ++t) {
         mbar_init(&ctl->k_full[s][t], 1);
@@ -510,9 +521,9 @@ __global__ void __launch_bounds__(384, 1)
         umma_commit(&ctl->r_full);
       }
     }
-  } else if (warp >= 10) {
+  } else if (warp >= 2 + kSoftWarps) {
     // ------------------------------------- MMA issuer of one head: S_x(j) and O_x += P_x(j) V_x(j)
-    const int x = warp - 10;
+    const int x = warp - (2 + kSoftWarps);
     if (lane == 0 && x < nh) {
       const uint32_t q_addr = smem_u32(smem + kOffQ + x * kQTileBytes);
       const uint32_t k_addr = smem_u32(smem + kOffK + x * 2 * kQTileBytes);
@@ -536,7 +547,7 @@ __global__ void __launch_bounds__(384, 1)
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks)   // 16 keys per step: 8 packed P columns, 2 KiB of V rows
-            umma_f16_ts(o_col, s_col + (ks & 3) * 8 + (ks >> 2) * 64, dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
+            umma_f16_ts(o_col, s_col + p_col_of_key(ks * 16), dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
           umma_commit(&ctl->v_empty[x]);
           umma_commit(&ctl->pv_done[x]);
         }
@@ -557,7 +568,7 @@ __global__ void __launch_bounds__(384, 1)
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    const int half = (warp - 2) >> 2;           // one-pass layout: column half; two-pass layout: head of the pair
+    const int slice = (warp - 2) >> 2;          // one-pass layout: column slice; two-pass layout: slices 0, 1 = head
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int qrow = qt * kTile + row;
@@ -600,55 +611,63 @@ __global__ void __launch_bounds__(384, 1)
       flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow] && thr_ge >= 4e-6f && small);
     }
     if (__any_sync(0xffffffffu, flagged) && lane == 0) atomicOr(&ctl->cta_exact, 1u);
-    asm volatile("bar.sync 2, 256;" ::: "memory");
+    asm volatile("bar.sync 2, %0;" ::"r"(32 * kSoftWarps) : "memory");
     const bool exact = *reinterpret_cast<volatile uint32_t*>(&ctl->cta_exact) != 0u;
 
-    const int x = half;                           // head whose output rows this thread writes
+    // Output duty.  One-pass layout: slice s writes head s % 2, channels [d0, d0 + nd) with the 64
+    // channels of a head divided among the slices that share it; two-pass layout: slices 0 and 1
+    // write all channels of their head, the other slices idle.
+    constexpr int kParts = kSlices / 2;
+    const int x = slice & 1;                      // head whose output rows this thread writes
     const int h = h0 + x;
-    const uint32_t o_col = lane_base + kColO + x * kHeadDim;
+    const int d0 = exact ? 0 : (slice >> 1) * (kHeadDim / kParts);
+    const int nd = exact ? (slice < 2 ? kHeadDim : 0) : kHeadDim / kParts;
+    const uint32_t o_col = lane_base + kColO + x * kHeadDim + d0;
     bool ok = true;
     float inv = 0.f;
     if (!exact) {
       float l_part[2];
-      ok = softmax_tiles_split(ctl, lane_base, half, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, p.status,
+      ok = softmax_tiles_split(ctl, lane_base, slice, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, p.status,
                                abort_flag);
-      // The two column halves of a row add their partial sums through the indexer-query tile:
+      // The column slices of a row add their partial sums through the indexer-query tile:
       // every routing-weight MMA that read it has retired once any warp has left its loop.
-      float* lsum = reinterpret_cast<float*>(smem + kOffWq);      // [2 heads][128 rows][2 halves]
-      lsum[(0 * kTile + row) * 2 + half] = l_part[0];
-      lsum[(1 * kTile + row) * 2 + half] = l_part[1];
-      asm volatile("bar.sync 2, 256;" ::: "memory");
-      inv = 1.f / (lsum[(x * kTile + row) * 2] + lsum[(x * kTile + row) * 2 + 1]);   // the clamp cannot bind
-    } else if (x < nh) {
+      float* lsum = reinterpret_cast<float*>(smem + kOffWq);      // [2 heads][128 rows][kSlices]
+      lsum[(0 * kTile + row) * kSlices + slice] = l_part[0];
+      lsum[(1 * kTile + row) * kSlices + slice] = l_part[1];
+      asm volatile("bar.sync 2, %0;" ::"r"(32 * kSoftWarps) : "memory");
+      float lt = 0.f;
+#pragma unroll
+      for (int i = 0; i < kSlices; ++i) lt += lsum[(x * kTile + row) * kSlices + i];
+      inv = 1.f / lt;                             // the clamp cannot bind
+    } else if (slice < 2 && x < nh) {
       SoftmaxRow st;
       st.lane_base = lane_base;
       st.s_col = lane_base + kColS + x * kTile;
-      st.o_col = o_col;
+      st.o_col = lane_base + kColO + x * kHeadDim;
       st.mask_tile =
           reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
       st.sc = p.scale_log2;
       st.m_true = st.m_used = -__int_as_float(0x7f800000);
       st.l = 0.f;
-      ok = softmax_tiles_exact(st, ctl, x, nKT, lane, 2 / nh, p.status, abort_flag);
+      ok = softmax_tiles_exact(st, ctl, x, nKT, lane, kSoftWarps / (4 * nh), p.status, abort_flag);
       // the reference's clamp: out = O c / max(l c, 1e-6), c = 2^(m_used - m_true)
       const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
       inv = corr / fmaxf(st.l * corr, 1e-6f);
     }
-    if (x < nh) {
+    if (x < nh && nd > 0) {
       if (ok && !mbar_wait_bounded(&ctl->pv_done[x], (nKT - 1) & 1, abort_flag)) {
         record_status(p.status, kDevWaitPvDone);
         ok = false;
       }
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < nd / 16; ++c) {
           uint32_t o[16];
           tmem_ld16(o_col + c * 16, o);
           tc_wait_ld();
           if (!row_ok) continue;
           if (p.o_dtype == SWV_F32) {
-            float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
+            float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
               *reinterpret_cast<float4*>(orow + i) =
@@ -656,7 +675,7 @@ __global__ void __launch_bounds__(384, 1)
                               __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
             }
           } else {
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
+            uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
 #pragma unroll
             for (int i = 0; i < 16; i += 8) {
               uint32_t w4[4];
@@ -757,7 +776,7 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(attn_smem_bytes())));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP;
-  dsa_attn_masked_kernel<<<grid, 384, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  dsa_attn_masked_kernel<<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }

@@ -569,7 +569,6 @@ int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win,
 //   window branch    : the 128-token blocks that intersect [q0 - reach, q1 + reach].
 __global__ void nsa_build_lists_kernel(int n_qb, int n_cb, int T, int reach, int32_t* full_ptr, int32_t* full_col,
                                        int32_t* win_ptr, int32_t* win_col) {
-  __shared__ int total;
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int i = 0; i < n_qb; ++i) {
@@ -581,7 +580,6 @@ __global__ void nsa_build_lists_kernel(int n_qb, int n_cb, int T, int reach, int
     }
     full_ptr[n_qb] = n_qb * n_cb;
     win_ptr[n_qb] = acc;
-    total = acc;
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n_qb * n_cb; i += blockDim.x) full_col[i] = i % n_cb;
@@ -590,7 +588,6 @@ __global__ void nsa_build_lists_kernel(int n_qb, int n_cb, int T, int reach, int
     const int n = win_ptr[i + 1] - win_ptr[i];
     for (int j = 0; j < n; ++j) win_col[win_ptr[i] + j] = lo + j;
   }
-  (void)total;
 }
 
 int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, int T, int D, int win, int stride,
