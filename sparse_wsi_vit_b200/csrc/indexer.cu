@@ -546,10 +546,12 @@ __global__ void __launch_bounds__(576, 1)
       int cnt = 0;
       int32_t* idx_row = p.idx + grow * p.top_k;
       float* sc_row = p.scores + grow * p.top_k;
-      uint32_t* stage = sm_hist + ew * (32 * 32);              // the staging tiles share the histogram's slot
-      uint2* xchg = reinterpret_cast<uint2*>(sm_hist + kEpiWarps * (32 * 32));   // [2][128 rows][4 quarters]
-      uint32_t* ring_i = reinterpret_cast<uint32_t*>(xchg + 2 * kTile * 4) + row * kRingStride;
-      uint32_t* ring_s = ring_i + kTile * kRingStride;
+      // 32-bit shared addresses: the staging tiles share the histogram's slot, then the exchange
+      // words [2][128 rows][4 quarters] x 8 B, then the two rings
+      const uint32_t stage = smem_u32(sm_hist) + static_cast<uint32_t>(ew * (32 * 32) + lane * 4) * 4u;
+      const uint32_t xchg = smem_u32(sm_hist) + static_cast<uint32_t>(kEpiWarps * (32 * 32)) * 4u;
+      const uint32_t ring_i = xchg + 2u * kTile * 4u * 8u + static_cast<uint32_t>(row * kRingStride) * 4u;
+      const uint32_t ring_s = ring_i + static_cast<uint32_t>(kTile * kRingStride) * 4u;
       const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.scores)) & 15) == 0 &&
                           (p.top_k & 3) == 0;
       int flushed = 0;                                          // entries of the row already in global memory
@@ -561,8 +563,8 @@ __global__ void __launch_bounds__(576, 1)
             uint32_t vi[8], vs[8];
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
-              vi[t] = ring_i[(e + t) & (kRing - 1)];
-              vs[t] = ring_s[(e + t) & (kRing - 1)];
+              vi[t] = lds32(ring_i + (((e + t) & (kRing - 1)) << 2));
+              vs[t] = lds32(ring_s + (((e + t) & (kRing - 1)) << 2));
             }
             *reinterpret_cast<uint4*>(idx_row + e) = make_uint4(vi[0], vi[1], vi[2], vi[3]);
             *reinterpret_cast<uint4*>(idx_row + e + 4) = make_uint4(vi[4], vi[5], vi[6], vi[7]);
@@ -570,8 +572,8 @@ __global__ void __launch_bounds__(576, 1)
             *reinterpret_cast<uint4*>(sc_row + e + 4) = make_uint4(vs[4], vs[5], vs[6], vs[7]);
             e += 8;
           } else {
-            idx_row[e] = static_cast<int32_t>(ring_i[e & (kRing - 1)]);
-            sc_row[e] = __uint_as_float(ring_s[e & (kRing - 1)]);
+            idx_row[e] = static_cast<int32_t>(lds32(ring_i + ((e & (kRing - 1)) << 2)));
+            sc_row[e] = __uint_as_float(lds32(ring_s + ((e & (kRing - 1)) << 2)));
             ++e;
           }
         }
@@ -603,7 +605,7 @@ __global__ void __launch_bounds__(576, 1)
           // threshold; a zero threshold admits everything: max(score, 0) >= 0).
 #pragma unroll
           for (int i = 0; i < 32; i += 4)
-            *reinterpret_cast<uint4*>(stage + ((i >> 2) * 32 + lane) * 4) = make_uint4(r[i], r[i + 1], r[i + 2], r[i + 3]);
+            sts128(stage + static_cast<uint32_t>((i >> 2) * 32 * 16), r[i], r[i + 1], r[i + 2], r[i + 3]);
 #pragma unroll
           for (int i = 0; i < 32; ++i) or_bit_if_ge_s32(w, r[i], thr_signed, 1u << i);
           if (warp_partial) {
@@ -617,11 +619,11 @@ __global__ void __launch_bounds__(576, 1)
             e &= vm;
           }
         }
-        uint2* x = xchg + (a * kTile + row) * 4;
-        x[ch] = make_uint2(w, e);
+        const uint32_t x = xchg + static_cast<uint32_t>((a * kTile + row) * 4) * 8u;
+        sts64(x + ch * 8, w, e);
         asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
-        const uint4 x01 = *reinterpret_cast<const uint4*>(x);
-        const uint4 x23 = *reinterpret_cast<const uint4*>(x + 2);
+        const uint4 x01 = lds128(x);
+        const uint4 x23 = lds128(x + 16);
         uint32_t fw[4] = {x01.x, x01.z, x23.x, x23.z};
         if (partial) {
           const uint32_t ee[4] = {x01.y, x01.w, x23.y, x23.w};
@@ -654,10 +656,10 @@ __global__ void __launch_bounds__(576, 1)
           const int i = __ffs(mine) - 1;
           mine &= mine - 1u;
           if (row_ok && off < p.top_k) {
-            const uint32_t v = relu_bits(stage[((i >> 2) * 32 + lane) * 4 + (i & 3)]);
+            const uint32_t v = relu_bits(lds32(stage + static_cast<uint32_t>((i >> 2) * 32 * 16 + (i & 3) * 4)));
             if (ring_ok) {
-              ring_i[off & (kRing - 1)] = static_cast<uint32_t>(key0 + i);
-              ring_s[off & (kRing - 1)] = v;
+              sts32(ring_i + ((off & (kRing - 1)) << 2), static_cast<uint32_t>(key0 + i));
+              sts32(ring_s + ((off & (kRing - 1)) << 2), v);
             } else {
               idx_row[off] = key0 + i;
               sc_row[off] = __uint_as_float(v);
