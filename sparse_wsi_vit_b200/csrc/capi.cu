@@ -9,7 +9,7 @@ int dsa_mask_bytes_impl(int B, int Tq, int Tk, size_t* bytes);
 int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks, int dtype,
                           const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
                           float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
-                          int* status, cudaStream_t st);
+                          int* status, cudaStream_t st, bool allow_split);
 int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
                                  int dtype, const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k,
                                  int32_t* idx, float* valid, float* scores, uint32_t* maskbits, int* status,
@@ -91,7 +91,7 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
                              void* stream) {
   return swv::dsa_indexer_topk_impl(q_idx, q_strides, k_idx, k_strides, idx_dtype, w, B, Tq, Tk, IH, ID, top_k, idx,
                                     valid, scores, maskbits, workspace, workspace_bytes, status,
-                                    static_cast<cudaStream_t>(stream));
+                                    static_cast<cudaStream_t>(stream), /*allow_split=*/true);
 }
 
 // The variant for callers that cannot allocate: the scratch is a fixed device array inside the

@@ -84,6 +84,17 @@ struct IndexerParams {
   uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
   uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
   uint32_t* st_neq;       // [B*Tq] after the last pass: number of keys whose score equals the threshold
+  // Key-range split: with few query tiles (a rank of a sequence-sharded run) `split` = 2 CTAs share
+  // a query tile, each sweeping half of the key tiles; the part that finishes last merges.
+  int split, nKT0;               // CTAs per query tile; key tiles of part 0
+  const uint32_t* flags_spec;    // [tiles] speculative pass failed: the candidate pass runs unsplit
+  uint32_t* flags_unsplit;       // [tiles] written by the candidate pass: emit runs unsplit
+  uint32_t* tickets;             // [tiles] arrival counter of a tile's parts (reset by the last one)
+  uint32_t* ghist;               // [tiles][2][kTile * kHistStride] per-part window histograms
+  uint16_t* glist;               // [tiles][2][kTile * kListStride] per-part candidate lists
+  uint32_t* gcnt;                // [tiles][2][kTile] per-part candidate counts
+  uint32_t* st_cnt0;             // [B*Tq] selected keys of the row strictly above the threshold in part 0's range
+  uint32_t* st_eq0;              // [B*Tq] keys equal to the threshold in part 0's range
   int32_t* idx;           // EMIT outputs
   float* scores;
   uint32_t* maskbits;     // may be null
@@ -99,6 +110,7 @@ struct TileSmemCtl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t overflow;
+  uint32_t ticket;
 };
 
 // EMIT: per epilogue warp a [32 columns][32 lanes] word tile, then the row exchange [2][128][4] x 8 B,
@@ -190,16 +202,29 @@ __global__ void __launch_bounds__(576, 1)
   TileSmemCtl* ctl = reinterpret_cast<TileSmemCtl*>(smem + kTileBytes * (1 + kStages) +
                                                     (MODE == kModeHist ? kHistBytes : kStageBytes));
 
-  if (MODE == kModeHist && p.only_flagged != 0 && p.flags_in[blockIdx.x] == 0u) return;
+  const int tile = blockIdx.x / p.split;         // (batch, query tile)
+  const int part = blockIdx.x - tile * p.split;  // which share of the key range
+  if (MODE == kModeHist && p.only_flagged != 0 && p.flags_in[tile] == 0u) return;
+  // Which launches split the key range: the speculative pass always; the candidate pass unless the
+  // speculative pass failed for the tile; emit unless the candidate pass said otherwise; the
+  // classic histogram passes never.  An unsplit tile is swept by part 0 alone.
+  bool use_split = false;
+  if (p.split > 1) {
+    if (MODE == kModeEmit) use_split = p.flags_unsplit[tile] == 0u;
+    else if (p.kind == kKindSpec) use_split = true;
+    else if (p.kind == kKindCand) use_split = p.flags_spec[tile] == 0u;
+    if (!use_split && part != 0) return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int b = blockIdx.x / p.nQT;
-  const int qt = blockIdx.x % p.nQT;
-  const int nKT = p.nKT;
+  const int b = tile / p.nQT;
+  const int qt = tile % p.nQT;
+  const int kt0 = (use_split && part == 1) ? p.nKT0 : 0;                 // first key tile of this CTA
+  const int nKT = (use_split ? (part == 0 ? p.nKT0 : p.nKT - p.nKT0) : p.nKT);   // key tiles of this CTA
   // The speculative pass first streams a sample of nSample key tiles twice (top byte, then second
-  // byte of every row's estimated threshold), then the whole key range.
-  const int nSample = (MODE == kModeHist && p.kind == kKindSpec) ? min(nKT, kSampleTiles) : 0;
+  // byte of every row's estimated threshold; the same tiles for every part), then its key range.
+  const int nSample = (MODE == kModeHist && p.kind == kKindSpec) ? min(p.nKT, kSampleTiles) : 0;
   const int nPre = 2 * nSample;
   const int nIt = nKT + nPre;
 
@@ -236,7 +261,7 @@ __global__ void __launch_bounds__(576, 1)
       tma_load_3d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, b);
       tma_load_3d(sm_q + kTileBytes / 2, &tm_q, &ctl->q_full, 32, qt * kTile, b);
       for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? (it < nSample ? it : it - nSample) : it - nPre;
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) : kt0 + it - nPre;
         const int s = it % kStages;
         if (!mbar_wait_bounded(&ctl->k_empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
@@ -305,7 +330,7 @@ __global__ void __launch_bounds__(576, 1)
       const uint32_t k_eff = static_cast<uint32_t>(min(p.top_k, p.Tk));
       uint32_t zeros = 0, lo = 0, rank = 1, est_hi = 0;
       for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? (it < nSample ? it : it - nSample) : it - nPre;
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) : kt0 + it - nPre;
         const int a = it & 1;
         if (it == nSample || it == nPre) {
           // ---- end of a sample round: take the digit that holds the scaled rank, clear the histogram
@@ -363,6 +388,29 @@ __global__ void __launch_bounds__(576, 1)
         }
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
+      // Split key range: every part publishes its histogram; the part that arrives last adds the
+      // other one's to its own and finishes the tile (the estimate, hence the window, is the same
+      // in both parts: it comes from the same sample tiles).
+      bool finisher = true;
+      const uint32_t* h0_row = nullptr;          // part 0's histogram of this row (global), for the part-0 count
+      if (use_split) {
+        uint32_t* gh = p.ghist + (static_cast<size_t>(tile) * 2 + part) * (kTile * kHistStride);
+        for (int i = et; i < kTile * kHistStride; i += 512) gh[i] = sm_hist[i];
+        __threadfence();
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        if (et == 0) ctl->ticket = atomicAdd(p.tickets + tile, 1u);
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        finisher = ctl->ticket == static_cast<uint32_t>(p.split - 1);
+        if (finisher) {
+          __threadfence();
+          if (et == 0) p.tickets[tile] = 0u;
+          const uint32_t* go = p.ghist + (static_cast<size_t>(tile) * 2 + (1 - part)) * (kTile * kHistStride);
+          for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] += __ldcg(go + i);
+          h0_row = p.ghist + static_cast<size_t>(tile) * 2 * (kTile * kHistStride) + row * kHistStride;
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+        }
+      }
+      if (finisher) {
       bool row_valid = true;
       uint32_t digit = 0, cum = 0, kth = 0;
       if (ch == 0 && row_ok) {
@@ -385,10 +433,17 @@ __global__ void __launch_bounds__(576, 1)
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
       const bool redo = ctl->overflow != 0u || !ok || *abort_flag != 0u;
-      if (et == 0) p.flags_out[blockIdx.x] = redo ? 1u : 0u;
+      if (et == 0) p.flags_out[tile] = redo ? 1u : 0u;
       if (!redo && ch == 0 && row_ok) {
         p.st_prefix[grow] = (lo >> 16) + digit;
         p.st_kth[grow] = kth - cum;
+        if (h0_row != nullptr) {
+          // keys of part 0's range whose top 16 bits lie above the threshold's
+          uint32_t above0 = __ldcg(h0_row + 257);
+          for (int bin = 255; bin > static_cast<int>(digit); --bin) above0 += __ldcg(h0_row + 1 + bin);
+          p.st_cnt0[grow] = above0;
+        }
+      }
       }
     } else if (MODE == kModeHist && p.kind == kKindCand) {
       // Candidate pass: the top 16 bits of every row's threshold are known.  The low 16 bits of
@@ -419,7 +474,7 @@ __global__ void __launch_bounds__(576, 1)
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->acc_empty[a]);
-        const int nvalid = p.Tk - (j * kTile + ch * 32);
+        const int nvalid = p.Tk - ((kt0 + j) * kTile + ch * 32);
         // two instances of the scan: the bounds test only exists for the ragged last key tile
         auto scan = [&](auto check) {
           constexpr bool kCheck = decltype(check)::value;
@@ -446,11 +501,45 @@ __global__ void __launch_bounds__(576, 1)
         else scan(std::true_type{});
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
-      const uint32_t n = cnt[row];
+      uint32_t n = cnt[row];
+      uint32_t n0 = 0;                           // entries [0, n0) of the row's list come from part 0's key range
+      bool finisher = true;
+      if (use_split) {
+        // every part publishes its lists; the part that arrives last reloads both (part 0's first)
+        uint16_t* gl = p.glist + (static_cast<size_t>(tile) * 2 + part) * (kTile * kListStride) + row * kListStride;
+        const uint32_t n_own = min(n, static_cast<uint32_t>(kListCap));
+        for (uint32_t i = ch; i < n_own; i += 4) gl[i] = lrow[i];
+        if (ch == 0) p.gcnt[(static_cast<size_t>(tile) * 2 + part) * kTile + row] = n;
+        __threadfence();
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        if (et == 0) ctl->ticket = atomicAdd(p.tickets + tile, 1u);
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        finisher = ctl->ticket == static_cast<uint32_t>(p.split - 1);
+        if (finisher) {
+          __threadfence();
+          if (et == 0) p.tickets[tile] = 0u;
+          const uint32_t c0 = __ldcg(p.gcnt + (static_cast<size_t>(tile) * 2 + 0) * kTile + row);
+          const uint32_t c1 = __ldcg(p.gcnt + (static_cast<size_t>(tile) * 2 + 1) * kTile + row);
+          n = c0 + c1;
+          if (c0 > kListCap || c1 > kListCap) n = kListCap + 1;     // a part overflowed
+          n0 = c0;
+          if (n <= kListCap) {
+            const uint16_t* g0 = p.glist + (static_cast<size_t>(tile) * 2 + 0) * (kTile * kListStride) + row * kListStride;
+            const uint16_t* g1 = g0 + kTile * kListStride;
+            for (uint32_t i = ch; i < c0; i += 4) lrow[i] = __ldcg(g0 + i);
+            for (uint32_t i = ch; i < c1; i += 4) lrow[c0 + i] = __ldcg(g1 + i);
+          }
+          asm volatile("bar.sync 1, 512;" ::: "memory");
+        }
+      }
+      if (finisher) {
       if (ch == 0 && row_ok && n > kListCap) atomicOr(&ctl->overflow, 1u);
       asm volatile("bar.sync 1, 512;" ::: "memory");
       const bool tile_overflow = ctl->overflow != 0u;
-      if (et == 0) p.flags_out[blockIdx.x] = tile_overflow ? 1u : 0u;
+      if (et == 0) {
+        p.flags_out[tile] = tile_overflow ? 1u : 0u;
+        if (p.split > 1) p.flags_unsplit[tile] = (tile_overflow || !use_split) ? 1u : 0u;
+      }
       if (ok && ch == 0 && row_ok && !tile_overflow && *abort_flag == 0u) {
         uint32_t kth = p.st_kth[grow];
         uint32_t val = 0;
@@ -466,6 +555,18 @@ __global__ void __launch_bounds__(576, 1)
         p.st_prefix[grow] = lo | val;
         p.st_kth[grow] = kth;
         p.st_neq[grow] = n_eq;
+        if (use_split) {
+          // part 0's share: candidates above the threshold (added to the keys above the bucket
+          // that the speculative pass counted) and candidates equal to it
+          uint32_t in0 = 0, eq0 = 0;
+          for (uint32_t i = 0; i < n0; ++i) {
+            in0 += (lrow[i] > val) ? 1u : 0u;
+            eq0 += (lrow[i] == val) ? 1u : 0u;
+          }
+          p.st_cnt0[grow] += in0;
+          p.st_eq0[grow] = eq0;
+        }
+      }
       }
     } else if constexpr (MODE == kModeHist) {
       const int ch = ew >> 2;                // column quarter 0..3 (32 columns each)
@@ -542,8 +643,15 @@ __global__ void __launch_bounds__(576, 1)
       const bool warp_partial = __any_sync(0xffffffffu, partial);
       const uint32_t thr_min = partial ? thr + 1u : thr;        // member iff bits >= thr_min (+ chosen ties)
       const int thr_signed = thr_min == 0u ? static_cast<int>(0x80000000u) : static_cast<int>(thr_min);
+      // A second part starts behind part 0's share of the row: the keys above the threshold in part
+      // 0's range plus the ties part 0 takes (ties are taken in ascending key order).
       uint32_t eq_seen = 0;
       int cnt = 0;
+      if (use_split && part == 1 && row_ok) {
+        eq_seen = min(p.st_eq0[grow], partial ? take_eq : 0xFFFFFFFFu);
+        cnt = static_cast<int>(p.st_cnt0[grow] + eq_seen);
+        if (!partial) eq_seen = 0;
+      }
       int32_t* idx_row = p.idx + grow * p.top_k;
       float* sc_row = p.scores + grow * p.top_k;
       // 32-bit shared addresses: the staging tiles share the histogram's slot, then the exchange
@@ -554,7 +662,7 @@ __global__ void __launch_bounds__(576, 1)
       const uint32_t ring_s = ring_i + static_cast<uint32_t>(kTile * kRingStride) * 4u;
       const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.scores)) & 15) == 0 &&
                           (p.top_k & 3) == 0;
-      int flushed = 0;                                          // entries of the row already in global memory
+      int flushed = cnt;                                        // entries of the row below this index are not this CTA's to write
       // entries [from, to) of the row leave the ring
       auto flush = [&](int from, int to) {
         int e = from;
@@ -581,7 +689,7 @@ __global__ void __launch_bounds__(576, 1)
       uint4* mask_row = nullptr;
       if (p.maskbits != nullptr) {
         mask_row = reinterpret_cast<uint4*>(p.maskbits) +
-                   (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
+                   ((static_cast<int64_t>(b) * p.nQT + qt) * p.nKT + kt0) * kTile + row;
       }
       for (int j = 0; j < nKT; ++j) {
         const int a = j & 1;
@@ -591,7 +699,7 @@ __global__ void __launch_bounds__(576, 1)
           ok = false;
         }
         uint32_t w = 0, e = 0;
-        const int key0 = j * kTile + ch * 32;
+        const int key0 = (kt0 + j) * kTile + ch * 32;
         if (ok) {
           tc_fence_after();
           uint32_t r[32];
@@ -706,8 +814,20 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, flags2_off, total;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, flags2_off;
+  size_t flags3_off, tickets_off, cnt0_off, eq0_off, ghist_off, glist_off, gcnt_off;   // key-range split only
+  int split;
+  size_t total;
 };
+// Two CTAs share a query tile (each sweeps half of the key tiles) when the query tiles alone
+// would leave more than half of the SMs idle -- the situation of one rank of a sequence-sharded
+// run -- and the key range is long enough to be worth merging.
+constexpr int kSplitMaxTiles = 74;     // half of the 148 SMs
+constexpr int kSplitMinKeyTiles = 64;
+static int split_factor(int B, int Tq, int Tk) {
+  const int64_t tiles = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile);
+  return (tiles <= kSplitMaxTiles && (Tk + kTile - 1) / kTile >= kSplitMinKeyTiles) ? 2 : 1;
+}
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
   size_t off = 0;
@@ -723,10 +843,29 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.kmax_off = off;     // per (batch, head) key-norm maxima of the attention kernel, up to 1024 entries
   off += 4096;
+  const size_t tiles = static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile);
   L.flags_off = off;    // per 128-query tile: redo the two first passes classically
-  off += align_up(static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * 4, 1024);
+  off += align_up(tiles * 4, 1024);
   L.flags2_off = off;   // per 128-query tile: redo the two last passes classically
-  off += align_up(static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * 4, 1024);
+  off += align_up(tiles * 4, 1024);
+  L.split = split_factor(B, Tq, Tk);
+  L.flags3_off = L.tickets_off = L.cnt0_off = L.eq0_off = L.ghist_off = L.glist_off = L.gcnt_off = off;
+  if (L.split > 1) {
+    L.flags3_off = off;   // per tile: emit runs unsplit
+    off += align_up(tiles * 4, 1024);
+    L.tickets_off = off;
+    off += align_up(tiles * 4, 1024);
+    L.cnt0_off = off;
+    off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+    L.eq0_off = off;
+    off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+    L.ghist_off = off;
+    off += align_up(tiles * 2 * kTile * kHistStride * 4, 1024);
+    L.glist_off = off;
+    off += align_up(tiles * 2 * kTile * kListStride * 2, 1024);
+    L.gcnt_off = off;
+    off += align_up(tiles * 2 * kTile * 4, 1024);
+  }
   L.total = off;
   return L;
 }
@@ -772,13 +911,17 @@ int dsa_mask_bytes_impl(int B, int Tq, int Tk, size_t* bytes) {
 int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks, int dtype,
                           const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
                           float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
-                          int* status, cudaStream_t st) {
+                          int* status, cudaStream_t st, bool allow_split) {
   if (!q_idx || !k_idx || !w || !idx || !valid || !scores || !workspace || !status || !qs || !ks)
     return SWV_ERR_NULL;
   if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
   if (B < 1 || Tq < 1 || Tk < 1 || IH < 1 || ID < 1 || top_k < 1) return SWV_ERR_SHAPE;
   if (ID > kIdxDim) return SWV_ERR_UNSUPPORTED;
-  const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
+  WorkspaceLayout L = workspace_layout(B, Tq, Tk);
+  if (!allow_split && L.split > 1) {
+    L.split = 1;
+    L.total = L.flags3_off;      // the split regions are the tail of the layout
+  }
   if (workspace_bytes < L.total) return SWV_ERR_WORKSPACE;
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SWV_ERR_ALIGN;
   if ((reinterpret_cast<uintptr_t>(idx) & 3) || (reinterpret_cast<uintptr_t>(scores) & 3) ||
@@ -820,14 +963,26 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   uint32_t* flags_a = reinterpret_cast<uint32_t*>(ws + L.flags_off);
   uint32_t* flags_b = reinterpret_cast<uint32_t*>(ws + L.flags2_off);
   p.flags_in = flags_a; p.flags_out = flags_a;
+  p.split = L.split;
+  p.nKT0 = (p.nKT + 1) / 2;
+  p.flags_spec = flags_a;
+  p.flags_unsplit = reinterpret_cast<uint32_t*>(ws + L.flags3_off);
+  p.tickets = reinterpret_cast<uint32_t*>(ws + L.tickets_off);
+  p.st_cnt0 = reinterpret_cast<uint32_t*>(ws + L.cnt0_off);
+  p.st_eq0 = reinterpret_cast<uint32_t*>(ws + L.eq0_off);
+  p.ghist = reinterpret_cast<uint32_t*>(ws + L.ghist_off);
+  p.glist = reinterpret_cast<uint16_t*>(ws + L.glist_off);
+  p.gcnt = reinterpret_cast<uint32_t*>(ws + L.gcnt_off);
+  if (L.split > 1)
+    SWV_CUDA_OK(cudaMemsetAsync(p.tickets, 0, static_cast<size_t>(B) * p.nQT * 4, st));
 
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeHist>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeHist))));
   SWV_CUDA_OK(cudaFuncSetAttribute(indexer_tiles_kernel<kModeEmit>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(tile_smem_bytes(kModeEmit))));
-  const unsigned grid = static_cast<unsigned>(B) * p.nQT;
+  const unsigned grid = static_cast<unsigned>(B) * p.nQT * L.split;
   // Radix select of every row's K-th largest score, 32 bits:
-  //   bytes 0-1: one speculative fused pass (top byte guessed from a sample, checked with exact
+  //   bytes 0-1: one speculative fused pass (top 16 bits estimated from a sample, checked with exact
   //              counts); query tiles where the check fails redo the two classic histogram passes;
   //   bytes 2-3: one candidate-list pass; tiles whose list overflowed (massive ties) redo the two
   //              classic histogram passes.
@@ -873,7 +1028,7 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
   if (B < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (static_cast<int64_t>(B) * Tq > kStaticMaxTokens || static_cast<int64_t>(B) * Tk > kStaticMaxTokens)
     return SWV_ERR_TOO_LARGE;
-  if (workspace_layout(B, Tq, Tk).total > kStaticScratchBytes) return SWV_ERR_TOO_LARGE;
+  if (workspace_layout(B, Tq, Tk).flags3_off > kStaticScratchBytes) return SWV_ERR_TOO_LARGE;
   // In host code `g_static_scratch` names a host-side stand-in, not device memory: the device
   // address has to be asked for, once per device, with that device current.
   constexpr int kMaxDevices = 64;
@@ -887,7 +1042,7 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
     dev_ptr[dev] = ptr;
   }
   return dsa_indexer_topk_impl(q_idx, qs, k_idx, ks, dtype, w, B, Tq, Tk, IH, ID, top_k, idx, valid, scores, maskbits,
-                               dev_ptr[dev], kStaticScratchBytes, status, st);
+                               dev_ptr[dev], kStaticScratchBytes, status, st, /*allow_split=*/false);
 }
 
 }  // namespace swv

@@ -235,3 +235,56 @@ def test_benchmark_config_sampled_rows(swv):
     oidx, _, _ = O.topk_lower_index(s_ref, K)
     assert overlap_fraction(ridx, oidx, T) > 0.99
     _check(swv)
+
+
+def test_indexer_split_key_range(swv):
+    """Few query tiles against a long key range (one rank of a sequence-sharded run): two CTAs per
+    query tile sweep half of the keys each and merge.  Same bit-exact contract, including ties
+    that straddle the two halves and rows selected entirely from one half."""
+    Tq, Tk, IH, ID, K = 300, 8192 + 100, 4, 64, 512
+    g = torch.Generator().manual_seed(21)
+    qi = (torch.randn(1, Tq, IH, ID, generator=g) / 8).to(_dev())
+    ki = (torch.randn(1, Tk, IH, ID, generator=g) / 8).to(_dev())
+    w = torch.randn(IH, generator=g).to(_dev())
+    idx, valid, scores = swv.dsa_indexer_topk(qi, ki, w, K)
+    full = own_scores(qi, ki, w)[0].cpu()                # (Tq, Tk), itself through the split path (top_k = Tk)
+    ridx, rvalid, rsel = O.topk_lower_index(full, K)
+    assert torch.equal(idx[0].cpu(), ridx)
+    assert torch.equal(scores[0].cpu(), rsel)
+    assert torch.equal(valid[0].cpu(), rvalid)
+    s_ref = O.indexer_scores(qi[0].cpu(), ki[0].cpu(), w.cpu())
+    assert bool(((full - s_ref).abs() <= score_error_bound(qi[0].cpu(), ki[0].cpu(), w.cpu())).all())
+    # ties: 9 distinct key rows repeated over the whole range, so every threshold value occurs in both halves
+    base = torch.randn(1, 9, IH, ID, generator=g) / 8
+    kt = base[:, torch.arange(Tk) % 9].contiguous().to(_dev())
+    idx2, _, sc2 = swv.dsa_indexer_topk(qi, kt, w, K)
+    full2 = own_scores(qi, kt, w)[0].cpu()
+    assert O.rows_with_straddling_tie(full2, K).sum() > Tq // 2
+    r2, _, s2 = O.topk_lower_index(full2, K)
+    assert torch.equal(idx2[0].cpu(), r2)
+    assert torch.equal(sc2[0].cpu(), s2)
+    # every score zero: the first K keys win, all of them in the first half
+    idx3, _, sc3 = swv.dsa_indexer_topk(qi.abs(), -ki.abs(), w.abs(), K)
+    assert torch.equal(idx3[0].cpu(), torch.arange(K, dtype=torch.int32).expand(Tq, K))
+    assert float(sc3.abs().max()) == 0.0
+    _check(swv)
+
+
+def test_masked_attention_short_query_range(swv):
+    """Queries are a slice of a longer key sequence (the sharded layout): fused path == gather path."""
+    Tq, Tk, H, D, K = 256, 8192 + 64, 2, 64, 256
+    g = torch.Generator().manual_seed(22)
+    q = (torch.randn(1, H, Tq, D, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    k = torch.randn(1, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    v = torch.randn(1, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    qi = (torch.randn(1, Tq, 4, 64, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    ki = (torch.randn(1, Tk, 4, 64, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    w = torch.randn(4, generator=g).to(_dev())
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    o = torch.zeros((1, H, Tq, D), dtype=torch.float32, device=_dev())
+    swv.dsa_attention_masked(q, k, v, sel, o)
+    o2 = torch.zeros_like(o)
+    swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o2)
+    _check(swv)
+    assert float((o - o2).abs().max()) < 2e-2
+    assert float((o - o2).abs().mean()) < 1e-3
