@@ -280,8 +280,12 @@ def run_ours(args):
                     dbuf[i].copy_(pinned[i], non_blocking=True)
             qkv_ready = copy_stream.record_event()
         else:
-            for i in range(3):
-                dbuf[i].copy_(pinned[i], non_blocking=True)
+            # sharded: q, k, v go up on the communication stream, ahead of the K/V all-gathers that
+            # run there, while this stream gathers the indexer keys and runs the top-k sweeps
+            comm.wait_stream(cur)
+            with torch.cuda.stream(comm):
+                for i in range(3):
+                    dbuf[i].copy_(pinned[i], non_blocking=True)
         o, _ = step(*dbuf, qkv_ready=qkv_ready)
         if world == 1:
             # read the result back on the copy stream so the next step's uploads and top-k passes

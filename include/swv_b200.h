@@ -141,11 +141,16 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
  * weights recomputed on the tensor cores from the collapsed indexer vectors
  * kept in the workspace (bit-identical to the emitted scores).
  * bf16 q/k/v only, D == 64; q,k,v,o rows 16-byte aligned, unit inner stride.
+ * `scratch` (optional, may be NULL): swv_dsa_attn_scratch_bytes() bytes, 256-byte aligned.  With few
+ * query tiles (one rank of a sequence-sharded run) the grid is only a few waves of CTAs; given the
+ * scratch, 2 or 4 CTAs share a (query tile, head pair), each sweeping a share of the key tiles, and
+ * the last one adds the partial rows up.  swv_dsa_attn_scratch_bytes returns 0 when no split helps.
  */
+int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes);
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
                             const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
-                            int Tq, int Tk, int D, int* status, void* stream);
+                            int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream);
 
 /* Static block-sparse flash attention forward driven by a CSR list of key blocks per
  * query block (shared by all batches and heads):

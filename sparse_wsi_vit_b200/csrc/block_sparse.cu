@@ -287,13 +287,20 @@ __global__ void __launch_bounds__(192, 1)
       }
       tc_fence_after();
       // which columns of this block the row attends (bit i of word c = column 32c + i)
-      const bool masked = p.mode != 0 || key0 + BS > p.Tk;
+      // Token-pattern mode: a block whose every (query, key) pair lies inside the window (no CLS
+      // row or column involved, dilation 1) needs no per-element pattern test.
+      bool inside = false;
+      if (p.mode != 0 && dil == 1 && qb * BS >= p.num_cls && key0 >= p.num_cls) {
+        const int q0 = qb * BS, far = max(q0 + BS - 1 - key0, key0 + BS - 1 - q0);
+        inside = far <= reach;
+      }
+      const bool masked = (p.mode != 0 && !inside) || key0 + BS > p.Tk;
       uint32_t keep[BS / 32];
 #pragma unroll
       for (int c = 0; c < BS / 32; ++c) {
         uint32_t w = 0xFFFFFFFFu;
         const int base = key0 + c * 32;
-        if (p.mode != 0) {
+        if (p.mode != 0 && !inside) {
           w = 0;
 #pragma unroll 4
           for (int i = 0; i < 32; ++i) {

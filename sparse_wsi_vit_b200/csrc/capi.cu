@@ -16,8 +16,9 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
                                  cudaStream_t st);
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
-                         const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
-                         cudaStream_t st);
+                         const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
+                         size_t scratch_bytes, int* status, cudaStream_t st);
+int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes);
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
                          const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
@@ -52,7 +53,7 @@ int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t
 
 extern "C" {
 
-int swv_version(void) { return 100; }
+int swv_version(void) { return 101; }
 
 const char* swv_strerror(int code) {
   switch (code) {
@@ -115,12 +116,17 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
                                    kv_group, status, static_cast<cudaStream_t>(stream));
 }
 
+int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes) {
+  return swv::dsa_attn_scratch_bytes_impl(B, H, Tq, Tk, bytes);
+}
+
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
                             const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
-                            int Tq, int Tk, int D, int* status, void* stream) {
+                            int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream) {
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
-                                   o_dtype, B, H, Tq, Tk, D, status, static_cast<cudaStream_t>(stream));
+                                   o_dtype, B, H, Tq, Tk, D, scratch, scratch_bytes, status,
+                                   static_cast<cudaStream_t>(stream));
 }
 
 int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],

@@ -79,7 +79,14 @@ struct AttnParams {
   int o_dtype;
   float scale_log2;
   int* status;
+  // Key-range split: with few CTAs (a rank of a sequence-sharded run) `split` CTAs share one
+  // (query tile, head pair), each sweeping a share of the key tiles; every part leaves its
+  // unnormalised output rows and row statistics in `scratch`, the part that arrives last adds them up.
+  int split;
+  float* scratch;        // [CTAs][split][2 heads][128 rows][kPartRec floats]
+  uint32_t* tickets;     // [CTAs]
 };
+constexpr int kPartRec = kHeadDim + 4;                // output row + (l, m_used, m_true, pad)
 
 struct AttnCtl {
   uint64_t q_full;
@@ -91,6 +98,7 @@ struct AttnCtl {
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t cta_exact;          // some row of the CTA needs the two-pass path
+  uint32_t ticket;
 };
 
 constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
@@ -396,10 +404,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int hp = blockIdx.x % p.nHP;
-  const int qt = (blockIdx.x / p.nHP) % p.nQT;
-  const int b = blockIdx.x / (p.nHP * p.nQT);
-  const int nKT = p.nKT;
+  const int cta = blockIdx.x / p.split;          // (batch, query tile, head pair)
+  const int part = blockIdx.x - cta * p.split;   // which share of the key tiles
+  const int hp = cta % p.nHP;
+  const int qt = (cta / p.nHP) % p.nQT;
+  const int b = cta / (p.nHP * p.nQT);
+  const int kt0 = static_cast<int>(static_cast<int64_t>(part) * p.nKT / p.split);        // first key tile
+  const int nKT = static_cast<int>(static_cast<int64_t>(part + 1) * p.nKT / p.split) - kt0;   // key tiles of this CTA
   const int h0 = hp * 2;
   const int nh = (h0 + 1 < p.H) ? 2 : 1;   // heads handled by this CTA
 
@@ -460,8 +471,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         if (n_wk < nKT && mbar_test_wait(&ctl->wk_empty[n_wk & 1], ((n_wk >> 1) & 1) ^ 1)) {
           uint8_t* dst = smem + kOffWk + (n_wk & 1) * kWTileBytes;
           mbar_expect_tx(&ctl->wk_full[n_wk & 1], kWTileBytes);
-          tma_load_3d(dst, &tm_wk, &ctl->wk_full[n_wk & 1], 0, n_wk * kTile, b);
-          tma_load_3d(dst + kWTileBytes / 2, &tm_wk, &ctl->wk_full[n_wk & 1], 32, n_wk * kTile, b);
+          tma_load_3d(dst, &tm_wk, &ctl->wk_full[n_wk & 1], 0, (kt0 + n_wk) * kTile, b);
+          tma_load_3d(dst + kWTileBytes / 2, &tm_wk, &ctl->wk_full[n_wk & 1], 32, (kt0 + n_wk) * kTile, b);
           ++n_wk;
           progress = true;
         }
@@ -471,7 +482,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           int j = n_k[x];
           if (j < nKT && mbar_test_wait(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1)) {
             mbar_expect_tx(&ctl->k_full[x][j & 1], kQTileBytes);
-            tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, j * kTile,
+            tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, (kt0 + j) * kTile,
                         h0 + x, b);
             ++n_k[x];
             progress = true;
@@ -479,7 +490,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           j = n_v[x];
           if (j < nKT && mbar_test_wait(&ctl->v_empty[x], (j & 1) ^ 1)) {
             mbar_expect_tx(&ctl->v_full[x], kQTileBytes);
-            tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, j * kTile, h0 + x, b);
+            tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, (kt0 + j) * kTile, h0 + x, b);
             ++n_v[x];
             progress = true;
           }
@@ -625,6 +636,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     const uint32_t o_col = lane_base + kColO + x * kHeadDim + d0;
     bool ok = true;
     float inv = 0.f;
+    float row_l = 0.f, row_mu = 0.f, row_mt = 0.f;   // row statistics of this CTA's key range (for the split merge)
     if (!exact) {
       float l_part[2];
       ok = softmax_tiles_split(ctl, lane_base, slice, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, p.status,
@@ -639,13 +651,15 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 #pragma unroll
       for (int i = 0; i < kSlices; ++i) lt += lsum[(x * kTile + row) * kSlices + i];
       inv = 1.f / lt;                             // the clamp cannot bind
+      row_l = lt;
     } else if (slice < 2 && x < nh) {
       SoftmaxRow st;
       st.lane_base = lane_base;
       st.s_col = lane_base + kColS + x * kTile;
       st.o_col = lane_base + kColO + x * kHeadDim;
       st.mask_tile =
-          reinterpret_cast<const uint4*>(p.maskbits) + (static_cast<int64_t>(b) * p.nQT + qt) * nKT * kTile + row;
+          reinterpret_cast<const uint4*>(p.maskbits) +
+          ((static_cast<int64_t>(b) * p.nQT + qt) * p.nKT + kt0) * kTile + row;
       st.sc = p.scale_log2;
       st.m_true = st.m_used = -__int_as_float(0x7f800000);
       st.l = 0.f;
@@ -653,44 +667,122 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       // the reference's clamp: out = O c / max(l c, 1e-6), c = 2^(m_used - m_true)
       const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
       inv = corr / fmaxf(st.l * corr, 1e-6f);
+      row_l = st.l;
+      row_mu = st.m_used;
+      row_mt = st.m_true;
     }
-    if (x < nh && nd > 0) {
-      if (ok && !mbar_wait_bounded(&ctl->pv_done[x], (nKT - 1) & 1, abort_flag)) {
-        record_status(p.status, kDevWaitPvDone);
-        ok = false;
+    const bool duty = x < nh && nd > 0;
+    if (duty && ok && !mbar_wait_bounded(&ctl->pv_done[x], (nKT - 1) & 1, abort_flag)) {
+      record_status(p.status, kDevWaitPvDone);
+      ok = false;
+    }
+    if (duty && ok) tc_fence_after();
+
+    // writes 16 channels [d0 + c*16, +16) of the output row, scaled
+    auto store_chunk = [&](int c, const float (&acc)[16], float scale) {
+      if (p.o_dtype == SWV_F32) {
+        float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i += 4)
+          *reinterpret_cast<float4*>(orow + i) =
+              make_float4(acc[i] * scale, acc[i + 1] * scale, acc[i + 2] * scale, acc[i + 3] * scale);
+      } else {
+        uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
+#pragma unroll
+        for (int i = 0; i < 16; i += 8) {
+          uint32_t w4[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float a0 = acc[i + 2 * q] * scale, a1 = acc[i + 2 * q + 1] * scale;
+            if (p.o_dtype == SWV_BF16) {
+              w4[q] = pack_bf16x2(a0, a1);
+            } else {
+              const __half2 h2 = __floats2half2_rn(a0, a1);
+              w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
+            }
+          }
+          *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+        }
       }
-      if (ok) {
-        tc_fence_after();
+    };
+
+    if (p.split == 1) {
+      if (duty && ok) {
         for (int c = 0; c < nd / 16; ++c) {
           uint32_t o[16];
           tmem_ld16(o_col + c * 16, o);
           tc_wait_ld();
           if (!row_ok) continue;
-          if (p.o_dtype == SWV_F32) {
-            float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
+          float acc[16];
 #pragma unroll
-            for (int i = 0; i < 16; i += 4) {
-              *reinterpret_cast<float4*>(orow + i) =
-                  make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                              __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
-            }
+          for (int i = 0; i < 16; ++i) acc[i] = __uint_as_float(o[i]);
+          store_chunk(c, acc, inv);
+        }
+      }
+    } else {
+      // every part leaves its unnormalised rows and statistics; the last one to arrive merges
+      const size_t rec_stride = static_cast<size_t>(2) * kTile * kPartRec;          // floats per part
+      float* rec0 = p.scratch + static_cast<size_t>(cta) * p.split * rec_stride + (static_cast<size_t>(x) * kTile + row) * kPartRec;
+      if (duty && ok) {
+        float* mine = rec0 + part * rec_stride;
+        for (int c = 0; c < nd / 16; ++c) {
+          uint32_t o[16];
+          tmem_ld16(o_col + c * 16, o);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; i += 4)
+            *reinterpret_cast<float4*>(mine + d0 + c * 16 + i) =
+                make_float4(__uint_as_float(o[i]), __uint_as_float(o[i + 1]), __uint_as_float(o[i + 2]),
+                            __uint_as_float(o[i + 3]));
+        }
+        if (d0 == 0) *reinterpret_cast<float4*>(mine + kHeadDim) = make_float4(row_l, row_mu, row_mt, 0.f);
+      }
+      __threadfence();
+      asm volatile("bar.sync 2, %0;" ::"r"(32 * kSoftWarps) : "memory");
+      if (threadIdx.x == 64) ctl->ticket = atomicAdd(p.tickets + cta, 1u);
+      asm volatile("bar.sync 2, %0;" ::"r"(32 * kSoftWarps) : "memory");
+      if (*reinterpret_cast<volatile uint32_t*>(&ctl->ticket) == static_cast<uint32_t>(p.split - 1)) {
+        __threadfence();
+        if (threadIdx.x == 64) p.tickets[cta] = 0u;
+        if (duty && row_ok && *abort_flag == 0u) {
+          // one-pass parts share the constant stabiliser (statistics m = 0): plain sums.  Two-pass
+          // parts are first brought to the largest stabiliser among them.
+          float m_all = -__int_as_float(0x7f800000), mt_all = m_all;
+          for (int q = 0; q < p.split; ++q) {
+            const float4 stq = __ldcg(reinterpret_cast<const float4*>(rec0 + q * rec_stride + kHeadDim));
+            m_all = fmaxf(m_all, stq.y);
+            mt_all = fmaxf(mt_all, stq.z);
+          }
+          float l_all = 0.f;
+          float f[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int q = 0; q < p.split; ++q) {
+            const float4 stq = __ldcg(reinterpret_cast<const float4*>(rec0 + q * rec_stride + kHeadDim));
+            f[q] = !exact ? 1.f : (stq.y == m_all ? 1.f : ex2_approx(stq.y - m_all));   // 2^(-inf) = 0 for empty parts
+            l_all += stq.x * f[q];
+          }
+          float scale;
+          if (!exact) {
+            scale = 1.f / l_all;
           } else {
-            uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + d0 + c * 16;
+            const float corr = (m_all == mt_all) ? 1.f : ex2_approx(m_all - mt_all);
+            scale = corr / fmaxf(l_all * corr, 1e-6f);
+          }
+          for (int c = 0; c < nd / 16; ++c) {
+            float acc[16];
 #pragma unroll
-            for (int i = 0; i < 16; i += 8) {
-              uint32_t w4[4];
+            for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+            for (int q = 0; q < p.split; ++q) {
+              const float* src = rec0 + q * rec_stride + d0 + c * 16;
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float a0 = __uint_as_float(o[i + 2 * q]) * inv, a1 = __uint_as_float(o[i + 2 * q + 1]) * inv;
-                if (p.o_dtype == SWV_BF16) {
-                  w4[q] = pack_bf16x2(a0, a1);
-                } else {
-                  const __half2 h2 = __floats2half2_rn(a0, a1);
-                  w4[q] = *reinterpret_cast<const uint32_t*>(&h2);
-                }
+              for (int i = 0; i < 16; i += 4) {
+                const float4 v4 = __ldcg(reinterpret_cast<const float4*>(src + i));
+                acc[i] = fmaf(v4.x, f[q], acc[i]);
+                acc[i + 1] = fmaf(v4.y, f[q], acc[i + 1]);
+                acc[i + 2] = fmaf(v4.z, f[q], acc[i + 2]);
+                acc[i + 3] = fmaf(v4.w, f[q], acc[i + 3]);
               }
-              *reinterpret_cast<uint4*>(orow + i) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
             }
+            store_chunk(c, acc, scale);
           }
         }
       }
@@ -712,10 +804,39 @@ static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
                          uint32_t** kth, uint32_t** neq, uint32_t** kmax2);
 
+// How many CTAs share one (query tile, head pair): with grids of only a few waves the last wave is
+// far from full, so the key range is divided (1, 2 or 4 ways) to even the load out.
+static int attn_split_factor(int B, int H, int Tq, int Tk) {
+  const int64_t ctas = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile) * ((H + 1) / 2);
+  const int n_kt = (Tk + kTile - 1) / kTile;
+  const int n_sm = 148;
+  if (ctas >= 4 * n_sm) return 1;
+  int best = 1;
+  double best_cost = static_cast<double>((ctas + n_sm - 1) / n_sm);
+  for (int s = 2; s <= 4; s *= 2) {
+    if (n_kt / s < 32) break;
+    const double cost = static_cast<double>((ctas * s + n_sm - 1) / n_sm) / s + 0.02 * s;   // + merge overhead
+    if (cost < best_cost - 1e-9) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes) {
+  if (!bytes) return SWV_ERR_NULL;
+  if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
+  const int s = attn_split_factor(B, H, Tq, Tk);
+  const size_t ctas = static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * ((H + 1) / 2);
+  *bytes = s == 1 ? 0 : ((ctas * 4 + 255) / 256 * 256 + ctas * s * 2 * kTile * kPartRec * 4);
+  return SWV_OK;
+}
+
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
-                         const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
-                         cudaStream_t st) {
+                         const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
+                         size_t scratch_bytes, int* status, cudaStream_t st) {
   if (!q || !k || !v || !maskbits || !workspace || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (D != kHeadDim) return SWV_ERR_UNSUPPORTED;
@@ -767,6 +888,21 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   p.status = status;
 
+  // the key range is split only if the caller brought the scratch buffer for it
+  p.split = 1;
+  p.scratch = nullptr;
+  p.tickets = nullptr;
+  {
+    size_t need = 0;
+    dsa_attn_scratch_bytes_impl(B, H, Tq, Tk, &need);
+    if (need > 0 && scratch != nullptr && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0) {
+      const size_t ctas = static_cast<size_t>(B) * p.nQT * p.nHP;
+      p.split = attn_split_factor(B, H, Tq, Tk);
+      p.tickets = static_cast<uint32_t*>(scratch);
+      p.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + (ctas * 4 + 255) / 256 * 256);
+      SWV_CUDA_OK(cudaMemsetAsync(p.tickets, 0, ctas * 4, st));
+    }
+  }
   SWV_CUDA_OK(cudaMemsetAsync(kmax2, 0, static_cast<size_t>(B) * H * 4, st));
   {
     const int64_t total = static_cast<int64_t>(B) * H * Tk;
@@ -775,7 +911,7 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   }
   SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(attn_smem_bytes())));
-  const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP;
+  const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP * p.split;
   dsa_attn_masked_kernel<<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;

@@ -796,17 +796,26 @@ __global__ void __launch_bounds__(576, 1)
   }
 }
 
-// valid[b,t,s] = s < k_eff ; slots >= k_eff of idx / scores are zeroed.
+// valid[b,t,s] = s < k_eff ; slots >= k_eff of idx / scores are zeroed.  VEC consecutive slots per
+// thread (VEC divides top_k, so a thread never crosses a row).
+template <int VEC>
 __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict__ idx, float* __restrict__ scores,
                                   int64_t total, int top_k, int k_eff) {
-  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t gid = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * VEC;
   if (gid >= total) return;
-  const int s = static_cast<int>(gid % top_k);
-  const bool filled = s < k_eff;
-  valid[gid] = filled ? 1.f : 0.f;
-  if (!filled) {
-    idx[gid] = 0;
-    scores[gid] = 0.f;
+  const int s0 = static_cast<int>(gid % top_k);
+  if constexpr (VEC == 4) {
+    *reinterpret_cast<float4*>(valid + gid) = make_float4(s0 < k_eff ? 1.f : 0.f, s0 + 1 < k_eff ? 1.f : 0.f,
+                                                          s0 + 2 < k_eff ? 1.f : 0.f, s0 + 3 < k_eff ? 1.f : 0.f);
+  } else {
+    valid[gid] = s0 < k_eff ? 1.f : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    if (s0 + i >= k_eff) {
+      idx[gid + i] = 0;
+      scores[gid + i] = 0.f;
+    }
   }
 }
 
@@ -1005,8 +1014,13 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
 
   const int64_t total = static_cast<int64_t>(B) * Tq * top_k;
-  fill_valid_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(valid, idx, scores, total, top_k,
-                                                                                   top_k < Tk ? top_k : Tk);
+  const int k_eff = top_k < Tk ? top_k : Tk;
+  if ((top_k & 3) == 0 && (reinterpret_cast<uintptr_t>(valid) & 15) == 0)
+    fill_valid_kernel<4><<<static_cast<unsigned>((total / 4 + 255) / 256), 256, 0, st>>>(valid, idx, scores, total,
+                                                                                          top_k, k_eff);
+  else
+    fill_valid_kernel<1><<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(valid, idx, scores, total, top_k,
+                                                                                      k_eff);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }

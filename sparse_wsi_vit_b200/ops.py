@@ -151,10 +151,13 @@ def dsa_attention_masked(q, k, v, selection, o):
     q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
     dev = q.device
     st = status_word(dev)
+    nscr = ctypes.c_size_t()
+    check(lib.swv_dsa_attn_scratch_bytes(B, H, Tq, Tk, ctypes.byref(nscr)), "swv_dsa_attn_scratch_bytes")
+    scr = _buffer("attn_scratch", dev, nscr.value) if nscr.value else None
     rc = lib.swv_dsa_attn_masked_fwd(
         q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), mask.data_ptr(),
         ws.data_ptr(), o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D,
-        st.data_ptr(), _stream(dev))
+        scr.data_ptr() if scr is not None else None, nscr.value, st.data_ptr(), _stream(dev))
     check(rc, "swv_dsa_attn_masked_fwd")
     if _CHECK:
         check_status(dev, "swv_dsa_attn_masked_fwd")

@@ -87,7 +87,8 @@ def test_argument_validation_happens_before_any_launch(swv):
     assert L.swv_block_sparse_attn_fwd(*bs(64, 64, 2, 1)) == -8
     assert L.swv_block_sparse_attn_fwd(*bs(64, 64, 0, 3)) == -4
     # dense path: only head_dim 64, unit inner stride, 16-byte aligned rows
-    m = lambda D, qs: (fake, qs, fake, i64x4, fake, i64x4, fake, fake, fake, i64x4, 0, 1, 1, 8, 8, D, fake, null)
+    m = lambda D, qs: (fake, qs, fake, i64x4, fake, i64x4, fake, fake, fake, i64x4, 0, 1, 1, 8, 8, D, null, 0, fake,
+                       null)
     ok_strides = (ctypes.c_int64 * 4)(4096, 512, 64, 1)
     assert L.swv_dsa_attn_masked_fwd(*m(128, ok_strides)) == -8
     assert L.swv_dsa_attn_masked_fwd(*m(64, (ctypes.c_int64 * 4)(4096, 512, 64, 2))) == -2

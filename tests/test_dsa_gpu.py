@@ -270,9 +270,13 @@ def test_indexer_split_key_range(swv):
     _check(swv)
 
 
-def test_masked_attention_short_query_range(swv):
-    """Queries are a slice of a longer key sequence (the sharded layout): fused path == gather path."""
-    Tq, Tk, H, D, K = 256, 8192 + 64, 2, 64, 256
+@pytest.mark.parametrize("K", [256, 6000])
+def test_masked_attention_short_query_range(swv, K):
+    """Queries are a slice of a longer key sequence (the sharded layout): fused path == gather path.
+    With so few query tiles both the indexer and the attention split the key range over several
+    CTAs; K = 6000 exceeds the number of positive scores of a row (threshold 0), which takes the
+    two-pass softmax path through the same merge."""
+    Tq, Tk, H, D = 256, 8192 + 64, 2, 64
     g = torch.Generator().manual_seed(22)
     q = (torch.randn(1, H, Tq, D, generator=g) / 8).to(torch.bfloat16).to(_dev())
     k = torch.randn(1, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
