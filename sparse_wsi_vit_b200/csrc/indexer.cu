@@ -828,14 +828,18 @@ struct WorkspaceLayout {
   int split;
   size_t total;
 };
-// Two CTAs share a query tile (each sweeps half of the key tiles) when the query tiles alone
-// would leave more than half of the SMs idle -- the situation of one rank of a sequence-sharded
-// run -- and the key range is long enough to be worth merging.
-constexpr int kSplitMaxTiles = 74;     // half of the 148 SMs
+// Two CTAs share a query tile (each sweeps half of the key tiles) when that fills the SMs better:
+// with few query tiles (one rank of a sequence-sharded run: 64 tiles on 148 SMs) or when the last
+// wave of whole-tile CTAs would be far from full (512 tiles = 3.46 waves), provided the key range
+// is long enough to be worth merging.
+constexpr int kSplitSms = 148;
 constexpr int kSplitMinKeyTiles = 64;
 static int split_factor(int B, int Tq, int Tk) {
   const int64_t tiles = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile);
-  return (tiles <= kSplitMaxTiles && (Tk + kTile - 1) / kTile >= kSplitMinKeyTiles) ? 2 : 1;
+  if ((Tk + kTile - 1) / kTile < kSplitMinKeyTiles) return 1;
+  const double whole = static_cast<double>((tiles + kSplitSms - 1) / kSplitSms);
+  const double halves = static_cast<double>((2 * tiles + kSplitSms - 1) / kSplitSms) / 2 + 0.05;   // + merge
+  return halves < whole ? 2 : 1;
 }
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   WorkspaceLayout L;
