@@ -16,7 +16,8 @@
 //   warp 1     : UMMA issuer: S(j) = Q K(j)^T into one of TWO score buffers, O += P(j) V(j) with
 //                P read from TMEM; S(j+2) is issued as soon as the softmax has read S(j), so the
 //                tensor pipe works one tile ahead of the softmax
-//   warps 2..5 : online softmax, one thread per query row, ONE pass per tile: exponentials are
+//   warps 2..9 : online softmax, two threads per query row (one per half of the key columns), ONE
+//                pass per tile: exponentials are
 //                taken against the current stabiliser while the tile's maximum is tracked; only
 //                if some row's maximum exceeds its stabiliser by more than 2^8 is the stabiliser
 //                raised, O (in TMEM) rescaled and the pass repeated (S stays intact: P has its
@@ -49,6 +50,8 @@ struct BsaCtl {
   uint64_t s_full[2], p_full[2], pv_done[2];   // per score / probability buffer (tile parity)
   uint32_t tmem_base;
   uint32_t abort_flag;
+  float xm[2][kTile][2];                       // per tile parity and row: the tile maximum seen by each column half
+  float xl[kTile][2];                          // per row: the probability sum of each column half
 };
 
 template <int BS, int D>
@@ -70,7 +73,7 @@ struct BsaCfg {
 // columns, written as bf16 pairs; returns the row's maximum raw score over the kept columns and
 // the sum of the probabilities.  Loads run one 16-column unit ahead.
 template <int BS, bool MASKED>
-__device__ __forceinline__ void bsa_pass(uint32_t s_col, uint32_t p_col, const uint32_t (&keep)[BS / 32], float sc,
+__device__ __forceinline__ void bsa_pass(uint32_t s_col, uint32_t p_col, const uint32_t (&keep)[(BS + 31) / 32], float sc,
                                          float neg_m, float& mt_out, float& l_out) {
   const float ninf = -__int_as_float(0x7f800000);
   float mt0 = ninf, mt1 = ninf, l0 = 0.f, l1 = 0.f;
@@ -83,7 +86,7 @@ __device__ __forceinline__ void bsa_pass(uint32_t s_col, uint32_t p_col, const u
       if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
       else tmem_ld16(s_col + (u + 1) * 16, sb);
     }
-    const uint32_t w = MASKED ? keep[u >> 1] >> ((u & 1) * 16) : 0xFFFFu;
+    const uint32_t w = MASKED ? keep[u >> 1] >> ((u & 1) * 16) : 0xFFFFu;   // (BS = 32: one word)
     uint32_t packed[8];
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
@@ -122,7 +125,7 @@ __device__ __forceinline__ bool static_pattern(int qi, int kj, int C, int reach,
 }
 
 template <int BS, int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(320, 1)
     block_sparse_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const BsaParams p) {
   using Cfg = BsaCfg<BS, D>;
@@ -152,7 +155,7 @@ __global__ void __launch_bounds__(192, 1)
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&ctl->s_full[s], 1);
-      mbar_init(&ctl->p_full[s], 4);
+      mbar_init(&ctl->p_full[s], 8);
       mbar_init(&ctl->pv_done[s], 1);
     }
     ctl->abort_flag = 0;
@@ -260,12 +263,19 @@ __global__ void __launch_bounds__(192, 1)
     }
   } else {
     // ----------------------------------------------------------------- softmax
+    // Eight warps: warp (quarter, half) owns 32 query rows and half of the tile's key columns.  The
+    // two warps of a row quarter exchange their tile maxima through shared memory (one named
+    // barrier per tile), so both take the same decision on raising the stabiliser; each keeps the
+    // probability sum of its columns and rescales / writes its half of the output channels.
+    constexpr int HC = BS / 2;                 // key columns per warp
+    constexpr int DH = D / 2;                  // output channels per warp
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int qrow = qb * BS + row;
     const bool row_ok = row < BS && qrow < p.Tq;
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-    const uint32_t o_col = lane_base + Cfg::kColO;
+    const uint32_t o_col = lane_base + Cfg::kColO + half * DH;
     const float sc = p.scale_log2;
     const float ninf = -__int_as_float(0x7f800000);
     const int reach = p.window * p.dilation;
@@ -276,17 +286,17 @@ __global__ void __launch_bounds__(192, 1)
     for (int j = 0; j < nblk; ++j) {
       const int key0 = p.col_idx[list0 + j] * BS;
       const int sb = j & 1;
-      const uint32_t s_col = lane_base + sb * BS;
-      const uint32_t p_col = lane_base + Cfg::kColP + sb * (BS / 2);
-      // S(j) computed; P's buffer no longer read by PV(j-2)
-      if (!mbar_wait_bounded(&ctl->s_full[sb], (j >> 1) & 1, abort_flag) ||
-          (j >= 2 && !mbar_wait_bounded(&ctl->pv_done[sb], ((j >> 1) & 1) ^ 1, abort_flag))) {
+      const uint32_t s_col = lane_base + sb * BS + half * HC;
+      const uint32_t p_col = lane_base + Cfg::kColP + sb * (BS / 2) + half * (HC / 2);
+      // S(j) computed; P's buffer no longer read by PV(j-2).  (A wait that gave up keeps looping
+      // without work: both warps of a quarter pass the same barriers.)
+      if (ok && (!mbar_wait_bounded(&ctl->s_full[sb], (j >> 1) & 1, abort_flag) ||
+                 (j >= 2 && !mbar_wait_bounded(&ctl->pv_done[sb], ((j >> 1) & 1) ^ 1, abort_flag)))) {
         record_status(p.status, kDevWaitAccFull);
         ok = false;
-        break;
       }
       tc_fence_after();
-      // which columns of this block the row attends (bit i of word c = column 32c + i)
+      // which of its columns the row attends (bit i of word c = column half*HC + 32c + i)
       // Token-pattern mode: a block whose every (query, key) pair lies inside the window (no CLS
       // row or column involved, dilation 1) needs no per-element pattern test.
       bool inside = false;
@@ -295,11 +305,11 @@ __global__ void __launch_bounds__(192, 1)
         inside = far <= reach;
       }
       const bool masked = (p.mode != 0 && !inside) || key0 + BS > p.Tk;
-      uint32_t keep[BS / 32];
+      uint32_t keep[(HC + 31) / 32];
 #pragma unroll
-      for (int c = 0; c < BS / 32; ++c) {
+      for (int c = 0; c < (HC + 31) / 32; ++c) {
         uint32_t w = 0xFFFFFFFFu;
-        const int base = key0 + c * 32;
+        const int base = key0 + half * HC + c * 32;
         if (p.mode != 0 && !inside) {
           w = 0;
 #pragma unroll 4
@@ -315,10 +325,14 @@ __global__ void __launch_bounds__(192, 1)
       }
 
       // rows that have attended nothing yet have m_used = -inf; their stabiliser is 0 for now
-      float mt, lt;
-      if (masked) bsa_pass<BS, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
-      else bsa_pass<BS, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
-      const float m_new = fmaxf(m_used, mt * sc);
+      float mt = ninf, lt = 0.f;
+      if (ok) {
+        if (masked) bsa_pass<HC, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+        else bsa_pass<HC, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+      }
+      ctl->xm[sb][row][half] = mt;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+      const float m_new = fmaxf(m_used, fmaxf(ctl->xm[sb][row][0], ctl->xm[sb][row][1]) * sc);
       if (__any_sync(0xffffffffu, m_new > m_used + kStep)) {
         // raise the stabiliser, rescale what has been accumulated, repeat the pass
         const float factor = (m_new == m_used) ? 1.f : ex2_approx(m_used - m_new);
@@ -326,46 +340,53 @@ __global__ void __launch_bounds__(192, 1)
         m_used = m_new;
         if (j > 0) {
           // O of the tiles before this one is complete once PV(j-1) retired
-          if (!mbar_wait_bounded(&ctl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) {
+          if (ok && !mbar_wait_bounded(&ctl->pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag)) {
             record_status(p.status, kDevWaitPvDone);
             ok = false;
-            break;
           }
-          tc_fence_after();
+          if (ok) {
+            tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < D / 16; ++c) {
-            uint32_t o[16];
-            tmem_ld16(o_col + c * 16, o);
-            tc_wait_ld();
+            for (int c = 0; c < DH / 16; ++c) {
+              uint32_t o[16];
+              tmem_ld16(o_col + c * 16, o);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            tmem_st16(o_col + c * 16, o);
+              for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st16(o_col + c * 16, o);
+            }
+            tc_wait_st();
           }
-          tc_wait_st();
         }
-        if (masked) bsa_pass<BS, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
-        else bsa_pass<BS, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+        if (ok) {
+          if (masked) bsa_pass<HC, true>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+          else bsa_pass<HC, false>(s_col, p_col, keep, sc, (m_used == ninf) ? 0.f : -m_used, mt, lt);
+        }
       }
       l += lt;
       tc_wait_st();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->p_full[sb]);
+      if (ok && lane == 0) mbar_arrive(&ctl->p_full[sb]);
     }
 
     if (nblk > 0 && ok && !mbar_wait_bounded(&ctl->pv_done[(nblk - 1) & 1], ((nblk - 1) >> 1) & 1, abort_flag)) {
       record_status(p.status, kDevWaitPvDone);
       ok = false;
     }
+    // the row's probability sum: both column halves
+    ctl->xl[row][half] = l;
+    asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+    l = ctl->xl[row][0] + ctl->xl[row][1];
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      if (p.lse != nullptr && row_ok) {
+      if (p.lse != nullptr && row_ok && half == 0) {
         p.lse[(static_cast<int64_t>(b) * p.H + h) * p.Tq + qrow] =
             l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : ninf;
       }
 #pragma unroll 1
-      for (int c = 0; c < D / 16; ++c) {
+      for (int c = 0; c < DH / 16; ++c) {
         uint32_t o[16];
         if (nblk > 0) {
           tmem_ld16(o_col + c * 16, o);
@@ -376,7 +397,7 @@ __global__ void __launch_bounds__(192, 1)
         }
         if (!row_ok) continue;
         if (p.o_dtype == SWV_F32) {
-          float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
+          float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + half * DH + c * 16;
 #pragma unroll
           for (int i = 0; i < 16; i += 4) {
             *reinterpret_cast<float4*>(orow + i) =
@@ -384,7 +405,7 @@ __global__ void __launch_bounds__(192, 1)
                             __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
           }
         } else {
-          uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + c * 16;
+          uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + half * DH + c * 16;
 #pragma unroll
           for (int i = 0; i < 16; i += 8) {
             uint32_t w4[4];
@@ -499,7 +520,7 @@ static int launch_bsa(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   SWV_CUDA_OK(cudaFuncSetAttribute(block_sparse_attn_kernel<BS, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    static_cast<int>(Cfg::kSmem)));
   const unsigned grid = static_cast<unsigned>(p.B) * p.nQB * p.H;
-  block_sparse_attn_kernel<BS, D><<<grid, 192, Cfg::kSmem, st>>>(tq, tk, tv, p);
+  block_sparse_attn_kernel<BS, D><<<grid, 320, Cfg::kSmem, st>>>(tq, tk, tv, p);
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }
