@@ -206,7 +206,8 @@ int swv_nsa_select_blocks_fwd(const void* q, const int64_t q_strides[4], const v
 
 /* NSA-style attention, selected branch: plain softmax attention of every query head over the keys
  * of the blocks selected for its kv group, o (B,Hq,Tq,D) fp32 contiguous.  One pass reads every
- * selected key / value row once for the whole group.  q, k, v bf16 as above; sel_block a multiple
+ * selected key / value row once for the whole group (warp-level tensor-core tiles whose rows are the
+ * heads of the group).  q, k, v bf16 as above; sel_block a multiple
  * of 32; Hq / Hkv <= 8; `blocks` (B,Hkv,Tq,n_sel) int32, block ids < ceil(Tk / sel_block).
  */
 int swv_nsa_selected_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],

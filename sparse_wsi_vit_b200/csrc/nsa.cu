@@ -14,8 +14,9 @@
 //                           (TMA rings -> tcgen05 -> two TMEM accumulators), eight epilogue warps
 //                           turn scores into probabilities and add them up per selection block.
 //   nsa_select_kernel     : one warp per (b, g, t): iterative arg-max over the importance row.
-//   nsa_selected_attn_kernel : one warp per (b, g, t), all G heads at once, CUDA-core fp32: every
-//                           selected key / value row is read once for the whole group.
+//   nsa_selected_attn_mma_kernel : one warp per (b, g, t), the G heads as rows of mma.sync tiles: every
+//                           selected key / value row is read once for the whole group
+//                           (nsa_selected_attn_kernel: the same on CUDA cores, for unaligned layouts).
 //   nsa_combine_kernel    : out = sum_b sigmoid(gate_b) * O_b.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -419,6 +420,169 @@ __global__ void __launch_bounds__(128) nsa_selected_attn_kernel(const NsaSelPara
   }
 }
 
+// ---------------------------------------- selected attention on mma.sync tiles
+// The same operator with the two products on warp-level tensor-core tiles (m16n8k16, bf16 in, fp32
+// accumulate): the G <= 8 heads of the kv group are the rows of a 16-row tile (the other rows are
+// zero), so one tile multiplies all heads of a query with 8 keys (scores) or 8 channels (output).
+// tcgen05 tiles are 128 rows tall and would be 6 % used here; the limit of this kernel is the
+// gather of the selected key / value rows from L2 anyway.  One warp per (b, g, t); keys in chunks
+// of 16, copied with cp.async into a per-warp double buffer (rows padded to D*2 + 16 bytes so that
+// ldmatrix reads are free of bank conflicts).
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+// d += a (16x16, row) * b (16x8, col); the tile's rows 8..15 are zero: a1 = a3 = 0
+__device__ __forceinline__ void mma_16816_top(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+               "{%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+
+template <int D>
+__global__ void __launch_bounds__(128) nsa_selected_attn_mma_kernel(const NsaSelParams p) {
+  constexpr int kRowBytes = D * 2 + 16;              // padded key / value row
+  constexpr int kChunk = 16;                         // keys per step
+  constexpr int kBufBytes = kChunk * kRowBytes;      // one K or V chunk
+  extern __shared__ __align__(16) uint8_t sel_smem[];   // [4 warps][2 buffers][K chunk, V chunk]
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g4 = lane >> 2, t4 = lane & 3;           // fragment row / column-pair indices
+  const int64_t wid = static_cast<int64_t>(blockIdx.x) * 4 + wib;
+  const int64_t total = static_cast<int64_t>(p.B) * p.Hkv * p.Tq;
+  if (wid >= total) return;
+  const int t = static_cast<int>(wid % p.Tq);
+  const int g = static_cast<int>((wid / p.Tq) % p.Hkv);
+  const int b = static_cast<int>(wid / (static_cast<int64_t>(p.Tq) * p.Hkv));
+  const int G = p.G;
+  const uint32_t sbase = smem_u32(sel_smem) + wib * (4 * kBufBytes);
+  const __nv_bfloat16* kbase = p.k + b * p.ks[0] + g * p.ks[1];
+  const __nv_bfloat16* vbase = p.v + b * p.vs[0] + g * p.vs[1];
+  const int32_t* blk = p.blocks + ((static_cast<int64_t>(b) * p.Hkv + g) * p.Tq + t) * p.n_sel;
+  const float ninf = -__int_as_float(0x7f800000);
+
+  // Q fragments: row g4 = head g4 of the group (zero for g4 >= G), 16 channels per k-step
+  uint32_t qa0[D / 16], qa2[D / 16];
+  {
+    const __nv_bfloat16* qrow = p.q + b * p.qs[0] + (g * G + min(g4, G - 1)) * p.qs[1] + t * p.qs[2];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint32_t lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t4);
+      const uint32_t hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t4);
+      qa0[ks] = g4 < G ? lo : 0u;
+      qa2[ks] = g4 < G ? hi : 0u;
+    }
+  }
+
+  const int chunks_per_block = p.sel_block / kChunk;
+  const int n_chunks = p.n_sel * chunks_per_block;
+  // copies chunk c (16 key rows and 16 value rows) into buffer c & 1
+  auto issue = [&](int c) {
+    const int key0 = blk[c / chunks_per_block] * p.sel_block + (c % chunks_per_block) * kChunk;
+    const uint32_t dst = sbase + (c & 1) * (2 * kBufBytes);
+    constexpr int kPieces = kChunk * (D * 2 / 16);   // 16-byte pieces per chunk
+#pragma unroll
+    for (int i = 0; i < kPieces / 32; ++i) {
+      const int piece = i * 32 + lane;
+      const int r = piece / (D * 2 / 16), cpi = piece % (D * 2 / 16);
+      const int key = min(key0 + r, p.Tk - 1);
+      cp_async16(dst + r * kRowBytes + cpi * 16, kbase + static_cast<int64_t>(key) * p.ks[2] + cpi * 8);
+      cp_async16(dst + kBufBytes + r * kRowBytes + cpi * 16, vbase + static_cast<int64_t>(key) * p.vs[2] + cpi * 8);
+    }
+    cp_async_commit();
+  };
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int n = 0; n < D / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float m = ninf, l = 0.f;
+
+  issue(0);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) {
+      issue(c + 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncwarp();
+    const uint32_t kb = sbase + (c & 1) * (2 * kBufBytes);
+    const uint32_t vb = kb + kBufBytes;
+    const int key0 = blk[c / chunks_per_block] * p.sel_block + (c % chunks_per_block) * kChunk;
+
+    // ---- scores: s[nt][0..1] = head g4 against keys key0 + 8*nt + 2*t4 (+1)
+    float s[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      // four 8x8 matrices: (keys 0-7 | 8-15) x (channels 16ks..+7 | +8..+15)
+      uint32_t kf[4];
+      const int mat = lane >> 3, mr = lane & 7;
+      ldmatrix_x4(kf, kb + ((mat >> 1) * 8 + mr) * kRowBytes + ks * 32 + (mat & 1) * 16);
+      mma_16816_top(s[0], qa0[ks], qa2[ks], kf[0], kf[1]);
+      mma_16816_top(s[1], qa0[ks], qa2[ks], kf[2], kf[3]);
+    }
+    // ---- online softmax of row g4 (log2 domain); the four lanes of a row hold 4 keys each
+    float sv[4];
+    float mx = ninf;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int key = key0 + nt * 8 + 2 * t4 + e;
+        sv[nt * 2 + e] = key < p.Tk ? s[nt][e] * p.scale_log2 : ninf;
+        mx = fmaxf(mx, sv[nt * 2 + e]);
+      }
+    }
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m, mx);
+    const float alpha = (m == m_new) ? 1.f : ex2_approx(m - m_new);      // m_new = -inf only if m is too
+    float pr[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) pr[e] = (m_new == ninf) ? 0.f : ex2_approx(sv[e] - m_new);
+    l = l * alpha + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+    m = m_new;
+    const uint32_t pa0 = pack_bf16x2(pr[0], pr[1]);   // keys 2*t4, +1 of the first eight
+    const uint32_t pa2 = pack_bf16x2(pr[2], pr[3]);   // of the second eight
+    // ---- O = O * alpha + P V
+#pragma unroll
+    for (int n2 = 0; n2 < D / 16; ++n2) {
+      // four 8x8 matrices, transposed on load: (keys 0-7 | 8-15) x (channels 16*n2..+7 | +8..+15)
+      uint32_t vf[4];
+      const int mat = lane >> 3, mr = lane & 7;
+      ldmatrix_x4_trans(vf, vb + ((mat & 1) * 8 + mr) * kRowBytes + n2 * 32 + (mat >> 1) * 16);
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        float (&acc)[4] = o[n2 * 2 + h2];
+        acc[0] *= alpha;
+        acc[1] *= alpha;
+        mma_16816_top(acc, pa0, pa2, vf[h2 * 2], vf[h2 * 2 + 1]);
+      }
+    }
+    __syncwarp();   // the buffer is refilled two chunks later
+  }
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  if (g4 < G) {
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+    float* dst = p.o + ((static_cast<int64_t>(b) * p.Hq + g * G + g4) * p.Tq + t) * D + 2 * t4;
+#pragma unroll
+    for (int n = 0; n < D / 8; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0] * inv, o[n][1] * inv);
+  }
+}
+
 // ------------------------------------------------------------------ combine
 // out[b,h,t,:] = sum_j sigmoid(gate[b,t,h,j]) * o_j[b,h,t,:], branches (B,Hq,T,D) fp32 contiguous.
 __global__ void nsa_combine_kernel(const float* __restrict__ o_cmp, const float* __restrict__ o_sel,
@@ -544,8 +708,26 @@ int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   const int64_t total = static_cast<int64_t>(B) * Hkv * Tq;
   const unsigned grid = static_cast<unsigned>((total + 3) / 4);
-  if (D == 64) nsa_selected_attn_kernel<64, 8><<<grid, 128, 0, st>>>(p);
-  else nsa_selected_attn_kernel<128, 8><<<grid, 128, 0, st>>>(p);
+  // tensor-core tiles when the layout allows 16-byte row copies (the usual case), else CUDA cores
+  const bool mma_ok = sel_block % 16 == 0 && nsa_aligned16(q) && (qs[0] * 2) % 4 == 0 && (qs[1] * 2) % 4 == 0 &&
+                      (qs[2] * 2) % 4 == 0;
+  if (mma_ok) {
+    if (D == 64) {
+      const size_t sm = 4 * 4 * 16 * (64 * 2 + 16);
+      SWV_CUDA_OK(cudaFuncSetAttribute(nsa_selected_attn_mma_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sm)));
+      nsa_selected_attn_mma_kernel<64><<<grid, 128, sm, st>>>(p);
+    } else {
+      const size_t sm = 4 * 4 * 16 * (128 * 2 + 16);
+      SWV_CUDA_OK(cudaFuncSetAttribute(nsa_selected_attn_mma_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sm)));
+      nsa_selected_attn_mma_kernel<128><<<grid, 128, sm, st>>>(p);
+    }
+  } else if (D == 64) {
+    nsa_selected_attn_kernel<64, 8><<<grid, 128, 0, st>>>(p);
+  } else {
+    nsa_selected_attn_kernel<128, 8><<<grid, 128, 0, st>>>(p);
+  }
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }

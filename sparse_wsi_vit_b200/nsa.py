@@ -7,7 +7,8 @@ are the builder-defined ones frozen in ``oracle/nsa.py`` (parity unpinned).
   selection  : `swv_nsa_select_blocks_fwd`: block importance recomputed on the tensor cores from
                q, the compressed keys and the log-sum-exp, then an arg-max kernel per query;
   selected   : `swv_nsa_selected_attn_fwd`: one warp per (kv group, query) reads each selected
-               key / value row once for all heads of the group;
+               key / value row once for all heads of the group (the heads are the rows of
+               warp-level tensor-core tiles);
   window     : the block-sparse kernel in token-pattern mode (|i-j| <= window/2);
   gate       : `swv_nsa_combine_fwd`, the sigmoid-weighted sum.
 """
