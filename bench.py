@@ -361,13 +361,21 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tokens", type=int, default=65536)
+    ap.add_argument("--tokens", type=int, default=None, help="sequence length (default 65536; with --workload "
+                    "block_sparse / nsa: run only this size)")
     ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "block_sparse", "nsa", "encoder", "static"])
     args = ap.parse_args()
     if args.workload != "dsa_fwd":
         from sparse_wsi_vit_b200.benchmarks import WORKLOADS
-        WORKLOADS[args.workload]()
+        kw = {}
+        if args.tokens is not None and args.workload == "block_sparse":
+            kw["sizes"] = (args.tokens,)
+        elif args.tokens is not None and args.workload in ("nsa", "static"):
+            kw["tokens"] = args.tokens
+        WORKLOADS[args.workload](**kw)
         return
+    if args.tokens is None:
+        args.tokens = 65536
     if args.impl == "reference":
         run_reference(args)
     else:
