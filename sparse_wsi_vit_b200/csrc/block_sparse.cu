@@ -139,8 +139,10 @@ __global__ void __launch_bounds__(320, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int h = blockIdx.x % p.H;
-  const int qb = (blockIdx.x / p.H) % p.nQB;
+  // query blocks fastest, heads slowest: the CTAs in flight at any time work on one or two heads,
+  // whose keys and values stay in L2 (all heads' K/V together can exceed it)
+  const int qb = blockIdx.x % p.nQB;
+  const int h = (blockIdx.x / p.nQB) % p.H;
   const int b = blockIdx.x / (p.H * p.nQB);
   const int list0 = p.row_ptr[qb];
   const int nblk = p.row_ptr[qb + 1] - list0;

@@ -390,6 +390,7 @@ __global__ void key_norm_max_kernel(const __nv_bfloat16* __restrict__ k, int64_t
   }
 }
 
+template <bool kSplit>      // the key range of a (query tile, head pair) is shared by p.split CTAs
 __global__ void __launch_bounds__(kAttnThreads, 1)
     dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
                            const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -404,13 +405,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int cta = blockIdx.x / p.split;          // (batch, query tile, head pair)
-  const int part = blockIdx.x - cta * p.split;   // which share of the key tiles
+  const int cta = kSplit ? blockIdx.x / p.split : blockIdx.x;     // (batch, query tile, head pair)
+  const int part = kSplit ? blockIdx.x - cta * p.split : 0;       // which share of the key tiles
   const int hp = cta % p.nHP;
   const int qt = (cta / p.nHP) % p.nQT;
   const int b = cta / (p.nHP * p.nQT);
-  const int kt0 = static_cast<int>(static_cast<int64_t>(part) * p.nKT / p.split);        // first key tile
-  const int nKT = static_cast<int>(static_cast<int64_t>(part + 1) * p.nKT / p.split) - kt0;   // key tiles of this CTA
+  const int kt0 = kSplit ? static_cast<int>(static_cast<int64_t>(part) * p.nKT / p.split) : 0;   // first key tile
+  const int nKT = kSplit ? static_cast<int>(static_cast<int64_t>(part + 1) * p.nKT / p.split) - kt0 : p.nKT;
   const int h0 = hp * 2;
   const int nh = (h0 + 1 < p.H) ? 2 : 1;   // heads handled by this CTA
 
@@ -706,7 +707,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       }
     };
 
-    if (p.split == 1) {
+    if constexpr (!kSplit) {
       if (duty && ok) {
         for (int c = 0; c < nd / 16; ++c) {
           uint32_t o[16];
@@ -909,10 +910,16 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
     key_norm_max_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
         static_cast<const __nv_bfloat16*>(k), ks[0], ks[1], ks[2], B, H, Tk, kmax2);
   }
-  SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                   static_cast<int>(attn_smem_bytes())));
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP * p.split;
-  dsa_attn_masked_kernel<<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  if (p.split == 1) {
+    SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(attn_smem_bytes())));
+    dsa_attn_masked_kernel<false><<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  } else {
+    SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(attn_smem_bytes())));
+    dsa_attn_masked_kernel<true><<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  }
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }
