@@ -37,10 +37,12 @@ METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 # key-norm maximum, attention
 KERNELS_PER_STEP = 12
 
-# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch on the 65536-token workload: the ncu
-# capture at 16384 tokens (profiles/dsa_attn_masked_kernel_16k.md: 59.5 MB read + 5.0 MB written)
-# times 4 -- this kernel's DRAM traffic is its inputs and outputs, which grow with T, not T^2.
-ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 258e6, 16384: 64.5e6}
+# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, measured with ncu
+# (dram__bytes_read.sum + dram__bytes_write.sum, one pass): 5.26 GB + 0.07 GB on the 65536-token workload
+# (profiles/dsa_attn_masked_kernel_64k_dram.md) -- K, V of all heads and the indexer keys, 144 MiB, do
+# not fit the 126 MB L2, so key tiles are re-fetched; 59.5 MB + 5.0 MB at 16384 tokens, where they fit
+# (profiles/dsa_attn_masked_kernel_16k.md).
+ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 5.327e9, 16384: 64.5e6}
 
 
 def measured_peaks():
