@@ -3,7 +3,7 @@ branches, sigmoid gate).
 
 TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).  PARITY UNPINNED: the reference contains
 no NSA code (only a docstring intent, scripts/virchow_preprocess.py:44-53); every choice below is
-frozen here and stated in DESIGN.md.
+frozen here (and restated in the design notes of the repository).
 
   q (Hq, T, D), k, v (Hkv, T, D), gate logits g (T, Hq, 3) ordered [compressed, selected, window];
   G = Hq / Hkv query heads share one key/value head (head h uses kv head h // G).

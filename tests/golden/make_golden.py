@@ -121,7 +121,9 @@ def make_rope(ref_rope):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: TRITON_INTERPRET=1 python tests/golden/make_golden.py <path to a sparse-wsi-vit checkout>")
+    ref = sys.argv[1]
     sys.path.insert(0, os.path.join(ref, "src"))
     from sparse_wsi_vit.models.deepseek_sparse_attention_kernels import kernels as ref_kernels
     from sparse_wsi_vit.models import deepseek_sparse_attention as ref_mod
