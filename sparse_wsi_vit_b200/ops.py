@@ -74,7 +74,9 @@ def mask_bytes(B, Tq, Tk):
 
 def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=None):
     """q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID), w (IH,) -> idx int32, valid f32, scores f32,
-    each (B,Tq,top_k), keys in ascending order; optionally the tile-major bitmask."""
+    each (B,Tq,top_k), keys in ascending order.  With `want_mask` also the selection handle
+    ``(bitmask, workspace)`` that ``dsa_attention_masked`` consumes; it owns both buffers, so it
+    stays valid across later indexer calls."""
     _require_cuda(q_idx, k_idx, w)
     if q_idx.dim() != 4 or k_idx.dim() != 4:
         raise SwvError("indexer projections must be (B, T, IH, ID)")
@@ -92,7 +94,9 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
         scores = torch.empty((B, Tq, top_k), dtype=torch.float32, device=dev)
     else:
         idx, valid, scores = out
-    ws = _buffer("ws", dev, workspace_bytes(B, Tq, Tk))
+    nws = workspace_bytes(B, Tq, Tk)
+    # a selection handle keeps its own workspace (the attention reads it); plain calls share one
+    ws = torch.empty(nws, dtype=torch.uint8, device=dev) if want_mask else _buffer("ws", dev, nws)
     mptr = None
     if want_mask:
         if mask is None:

@@ -292,3 +292,30 @@ def test_masked_attention_short_query_range(swv, K):
     _check(swv)
     assert float((o - o2).abs().max()) < 2e-2
     assert float((o - o2).abs().mean()) < 1e-3
+
+
+def test_split_paths_batch_odd_heads_ragged(swv):
+    """The key-range splits with a batch of 2, an odd number of heads (a CTA with one head), query and
+    key counts that are not multiples of the tile: fused path == gather path, indices == stable top-k."""
+    B, Tq, Tk, H, D, K = 2, 200, 8192 + 37, 3, 64, 300
+    g = torch.Generator().manual_seed(23)
+    q = (torch.randn(B, H, Tq, D, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    k = torch.randn(B, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    v = torch.randn(B, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    qi = (torch.randn(B, Tq, 4, 64, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    ki = (torch.randn(B, Tk, 4, 64, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    w = torch.randn(4, generator=g).to(_dev())
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    # (the selection refers to the library's cached workspace: use it before the next indexer call)
+    o = torch.zeros((B, H, Tq, D), dtype=torch.float32, device=_dev())
+    swv.dsa_attention_masked(q, k, v, sel, o)
+    o2 = torch.zeros_like(o)
+    swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o2)
+    _check(swv)
+    for b in range(B):
+        full = own_scores(qi[b:b + 1].contiguous(), ki[b:b + 1].contiguous(), w)[0].cpu()
+        ridx, _, rsel = O.topk_lower_index(full, K)
+        assert torch.equal(idx[b].cpu(), ridx)
+        assert torch.equal(scores[b].cpu(), rsel)
+    assert float((o - o2).abs().max()) < 2e-2
+    assert float((o - o2).abs().mean()) < 1e-3

@@ -10,7 +10,8 @@ DEV = torch.device("cuda:0")
 
 
 @pytest.mark.parametrize("T,Hq,Hkv,D,topk,window", [(700, 4, 2, 128, 4, 128), (1500, 8, 2, 64, 16, 512),
-                                                    (300, 2, 1, 128, 16, 64)])
+                                                    (300, 2, 1, 128, 16, 64), (1111, 8, 1, 128, 8, 256),
+                                                    (900, 16, 2, 64, 4, 128)])
 def test_nsa_vs_oracle(T, Hq, Hkv, D, topk, window):
     import sparse_wsi_vit_b200 as swv
     from sparse_wsi_vit_b200.nsa import nsa_attention
