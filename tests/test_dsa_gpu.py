@@ -38,7 +38,7 @@ def _check(swv):
 
 
 @pytest.mark.parametrize("T,K", [(1, 8), (5, 8), (63, 8), (64, 64), (65, 16), (127, 64), (200, 256), (1000, 64),
-                                 (1000, 2048), (384, 128)])
+                                 (1000, 2048), (384, 128), (500, 33), (700, 100), (3000, 7)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_indexer_topk_small(swv, T, K, dtype):
     q, k, v, qi, ki, w = make_dsa_inputs(T, 1, 64, 4, 64, seed=T * 7 + K, dtype=dtype, device=_dev())
