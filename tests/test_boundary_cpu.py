@@ -47,6 +47,22 @@ def test_size_queries(swv):
     assert n.value == 2 * 2 * 3 * 128 * 16
     assert L.swv_dsa_workspace_bytes(0, 1, 1, ctypes.byref(n)) == -4
     assert L.swv_dsa_workspace_bytes(1, 1, 1, None) == -1
+    # key-range splits: only where they fill the SMs better
+    small, big = ctypes.c_size_t(), ctypes.c_size_t()
+    assert L.swv_dsa_workspace_bytes(1, 16384, 16384, ctypes.byref(small)) == 0     # 128 tiles: no split
+    assert L.swv_dsa_workspace_bytes(1, 8192, 65536, ctypes.byref(big)) == 0        # 64 tiles, 512 key tiles: split
+    assert big.value > 2 * 64 * 128 * 259 * 4
+    assert L.swv_dsa_attn_scratch_bytes(1, 8, 65536, 65536, ctypes.byref(n)) == 0 and n.value == 0
+    assert L.swv_dsa_attn_scratch_bytes(1, 8, 8192, 65536, ctypes.byref(n)) == 0 and n.value > 0
+    assert L.swv_dsa_attn_scratch_bytes(1, 8, 256, 1024, ctypes.byref(n)) == 0 and n.value == 0
+    assert L.swv_dsa_attn_scratch_bytes(0, 8, 1, 1, ctypes.byref(n)) == -4
+    # NSA sizes
+    assert L.swv_nsa_importance_bytes(1, 2, 65536, 4095, 16, 64, ctypes.byref(n)) == 0
+    assert n.value == 2 * 65536 * 1024 * 4
+    assert L.swv_nsa_importance_bytes(1, 2, 65536, 4095, 16, 40, ctypes.byref(n)) == -4
+    assert L.swv_nsa_workspace_bytes(1, 16, 2, 65536, 128, 32, 16, 64, 16, 512, ctypes.byref(n)) == 0
+    assert n.value > 3 * 16 * 65536 * 128 * 4
+    assert L.swv_nsa_workspace_bytes(1, 16, 3, 65536, 128, 32, 16, 64, 16, 512, ctypes.byref(n)) == -4
 
 
 def test_argument_validation_happens_before_any_launch(swv):
