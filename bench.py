@@ -269,44 +269,15 @@ def run_ours(args):
 
     copy_stream = torch.cuda.Stream(dev)
 
-    def e2e_step():
-        # the indexer needs only its own two inputs: q, k, v are uploaded on a second stream while
-        # the top-k passes run, and the attention waits for them
-        dbuf[3].copy_(pinned[3], non_blocking=True)
-        dbuf[4].copy_(pinned[4], non_blocking=True)
-        qkv_ready = None
-        if world == 1:
-            copy_stream.wait_stream(cur)
-            with torch.cuda.stream(copy_stream):
-                for i in range(3):
-                    dbuf[i].copy_(pinned[i], non_blocking=True)
-            qkv_ready = copy_stream.record_event()
-        else:
-            # sharded: q, k, v go up on the communication stream, ahead of the K/V all-gathers that
-            # run there, while this stream gathers the indexer keys and runs the top-k sweeps
-            comm.wait_stream(cur)
-            with torch.cuda.stream(comm):
-                for i in range(3):
-                    dbuf[i].copy_(pinned[i], non_blocking=True)
-        o, _ = step(*dbuf, qkv_ready=qkv_ready)
-        if world == 1:
-            # read the result back on the copy stream so the next step's uploads and top-k passes
-            # need not wait for it (the download engine is separate from the upload engine)
-            done = cur.record_event()
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(done)
-                o_host.copy_(o, non_blocking=True)
-                o.record_stream(copy_stream)
-        else:
-            o_host.copy_(o, non_blocking=True)
-
-    # Single GPU: a double-buffered pipeline, as a service that streams slides would run it.  The five
-    # input tensors of step s + 1 are copied from pinned host memory (upload stream, second set of
-    # device buffers) while step s computes; the output of step s goes back on the download stream
-    # while step s + 1 computes.  Every step's uploads and download happen inside the timed region;
-    # the first step's upload and the last step's download are not hidden.
-    up_stream = torch.cuda.Stream(dev) if world == 1 else None
-    dbuf2 = [torch.empty_like(t) for t in dbuf] if world == 1 else None
+    # A double-buffered pipeline, as a service that streams slides would run it.  The five input
+    # tensors of step s + 1 are copied from pinned host memory (upload stream, second set of device
+    # buffers) while step s computes; the output of step s goes back on the download stream while
+    # step s + 1 computes.  Every step's uploads and download happen inside the timed region; the
+    # first step's upload and the last step's download are not hidden.  On one GPU the step starts as
+    # soon as the two indexer tensors are up (the attention waits for q, k, v); a sharded step
+    # starts when all five are up, because its K/V all-gather is issued at once.
+    up_stream = torch.cuda.Stream(dev)
+    dbuf2 = [torch.empty_like(t) for t in dbuf]
 
     def e2e_pipeline(n):
         sets = (dbuf, dbuf2)
@@ -330,8 +301,12 @@ def run_ours(args):
             slot = s_ & 1
             if s_ + 1 < n:
                 nxt = upload(slot ^ 1)
-            cur.wait_event(ev_idx)
-            o, _ = step(*sets[slot], qkv_ready=ev_qkv)
+            if world == 1:
+                cur.wait_event(ev_idx)
+                o, _ = step(*sets[slot], qkv_ready=ev_qkv)
+            else:
+                cur.wait_event(ev_qkv)
+                o, _ = step(*sets[slot])
             done[slot] = cur.record_event()
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(done[slot])
@@ -340,21 +315,12 @@ def run_ours(args):
         cur.wait_stream(copy_stream)           # the last download belongs to the timed region
         cur.wait_stream(up_stream)
 
-    if world == 1:
-        e2e_pipeline(2)
-    else:
-        for _ in range(2):
-            e2e_step()
+    e2e_pipeline(2)
     barrier()
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record(cur)
-    if world == 1:
-        e2e_pipeline(args.steps)
-    else:
-        for _ in range(args.steps):
-            e2e_step()
-        cur.wait_stream(copy_stream)
+    e2e_pipeline(args.steps)
     e1.record(cur)
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
@@ -375,8 +341,7 @@ def run_ours(args):
                        "parallelism": f"sp{world}" if world > 1 else "single",
                        "l2": "inputs+outputs per step (>1.9 GiB) exceed the 126 MB L2"},
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
-                    "mode": "double-buffered uploads/downloads overlapped with the neighbouring steps" if world == 1
-                            else "uploads on the communication stream, per step",
+                    "mode": "double-buffered uploads/downloads overlapped with the neighbouring steps",
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned) * world,
                     "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world},
             "gpu_launches": args.steps * KERNELS_PER_STEP * world,
