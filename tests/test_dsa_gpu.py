@@ -306,7 +306,6 @@ def test_split_paths_batch_odd_heads_ragged(swv):
     ki = (torch.randn(B, Tk, 4, 64, generator=g) / 8).to(torch.bfloat16).to(_dev())
     w = torch.randn(4, generator=g).to(_dev())
     idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
-    # (the selection refers to the library's cached workspace: use it before the next indexer call)
     o = torch.zeros((B, H, Tq, D), dtype=torch.float32, device=_dev())
     swv.dsa_attention_masked(q, k, v, sel, o)
     o2 = torch.zeros_like(o)
@@ -319,3 +318,48 @@ def test_split_paths_batch_odd_heads_ragged(swv):
         assert torch.equal(scores[b].cpu(), rsel)
     assert float((o - o2).abs().max()) < 2e-2
     assert float((o - o2).abs().mean()) < 1e-3
+
+
+def _random_case(seed):
+    r = np.random.RandomState(seed)
+    B = int(r.choice([1, 1, 2]))
+    Tq = int(r.randint(1, 600))
+    Tk = Tq if r.rand() < 0.4 else int(r.randint(Tq, 9000))
+    H = int(r.randint(1, 5))
+    K = int(r.randint(1, min(Tk, 2500) + 1))
+    quantised = bool(r.rand() < 0.3)                     # few distinct score values: many ties at the threshold
+    return B, Tq, Tk, H, K, quantised
+
+
+@pytest.mark.parametrize("seed", list(range(100, 112)))
+def test_random_shapes(swv, seed):
+    """Seeded random shapes (batch, ragged query / key counts, 1-4 heads, any top_k, some with heavily
+    tied scores): indices == stable top-k of the library's own scores, fused path == gather path."""
+    B, Tq, Tk, H, K, quantised = _random_case(seed)
+    D = 64
+    g = torch.Generator().manual_seed(seed)
+    q = (torch.randn(B, H, Tq, D, generator=g) / 8).to(torch.bfloat16).to(_dev())
+    k = torch.randn(B, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    v = torch.randn(B, H, Tk, D, generator=g).to(torch.bfloat16).to(_dev())
+    qi = torch.randn(B, Tq, 4, 64, generator=g) / 8
+    ki = torch.randn(B, Tk, 4, 64, generator=g) / 8
+    if quantised:
+        qi, ki = (qi * 4).round() / 4, (ki * 4).round() / 4
+    qi, ki = qi.to(torch.bfloat16).to(_dev()), ki.to(torch.bfloat16).to(_dev())
+    w = torch.randn(4, generator=g).to(_dev())
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    o = torch.zeros((B, H, Tq, D), dtype=torch.float32, device=_dev())
+    swv.dsa_attention_masked(q, k, v, sel, o)
+    o2 = torch.zeros_like(o)
+    swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o2)
+    _check(swv)
+    tag = f"B={B} Tq={Tq} Tk={Tk} H={H} K={K} quantised={quantised}"
+    for b in range(B):
+        full = own_scores(qi[b:b + 1].contiguous(), ki[b:b + 1].contiguous(), w)[0].cpu()
+        ridx, rvalid, rsel = O.topk_lower_index(full, K)
+        assert torch.equal(idx[b].cpu(), ridx), tag
+        assert torch.equal(valid[b].cpu(), rvalid), tag
+        assert torch.equal(scores[b].cpu(), rsel), tag
+    assert torch.isfinite(o).all(), tag
+    assert float((o - o2).abs().max()) < 2e-2, tag
+    assert float((o - o2).abs().mean()) < 1e-3, tag
