@@ -16,7 +16,9 @@ in HBM; `e2e` is the same through the public API with inputs in pinned host
 memory and the output read back, copies inside the timed region.
 """
 import argparse
+import datetime
 import json
+import math
 import os
 import statistics
 import subprocess
@@ -72,14 +74,19 @@ def make_inputs(T, seed, device, pinned=False):
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    """nvidia-smi polling every 100 ms in a child process.  It is started before the warm-up steps
+    (its start-up takes longer than a short timed region) and every sample carries its time stamp;
+    `stop()` keeps the samples between `begin()` and `end()`."""
+    QUERY = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    MIN_WINDOW_S = 1.0
 
     def __init__(self, gpu_index):
         self.gpu = gpu_index
         self.proc = None
         self.path = None
+        self.t_begin = self.t_end = None
 
     def start(self):
         try:
@@ -91,6 +98,12 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
+    def begin(self):
+        self.t_begin = datetime.datetime.now()
+
+    def end(self):
+        self.t_end = datetime.datetime.now()
+
     def stop(self):
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
@@ -100,25 +113,37 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        rows = []                                  # (inside the window?, sm, max sm, reasons)
         try:
             with open(self.path) as f:
                 for line in f:
                     c = [x.strip() for x in line.split(",")]
-                    if len(c) < 9:
+                    if len(c) < 10:
                         continue
                     try:
-                        sm.append(float(c[1]))
-                        mx.append(float(c[2]))
+                        vals = (float(c[2]), float(c[3]))
                     except ValueError:
                         continue
-                    for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
-                                          "sw_power_cap"), c[5:9]):
-                        if val.lower().startswith("active"):
-                            reasons.add(name)
+                    try:
+                        ts = datetime.datetime.strptime(c[0], "%Y/%m/%d %H:%M:%S.%f")
+                        inside = self.t_begin is None or self.t_begin <= ts <= (self.t_end or ts)
+                    except ValueError:
+                        inside = False
+                    rows.append((inside, *vals, [name for name, val in zip(
+                        ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[6:10])
+                        if val.lower().startswith("active")]))
             os.unlink(self.path)
         except Exception:
             pass
+        kept = [r for r in rows if r[0]]
+        if not kept and rows and self.t_begin is not None and self.t_end is not None:
+            # time stamps unreadable or in another zone: the last samples cover the window, which
+            # ended just before the sampler was stopped
+            n = max(1, int((self.t_end - self.t_begin).total_seconds() / 0.1))
+            kept = rows[-n:]
+        sm = [r[1] for r in kept]
+        mx = [r[2] for r in kept]
+        reasons = {name for r in kept for name in r[3]}
         if sm:
             out = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
                    "samples": len(sm)}
@@ -243,24 +268,40 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         step(q, k, v, qi, ki)
     ops.check_status(dev, "bench warm-up")
 
     # ---- device-resident timing
-    sampler = ClockSampler(local_rank)
     barrier()
-    if rank == 0:
-        sampler.start()
+    sampler.begin()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record(cur)
+    _h0 = time.perf_counter()
     for i in range(args.steps):
         step(q, k, v, qi, ki, timed_idx=i)
+    _h1 = time.perf_counter()
     t1.record(cur)
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     ms = t0.elapsed_time(t1) / args.steps
+    # A timed region shorter than a few sampling periods gives the clock sampler nothing to read:
+    # the same step keeps running, untimed, until the sampled window is MIN_WINDOW_S long (the
+    # count comes from rank 0, so that every rank issues the same collectives).
+    extra = torch.tensor([max(0, math.ceil((ClockSampler.MIN_WINDOW_S * 1e3 - ms * args.steps) / ms))], device=dev)
+    if world > 1:
+        dist.broadcast(extra, 0)
+    for _ in range(int(extra.item())):
+        step(q, k, v, qi, ki)
+    barrier()
+    sampler.end()
+    clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = (f"the {args.steps} timed steps" if int(extra.item()) == 0 else
+                            f"the {args.steps} timed steps and {int(extra.item())} identical untimed steps after them")
     ops.check_status(dev, "bench timed region")
 
     # ---- end to end: pinned host inputs -> device, forward, output back to pinned host
@@ -282,6 +323,8 @@ def run_ours(args):
     def e2e_pipeline(n):
         sets = (dbuf, dbuf2)
         done = [None, None]                    # compute of the step that last read each buffer set
+        outs = [None, None]                    # output of that step, kept until its download is ordered
+        dl_done = [None, None]                 # ... and the download of it
 
         def upload(slot):
             with torch.cuda.stream(up_stream):
@@ -301,6 +344,13 @@ def run_ours(args):
             slot = s_ & 1
             if s_ + 1 < n:
                 nxt = upload(slot ^ 1)
+            # The output of two steps ago is released here, after this stream has been ordered behind
+            # its download: the allocator hands the block to this step at once.  (Marking the output
+            # as in use by the download stream instead would keep every block out of the pool until
+            # the GPU catches up with the host, one device allocation per step.)
+            if dl_done[slot] is not None:
+                cur.wait_event(dl_done[slot])
+                outs[slot] = None
             if world == 1:
                 cur.wait_event(ev_idx)
                 o, _ = step(*sets[slot], qkv_ready=ev_qkv)
@@ -311,7 +361,9 @@ def run_ours(args):
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(done[slot])
                 o_host.copy_(o, non_blocking=True)
-                o.record_stream(copy_stream)
+                dl_done[slot] = copy_stream.record_event()
+            outs[slot] = o
+            del o
         cur.wait_stream(copy_stream)           # the last download belongs to the timed region
         cur.wait_stream(up_stream)
 
@@ -320,7 +372,9 @@ def run_ours(args):
     e0 = torch.cuda.Event(enable_timing=True)
     e1 = torch.cuda.Event(enable_timing=True)
     e0.record(cur)
+    _h2 = time.perf_counter()
     e2e_pipeline(args.steps)
+    _h3 = time.perf_counter()
     e1.record(cur)
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
@@ -340,7 +394,10 @@ def run_ours(args):
                        "indexer": f"{IH}x{ID} tf32", "top_k": TOP_K, "batch": 1,
                        "parallelism": f"sp{world}" if world > 1 else "single",
                        "l2": "inputs+outputs per step (>1.9 GiB) exceed the 126 MB L2"},
+            # host time rank 0 spends issuing one step (no waiting): far below ms_per_step = not launch-bound
+            "host_issue_ms_per_step": (_h1 - _h0) * 1e3 / args.steps,
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
+                    "host_issue_ms_per_step": (_h3 - _h2) * 1e3 / args.steps,
                     "mode": "double-buffered uploads/downloads overlapped with the neighbouring steps",
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned) * world,
                     "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world},
