@@ -89,17 +89,36 @@ def sharded_dsa_attention(q_loc, k_loc, v_loc, qi_loc, ki_loc, w, top_k, plan: S
     use_side = comm_stream is not None and k_loc.is_cuda and plan.world > 1
     ki_all = all_gather_tokens(ki_loc, plan, group)
     if use_side:
+        # Ordering contract: the gathers run on `comm_stream` behind everything already queued on
+        # the current stream; the attention waits for `kv_ready` on the current stream.  The gathered
+        # buffers are allocated while `comm_stream` is current, so they are marked as used by the
+        # current stream too: the caching allocator must not hand them back to `comm_stream` while
+        # the attention kernels still read them.
         cur = torch.cuda.current_stream(k_loc.device)
         comm_stream.wait_stream(cur)
         with torch.cuda.stream(comm_stream):
             k_all = all_gather_tokens(k_loc, plan, group)
             v_all = all_gather_tokens(v_loc, plan, group)
         kv_ready = comm_stream.record_event()
+        k_all.record_stream(cur)
+        v_all.record_stream(cur)
     else:
         k_all = all_gather_tokens(k_loc, plan, group)
         v_all = all_gather_tokens(v_loc, plan, group)
         kv_ready = None
     T = plan.total
+    if plan.local == 0:
+        # An empty tail shard (a short slide on many ranks) has taken part in every collective
+        # above and has no query rows of its own: nothing to launch.
+        B, _, H, D = q_loc.shape
+        o = q_loc.new_zeros((B, H, 0, D), dtype=out_dtype or q_loc.dtype)
+        if kv_ready is not None:
+            torch.cuda.current_stream(k_loc.device).wait_event(kv_ready)
+        if not return_topk:
+            return o
+        return (o, torch.zeros((B, 0, top_k), dtype=torch.int32, device=q_loc.device),
+                torch.zeros((B, 0, top_k), dtype=torch.float32, device=q_loc.device),
+                torch.zeros((B, 0, top_k), dtype=torch.float32, device=q_loc.device))
     q = q_loc.transpose(1, 2)                    # (B, H, T_local, D) view
     k = k_all[:, :T].transpose(1, 2)             # (B, H, T, D) view of the gathered buffer
     v = v_all[:, :T].transpose(1, 2)
@@ -107,19 +126,25 @@ def sharded_dsa_attention(q_loc, k_loc, v_loc, qi_loc, ki_loc, w, top_k, plan: S
                    **({"kv_ready": kv_ready} if kv_ready is not None else {}))
 
 
-def sharded_encoder_forward(encoder, patches_local, plan: ShardPlan, group=None, comm_stream=None, compute=None):
+def sharded_encoder_forward(encoder, patches_local, plan: ShardPlan, group=None, comm_stream=None, compute=None,
+                            coords_local=None):
     """Forward of a ``DSAViTSlideEncoder`` with the token sequence [CLS..., patches...] sharded over
     the ranks of `group` (weights replicated).
 
     `plan` shards the FULL sequence of ``encoder.num_cls + n_patches`` tokens; `patches_local` holds
     the patch embeddings of this rank's slice, (B, n_local_patches, in_features): rank 0's slice
     starts with the CLS tokens, so it gets ``plan.local - num_cls`` patches, every other rank
-    ``plan.local``.  Token-local work (projections, LayerNorm, MLP) runs on the shard with no
-    communication; each attention layer all-gathers the indexer keys, K and V
-    (``sharded_dsa_attention``).  The CLS rows live on rank 0, which computes the logits and
+    ``plan.local`` (possibly none: a short slide on many ranks leaves empty tail shards, which
+    still take part in every collective).  Token-local work (projections, LayerNorm, 2-D RoPE, MLP)
+    runs on the shard with no communication; each attention layer all-gathers the indexer keys, K
+    and V (``sharded_dsa_attention``).  With `coords_local` ((B, n_local_patches, 2), the (y, x)
+    coordinates of this rank's patches) and an encoder built with ``rope_coord_high``, q and k of
+    the local patch tokens are rotated before the gather, CLS tokens excepted
+    (models/vit_5/models_vit5.py:84-90).  The CLS rows live on rank 0, which computes the logits and
     broadcasts them.  Returns {"logits": (B, out_features)} on every rank, the same dictionary
     ``DSAViTSlideEncoder.forward`` returns (deepseek_sparse_attention.py:267-305).
     """
+    from .modules import rope_qk_
     C = encoder.num_cls
     if plan.world > 1 and plan.per_rank < C:
         raise ValueError("the CLS tokens must fit into rank 0's shard")
@@ -127,20 +152,25 @@ def sharded_encoder_forward(encoder, patches_local, plan: ShardPlan, group=None,
         patches_local = patches_local.unsqueeze(0)
     B = patches_local.shape[0]
     x = encoder.input_proj(patches_local)
+    n_cls_local = C if plan.rank == 0 else 0
     if plan.rank == 0:
         x = torch.cat([encoder.cls_tokens.expand(B, -1, -1).to(x.dtype), x], dim=1)
-    if x.shape[1] != plan.local:
-        raise ValueError(f"rank {plan.rank} holds {x.shape[1]} tokens, the plan says {plan.local}")
+    Tl = x.shape[1]
+    if Tl != plan.local:
+        raise ValueError(f"rank {plan.rank} holds {Tl} tokens, the plan says {plan.local}")
+    rope = coords_local is not None and getattr(encoder, "rope_coord_high", None) is not None
     for blk in encoder.blocks:
         attn = blk.attn
         H, D = attn.attention_heads, attn.head_dim
         y = blk.norm1(x)
-        qkv = attn.qkv_proj(y).view(B, -1, 3, H, D)
+        qkv = attn.qkv_proj(y).view(B, Tl, 3, H, D)
+        if rope and Tl > 0:
+            rope_qk_(qkv, coords_local, encoder.rope_coord_high, n_cls_local, encoder.rope_theta)
         q_idx, k_idx = attn.indexer_proj(y)
         o = sharded_dsa_attention(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], q_idx, k_idx, attn.indexer_head_weights,
                                   attn.top_k, plan, group=group, out_dtype=y.dtype, compute=compute,
                                   comm_stream=comm_stream)
-        x = x + blk.drop1(attn.out_proj(o.transpose(1, 2).reshape(B, -1, H * D).to(y.dtype)))
+        x = x + blk.drop1(attn.out_proj(o.transpose(1, 2).reshape(B, Tl, H * D).to(y.dtype)))
         x = x + blk.mlp(blk.norm2(x))
     logits = torch.empty((B, encoder.out_features), dtype=x.dtype, device=x.device)
     if plan.rank == 0:
@@ -150,3 +180,38 @@ def sharded_encoder_forward(encoder, patches_local, plan: ShardPlan, group=None,
     if plan.world > 1:
         dist.broadcast(logits, src=0, group=group)
     return {"logits": logits}
+
+
+def local_patch_range(plan: ShardPlan, num_cls: int):
+    """Half-open range of PATCH indices (CLS tokens not counted) held by the rank of `plan`, which
+    shards the full sequence [CLS..., patches...]."""
+    return max(plan.start - num_cls, 0), max(plan.stop - num_cls, 0)
+
+
+def sharded_ragged_forward(encoder, slides, world: int, rank: int, coords=None, group=None, comm_stream=None,
+                           compute=None, align: int = 128):
+    """A ragged batch of slides through a sharded ``DSAViTSlideEncoder``: the slides run back to
+    back, each one split over ALL ranks (``plan_ragged``), so every all-gather is regular and the
+    load is balanced whatever the slide lengths.  The reference asserts batch size 1
+    (experiments/datamodules/h5_datamodule.py:22-24); this lifts it.
+
+    `slides`: list of (n_i, in_features) arrays -- tensors, or anything with ``.shape`` that can be
+    sliced by rows and converted with ``torch.as_tensor`` (a lazily read feature bag): a rank
+    touches only rows [lo, hi) of each slide, its own shard.  `coords`: matching list of (n_i, 2)
+    arrays or None.  Returns {"logits": (n_slides, out_features)} on every rank.
+    """
+    par = next(encoder.parameters())
+    plans = plan_ragged([int(s.shape[0]) + encoder.num_cls for s in slides], world, rank, align)
+    rows = []
+    for i, plan in enumerate(plans):
+        lo, hi = local_patch_range(plan, encoder.num_cls)
+        x = torch.as_tensor(slides[i][lo:hi]).to(par.device, non_blocking=True)
+        if not torch.is_autocast_enabled():
+            x = x.to(par.dtype)
+        c = None
+        if coords is not None:
+            c = torch.as_tensor(coords[i][lo:hi]).to(par.device, non_blocking=True)[None]
+        out = sharded_encoder_forward(encoder, x[None], plan, group=group, comm_stream=comm_stream, compute=compute,
+                                      coords_local=c)
+        rows.append(out["logits"][0])
+    return {"logits": torch.stack(rows, dim=0)}

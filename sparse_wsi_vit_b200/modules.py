@@ -14,7 +14,28 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
-from .ops import dsa_sparse_attention
+from .ops import dsa_sparse_attention, rope2d
+
+
+def rope_qk_(qkv: Tensor, coords: Tensor, coord_high: float, num_cls: int = 0, theta: float = 10000.0) -> None:
+    """2-D rotary embedding, in place, on the q and k slices of a fused projection output
+    ``qkv (B, T, 3, H, D)``: patch tokens turn with their (y, x) coordinates, the ``num_cls``
+    leading CLS tokens are left as they are -- the placement of the reference's ViT-5 attention
+    (src/sparse_wsi_vit/models/vit_5/models_vit5.py:84-90, rope.py:72-97).
+    ``coords`` is (B, T - num_cls, 2) or (T - num_cls, 2), in the units of ``coord_high``."""
+    B, T = qkv.shape[:2]
+    c = coords.reshape(B, -1, 2) if coords.dim() == 3 else coords.reshape(1, -1, 2).expand(B, -1, -1)
+    if c.shape[1] != T - num_cls:
+        raise ValueError(f"coords cover {c.shape[1]} tokens, the sequence has {T - num_cls} patch tokens")
+    if T == 0:
+        return
+    for b in range(B):
+        cb = c[b].to(torch.float32)
+        if num_cls:
+            cb = torch.cat([cb.new_zeros((num_cls, 2)), cb], dim=0)
+        for i in (0, 1):
+            x = qkv[b, :, i]
+            rope2d(x, cb, coord_high, theta=theta, skip_tokens=num_cls, out=x)
 
 
 class IndexerProjection(nn.Module):
@@ -57,12 +78,19 @@ class DeepSeekSparseAttention(nn.Module):
         self.qkv_proj = nn.Linear(d_model, 3 * d_model)
         self.out_proj = nn.Linear(d_model, d_model)
 
-    def forward(self, x):
+    def forward(self, x, coords=None, coord_high=None, num_cls=0, rope_theta=10000.0):
+        """``x (B, T, d_model)``.  The reference's layer has no positional term; with ``coords``
+        (and ``coord_high``) q and k of the patch tokens are first turned by the 2-D rotary
+        embedding (``rope_qk_``), the ``num_cls`` leading tokens excepted."""
         B, T, _ = x.shape
         H, D = self.attention_heads, self.head_dim
         # [q | k | v] outermost, then head, then head-dim; the kernels take the
         # (B, H, T, D) views as they are (strided), no contiguous copies.
         qkv = self.qkv_proj(x).view(B, T, 3, H, D)
+        if coords is not None:
+            if coord_high is None:
+                raise ValueError("coords need coord_high (the coordinate that maps to one radian per unit frequency)")
+            rope_qk_(qkv, coords, coord_high, num_cls, rope_theta)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
         q_idx, k_idx = self.indexer_proj(x)
         o = dsa_sparse_attention(q, k, v, q_idx, k_idx, self.indexer_head_weights, self.top_k, out_dtype=x.dtype)
@@ -85,8 +113,8 @@ class DSAViTBlock(nn.Module):
         self.mlp = nn.Sequential(nn.Linear(embed_dim, hidden), nn.GELU(), nn.Dropout(proj_dropout),
                                  nn.Linear(hidden, embed_dim), nn.Dropout(proj_dropout))
 
-    def forward(self, x: Tensor) -> Tensor:
-        x = x + self.drop1(self.attn(self.norm1(x)))
+    def forward(self, x: Tensor, coords=None, coord_high=None, num_cls: int = 0, rope_theta: float = 10000.0) -> Tensor:
+        x = x + self.drop1(self.attn(self.norm1(x), coords, coord_high, num_cls, rope_theta))
         return x + self.mlp(self.norm2(x))
 
 
@@ -99,12 +127,16 @@ class DSAViTSlideEncoder(nn.Module):
                  num_layers: int = 6, num_cls: int = 2, indexer_heads: int = 4, indexer_dim: int = 32,
                  top_k: int = 512, block_q: int = 16, block_k: int = 32, block_d: int = 32,
                  expansion_factor: float = 4.0, attn_dropout: float = 0.0, proj_dropout: float = 0.0,
-                 gradient_checkpointing: bool = False) -> None:
+                 gradient_checkpointing: bool = False, rope_coord_high=None, rope_theta: float = 10000.0) -> None:
         super().__init__()
         if embed_dim % num_heads != 0:
             raise ValueError(f"embed_dim ({embed_dim}) must be divisible by num_heads ({num_heads}). "
                              f"Recommended: embed_dim // num_heads == 64 or 128.")
         self.gradient_checkpointing = gradient_checkpointing
+        # Not in the reference's encoder: with a coordinate scale set, forward(x, coords) applies the
+        # 2-D rotary embedding to q and k of the patch tokens in every layer.
+        self.rope_coord_high = rope_coord_high
+        self.rope_theta = rope_theta
         self.num_cls = num_cls
         self.embed_dim = embed_dim
         self.out_features = out_features
@@ -122,13 +154,17 @@ class DSAViTSlideEncoder(nn.Module):
         nn.init.zeros_(self.input_proj.bias)
         nn.init.zeros_(self.head.bias)
 
-    def forward(self, x: Tensor) -> dict[str, Tensor]:
+    def forward(self, x: Tensor, coords=None) -> dict[str, Tensor]:
+        """``x (B, N, in_features)`` or ``(N, in_features)``; ``coords`` (optional, (B, N, 2) or (N, 2))
+        are used only when the encoder was built with ``rope_coord_high`` (the reference's wrapper
+        calls ``network(inputs, coords)``, experiments/lightning_wrappers/wsi_attn_wrapper.py:96)."""
         if x.dim() == 2:
             x = x.unsqueeze(0)
         x = self.input_proj(x)
         x = torch.cat([self.cls_tokens.expand(x.shape[0], -1, -1).to(x.dtype), x], dim=1)
+        rope = coords is not None and self.rope_coord_high is not None
         for blk in self.blocks:
-            x = blk(x)
+            x = blk(x, coords, self.rope_coord_high, self.num_cls, self.rope_theta) if rope else blk(x)
         x = self.norm(x)
         cls = x[:, :self.num_cls]
         pooled = (torch.softmax(self.cls_pool(cls), dim=1) * cls).sum(dim=1)
