@@ -39,12 +39,20 @@ METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 # key-norm maximum, attention
 KERNELS_PER_STEP = 12
 
-# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, measured with ncu
-# (dram__bytes_read.sum + dram__bytes_write.sum, one pass): 5.26 GB + 0.07 GB on the 65536-token workload
-# (profiles/dsa_attn_masked_kernel_64k_dram.md) -- K, V of all heads and the indexer keys, 144 MiB, do
-# not fit the 126 MB L2, so key tiles are re-fetched; 59.5 MB + 5.0 MB at 16384 tokens, where they fit
-# (profiles/dsa_attn_masked_kernel_16k.md).
+# DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, from one-pass ncu captures
+# (dram__bytes_read.sum + dram__bytes_write.sum): 5.26 GB + 0.07 GB on the 65536-token workload -- K, V
+# of all heads and the indexer keys, 144 MiB, do not fit the 126 MB L2, so key tiles are re-fetched;
+# 59.5 MB + 5.0 MB at 16384 tokens, where they fit.  A profiler figure cannot be taken inside a timed
+# run, so the JSON line carries it with `traffic_source` saying so.
 ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 5.327e9, 16384: 64.5e6}
+
+
+def workload_config(T, world):
+    """The `config` object of the JSON line; both arms print exactly this."""
+    return {"workload": f"dsa_fwd_{T // 1024}k", "tokens": T, "heads": H, "head_dim": D,
+            "indexer": f"{IH}x{ID} tf32", "top_k": TOP_K, "batch": 1,
+            "parallelism": f"sp{world}" if world > 1 else "single",
+            "l2": "inputs+outputs per step (>1.9 GiB) exceed the 126 MB L2"}
 
 
 def measured_peaks():
@@ -186,32 +194,75 @@ def cpu_baseline(T, budget_s=15.0, threads=None):
             "sample": f"{rows} of {T} query rows against all {T} keys, {H} heads, fp32, {t:.1f} s"}
 
 
+def triton_reference_baseline(src, T=1024, top_k=32):
+    """The reference's OWN kernels (LightningIndexerFunction + DSAAttentionFunction of
+    deepseek_sparse_attention_kernels/kernels.py) executed on CPU tensors by Triton's interpreter,
+    from a checkout whose `src` directory is given.  The interpreter needs about a minute per
+    forward at 1024 tokens and four times that per doubling, so this is a small-size figure beside
+    the full-size port, at the same selection density (top_k / T = 1/32) and head shapes."""
+    os.environ["TRITON_INTERPRET"] = "1"
+    sys.path.insert(0, src)
+    from sparse_wsi_vit.models.deepseek_sparse_attention_kernels import kernels as ref_kernels
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(1, H, T, D, generator=g) / D ** 0.5
+    k = torch.randn(1, H, T, D, generator=g)
+    v = torch.randn(1, H, T, D, generator=g)
+    qi = torch.randn(1, T, IH, ID, generator=g) / ID ** 0.5
+    ki = torch.randn(1, T, IH, ID, generator=g) / ID ** 0.5
+    w = torch.randn(IH, generator=g)
+    t0 = time.perf_counter()
+    idx, valid, scores = ref_kernels.LightningIndexerFunction.apply(qi, ki, w, 1, T, IH, ID, top_k, 64, 64, 64, IH)
+    o = torch.zeros(1, H, T, D)
+    ref_kernels.DSAAttentionFunction.apply(q, k, v, idx, valid, scores * valid, o, 1, H, T, D, top_k, 64, 64, H, 64)
+    dt = time.perf_counter() - t0
+    return {"value": T / dt, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "reference",
+            "sample": f"whole forward at {T} tokens, top-{top_k}, {H}x{D} heads, {IH}x{ID} indexer, fp32, Triton "
+                      f"interpreter on CPU tensors, {dt:.1f} s"}
+
+
 def run_reference(args):
     """`--impl reference`: the reference's forward arithmetic on the host cores.  The reference is
-    Python + Triton (no compiled CPU library to build), so its CPU port in oracle/ is what is timed."""
+    Python + Triton (no compiled CPU library to build), and its kernels only run on a CPU under
+    Triton's interpreter at toy sizes, so the full-size workload is timed with the CPU port in
+    oracle/ (pinned to the reference by the golden fixtures).  One step = one bounded sample of the
+    workload: `rows` query rows against all keys; `ms_per_step` is the time that sample took, the
+    extrapolation to all rows is a separate field.  With --reference-src (or SWV_REFERENCE_SRC)
+    pointing at the `src` directory of a checkout, the reference's own kernels are also timed, at
+    1024 tokens, and reported in `triton_interpreter`."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     T = args.tokens
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    per_step = []
-    base = None
+    per_step, per_step_s, base = [], [], None
     for i in range(args.warmup + args.steps):
-        base = cpu_baseline(T, budget_s=6.0 if i >= args.warmup else 2.0, threads=threads)
+        t0 = time.perf_counter()
+        base = cpu_baseline(T, budget_s=4.0 if i >= args.warmup else 1.0, threads=threads)
         if i >= args.warmup:
             per_step.append(base["value"])
+            per_step_s.append(time.perf_counter() - t0)
     value = statistics.mean(per_step)
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * T / value, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"dsa_fwd_{T // 1024}k", "tokens": T, "heads": H, "head_dim": D,
-                   "indexer": f"{IH}x{ID}", "top_k": TOP_K},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(per_step_s),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(T, world),
+        "step_is": "one bounded sample of the workload (see cpu_baseline.sample); value = sample rows / sample time",
+        "extrapolated_ms_full_workload": 1e3 * T / value,
         "cpu_baseline": {**base, "value": value},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    src = args.reference_src or os.environ.get("SWV_REFERENCE_SRC")
+    if src and os.path.isdir(src):
+        try:
+            line["triton_interpreter"] = triton_reference_baseline(src)
+        except Exception as e:                                   # a checkout that does not import here
+            line["triton_interpreter"] = {"skipped": f"{type(e).__name__}: {e}"[:200]}
+    else:
+        line["triton_interpreter"] = {"skipped": "no reference checkout given (--reference-src / SWV_REFERENCE_SRC)"}
     print(json.dumps(line), flush=True)
 
 
@@ -320,7 +371,9 @@ def run_ours(args):
     up_stream = torch.cuda.Stream(dev)
     dbuf2 = [torch.empty_like(t) for t in dbuf]
 
-    def e2e_pipeline(n):
+    idx_host = torch.empty((1, plan.local, TOP_K), dtype=torch.int32).pin_memory()
+
+    def e2e_pipeline(n, with_idx=False):
         sets = (dbuf, dbuf2)
         done = [None, None]                    # compute of the step that last read each buffer set
         outs = [None, None]                    # output of that step, kept until its download is ordered
@@ -353,17 +406,19 @@ def run_ours(args):
                 outs[slot] = None
             if world == 1:
                 cur.wait_event(ev_idx)
-                o, _ = step(*sets[slot], qkv_ready=ev_qkv)
+                o, ix = step(*sets[slot], qkv_ready=ev_qkv)
             else:
                 cur.wait_event(ev_qkv)
-                o, _ = step(*sets[slot])
+                o, ix = step(*sets[slot])
             done[slot] = cur.record_event()
             with torch.cuda.stream(copy_stream):
                 copy_stream.wait_event(done[slot])
                 o_host.copy_(o, non_blocking=True)
+                if with_idx:
+                    idx_host.copy_(ix, non_blocking=True)
                 dl_done[slot] = copy_stream.record_event()
-            outs[slot] = o
-            del o
+            outs[slot] = (o, ix) if with_idx else o
+            del o, ix
         cur.wait_stream(copy_stream)           # the last download belongs to the timed region
         cur.wait_stream(up_stream)
 
@@ -378,11 +433,20 @@ def run_ours(args):
     e1.record(cur)
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
+    # the same pipeline with the selected-key indices (the operator's second checked output) downloaded too
+    barrier()
+    e2 = torch.cuda.Event(enable_timing=True)
+    e3 = torch.cuda.Event(enable_timing=True)
+    e2.record(cur)
+    e2e_pipeline(args.steps, with_idx=True)
+    e3.record(cur)
+    barrier()
+    ms_e2e_idx = e2.elapsed_time(e3) / args.steps
 
     if world > 1:
-        tt = torch.tensor([ms, ms_e2e], device=dev, dtype=torch.float64)
+        tt = torch.tensor([ms, ms_e2e, ms_e2e_idx], device=dev, dtype=torch.float64)
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms, ms_e2e = float(tt[0]), float(tt[1])
+        ms, ms_e2e, ms_e2e_idx = float(tt[0]), float(tt[1]), float(tt[2])
 
     if rank == 0:
         tf_peak, hbm_peak, peak_src = measured_peaks()
@@ -390,17 +454,19 @@ def run_ours(args):
             "metric": METRIC, "value": T / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"dsa_fwd_{T // 1024}k", "tokens": T, "heads": H, "head_dim": D,
-                       "indexer": f"{IH}x{ID} tf32", "top_k": TOP_K, "batch": 1,
-                       "parallelism": f"sp{world}" if world > 1 else "single",
-                       "l2": "inputs+outputs per step (>1.9 GiB) exceed the 126 MB L2"},
+            "config": workload_config(T, world),
             # host time rank 0 spends issuing one step (no waiting): far below ms_per_step = not launch-bound
             "host_issue_ms_per_step": (_h1 - _h0) * 1e3 / args.steps,
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "ms_per_step": ms_e2e,
                     "host_issue_ms_per_step": (_h3 - _h2) * 1e3 / args.steps,
                     "mode": "double-buffered uploads/downloads overlapped with the neighbouring steps",
                     "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in pinned) * world,
-                    "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world},
+                    "d2h_bytes_per_step": o_host.numel() * o_host.element_size() * world,
+                    "outputs_downloaded": "the attention output o; idx / valid / scores stay on the device",
+                    "with_idx": {"value": T / (ms_e2e_idx * 1e-3), "ms_per_step": ms_e2e_idx,
+                                 "d2h_bytes_per_step": (o_host.numel() * o_host.element_size() +
+                                                        idx_host.numel() * 4) * world,
+                                 "outputs_downloaded": "o and the int32 index lists idx"}},
             "gpu_launches": args.steps * KERNELS_PER_STEP * world,
             "clocks": clocks,
         }
@@ -412,6 +478,8 @@ def run_ours(args):
             line["roofline"] = {
                 "kernel": "dsa_attn_masked_kernel", "bound": "tensor", "achieved": ach, "peak": tf_peak,
                 "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH.get(T),
+                "traffic_source": "one-pass ncu capture of this kernel on this workload, taken in a separate "
+                                  "run (a constant of bench.py, not measured by this run)",
                 "peak_source": f"bf16_tflops_sustained of {peak_src}",
                 "kernel_ms": attn_ms, "algorithmic_flops": kept,
                 "executed_flops": executed, "executed_tflops": executed / (attn_ms * 1e-3) / 1e12,
@@ -435,6 +503,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=None, help="sequence length (default 65536; with --workload "
                     "block_sparse / nsa: run only this size)")
+    ap.add_argument("--reference-src", default=None, help="with --impl reference: `src` directory of a "
+                    "sparse-wsi-vit checkout; its own Triton kernels are then timed too (interpreter, 1024 tokens)")
     ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "block_sparse", "nsa", "encoder", "static"])
     args = ap.parse_args()
     if args.workload != "dsa_fwd":

@@ -18,8 +18,12 @@
  *   - `status` points to one int32 in device memory, zeroed by the caller.
  *     Kernels write a positive code there when a bounded device-side wait gave
  *     up (see swv_strerror); the results of that call are then undefined.
- *   - Re-entrant; no global mutable state.  Calls sharing a workspace, a mask
- *     buffer or a status word must be ordered on the GPU by the caller.
+ *   - Re-entrant; no global mutable state -- with ONE exception,
+ *     swv_dsa_indexer_topk_static_fwd, whose scratch is a device array inside the
+ *     library (see its comment).  Calls sharing a workspace, a mask buffer or a
+ *     status word must be ordered on the GPU by the caller.
+ *     swv_dsa_attn_masked_fwd writes the per-(batch, head) key-norm maxima into the
+ *     indexer workspace it is given: two attention calls on one workspace must be ordered too.
  */
 #ifndef SWV_B200_H_
 #define SWV_B200_H_
@@ -97,8 +101,9 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
  * library's device data segment.
  * Same arguments, outputs and arithmetic as swv_dsa_indexer_topk_fwd (the same kernels run).
  * Limits and rules:
- *   - B*Tq <= 8192 and B*Tk <= 8192; anything larger returns SWV_ERR_TOO_LARGE and launches
- *     nothing.  The array (about 4.3 MB) is held by every GPU that loads the library, until
+ *   - B*Tq <= 8192 and B*Tk <= 8192 (any batch / length split of them); anything larger
+ *     returns SWV_ERR_TOO_LARGE and launches nothing.  The array (about 4.4 MB) is held by every GPU
+ *     that loads the library, until
  *     the process exits.
  *   - The first call on a device looks up the array's device address (with that device
  *     current); make that first call before any stream capture begins.
@@ -140,7 +145,8 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
  * the membership bitmask applied inside the online softmax and the routing
  * weights recomputed on the tensor cores from the collapsed indexer vectors
  * kept in the workspace (bit-identical to the emitted scores).
- * bf16 q/k/v only, D == 64; q,k,v,o rows 16-byte aligned, unit inner stride.
+ * bf16 q/k/v only, D == 64; q,k,v,o rows 16-byte aligned, unit inner stride; B*H <= 1024.
+ * `workspace` is read AND written (the key-norm maxima of this call live in it).
  * `scratch` (optional, may be NULL): swv_dsa_attn_scratch_bytes() bytes, 256-byte aligned.  With few
  * query tiles (one rank of a sequence-sharded run) the grid is only a few waves of CTAs; given the
  * scratch, 2 or 4 CTAs share a (query tile, head pair), each sweeping a share of the key tiles, and
@@ -149,7 +155,7 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
 int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes);
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
-                            const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
+                            void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream);
 
 /* Static block-sparse flash attention forward driven by a CSR list of key blocks per

@@ -18,5 +18,5 @@ Parity status per part:
   * Static (1-D window) sparse attention, 2-D RoPE: pinned by golden fixtures
     generated from the reference's own modules.
   * 2-D block-sparse attention and NSA: the reference contains no such code;
-    those oracles are builder-defined ("parity unpinned").
+    those oracles are library-defined ("parity unpinned").
 """

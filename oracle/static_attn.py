@@ -1,5 +1,5 @@
 """CPU restatements of the reference's static sparse attention and 2-D RoPE,
-and the builder-defined oracle for 2-D block-sparse attention.
+and the library-defined oracle for 2-D block-sparse attention.
 
 TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).
 
@@ -64,8 +64,18 @@ def static_sparse_attention(x, sd, num_heads, num_cls, window, dilation, dtype=t
     return torch.nn.functional.linear(o, sd["out_proj.weight"].to(dtype), sd["out_proj.bias"].to(dtype))
 
 
-def expand_block_mask(row_ptr, col_idx, block: int, Tq: int, Tk: int) -> torch.Tensor:
-    """CSR list of key blocks per query block -> (Tq, Tk) boolean keep-mask."""
+def expand_block_mask(row_ptr, col_idx, block: int, Tq: int, Tk: int, rows=None) -> torch.Tensor:
+    """CSR list of key blocks per query block -> (Tq, Tk) boolean keep-mask; with `rows` (1-D
+    tensor of query indices) only those rows, (len(rows), Tk), so that long sequences can be
+    checked on a sample of rows."""
+    if rows is not None:
+        mask = torch.zeros((len(rows), Tk), dtype=torch.bool)
+        for i, r in enumerate(rows.tolist()):
+            qb = r // block
+            for j in range(int(row_ptr[qb]), int(row_ptr[qb + 1])):
+                kb = int(col_idx[j])
+                mask[i, kb * block:min(Tk, (kb + 1) * block)] = True
+        return mask
     mask = torch.zeros((Tq, Tk), dtype=torch.bool)
     nqb = len(row_ptr) - 1
     for qb in range(nqb):

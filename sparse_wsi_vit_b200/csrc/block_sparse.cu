@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(320, 1)
       for (int j = 0; j < nblk; ++j) {
         const int s = j & 1;
         const uint32_t par = ((j >> 1) & 1) ^ 1;
-        const int key0 = p.col_idx[list0 + j] * BS;
+        const int key0 = checked_index(p.col_idx[list0 + j], (p.Tk + BS - 1) / BS, p.status) * BS;
         if (!mbar_wait_bounded(&ctl->k_empty[s], par, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
           break;
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(320, 1)
     float m_used = ninf, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nblk; ++j) {
-      const int key0 = p.col_idx[list0 + j] * BS;
+      const int key0 = checked_index(p.col_idx[list0 + j], (p.Tk + BS - 1) / BS, p.status) * BS;
       const int sb = j & 1;
       const uint32_t s_col = lane_base + sb * BS + half * HC;
       const uint32_t p_col = lane_base + Cfg::kColP + sb * (BS / 2) + half * (HC / 2);

@@ -15,7 +15,7 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
                                  int32_t* idx, float* valid, float* scores, uint32_t* maskbits, int* status,
                                  cudaStream_t st);
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
-                         const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
+                         const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
                          size_t scratch_bytes, int* status, cudaStream_t st);
 int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes);
@@ -122,7 +122,7 @@ int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes) {
 
 int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
                             const void* v, const int64_t v_strides[4], const uint32_t* maskbits,
-                            const void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
+                            void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream) {
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, scratch, scratch_bytes, status,

@@ -38,6 +38,21 @@ __device__ __forceinline__ void record_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// Bounds check of an index taken from a caller-supplied list.  In the checked build (-DSWV_CHECKS,
+// `build.py --checks`, which writes libswv_b200_checked.so) an index outside [0, n) is reported
+// through the status word as kDevBadIndex and replaced by 0, so nothing is accessed through it;
+// the release build trusts the list.  This build is the stand-in for a memory checker on machines
+// where none may be run.
+__device__ __forceinline__ int checked_index(int i, int n, int* status) {
+#ifdef SWV_CHECKS
+  if (i < 0 || i >= n) {
+    record_status(status, kDevBadIndex);
+    return 0;
+  }
+#endif
+  return i;
+}
+
 // Bounded mbarrier wait.  Gives up after kWaitLimitNs or as soon as another
 // thread of the CTA raised `abort_flag`; on its own timeout raises the flag.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag) {

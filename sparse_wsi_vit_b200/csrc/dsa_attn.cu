@@ -835,7 +835,7 @@ int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes) {
 }
 
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
-                         const int64_t* vs, const uint32_t* maskbits, const void* workspace, void* o,
+                         const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
                          size_t scratch_bytes, int* status, cudaStream_t st) {
   if (!q || !k || !v || !maskbits || !workspace || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
@@ -856,7 +856,7 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
 
   float *wq = nullptr, *wk = nullptr;
   uint32_t *st_prefix = nullptr, *st_kth = nullptr, *st_neq = nullptr, *kmax2 = nullptr;
-  dsa_workspace_views(const_cast<void*>(workspace), B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq, &kmax2);
+  dsa_workspace_views(workspace, B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq, &kmax2);
   if (static_cast<int64_t>(B) * H > 1024) return SWV_ERR_UNSUPPORTED;
 
   CUtensorMap tm_wq, tm_wk, tm_q, tm_k, tm_v;

@@ -29,6 +29,7 @@ struct GatherParams {
   int B, H, Tq, Tk, D, top_k;
   int kv_group;   // query heads per key/value head
   float scale;
+  int* status;    // receives kDevBadIndex when a valid slot names a key outside [0, Tk)
 };
 
 template <typename T>
@@ -87,6 +88,13 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
       id = idx_row[slot * p.is[2]];
       ok = val_row[slot * p.vls[2]] > 0.f;
       w = rw_row[slot * p.rs[2]];
+    }
+    if (ok && (id < 0 || id >= p.Tk)) {
+      // a valid slot that names no key: reported through the status word, the slot is dropped
+      // (nothing is read through it)
+      record_status(p.status, kDevBadIndex);
+      ok = false;
+      w = 0.f;
     }
     id = min(max(id, 0), p.Tk - 1);
     float logit = ninf;
@@ -163,6 +171,7 @@ int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const 
   for (int i = 0; i < 3; ++i) { p.is[i] = is[i]; p.vls[i] = vls[i]; p.rs[i] = rs[i]; }
   p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k; p.kv_group = kv_group;
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
+  p.status = status;
   if (dtype == SWV_F32) return launch_gather<float>(p, D, st);
   if (dtype == SWV_BF16) return launch_gather<__nv_bfloat16>(p, D, st);
   return launch_gather<__half>(p, D, st);

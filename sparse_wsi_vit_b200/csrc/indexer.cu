@@ -19,6 +19,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
 #include <type_traits>
 
 #include "common.cuh"
@@ -764,6 +765,7 @@ __global__ void __launch_bounds__(576, 1)
           const int i = __ffs(mine) - 1;
           mine &= mine - 1u;
           if (row_ok && off < p.top_k) {
+            (void)checked_index(key0 + i, p.Tk, p.status);
             const uint32_t v = relu_bits(lds32(stage + static_cast<uint32_t>((i >> 2) * 32 * 16 + (i & 3) * 4)));
             if (ring_ok) {
               sts32(ring_i + ((off & (kRing - 1)) << 2), static_cast<uint32_t>(key0 + i));
@@ -1036,7 +1038,8 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
 constexpr int kStaticMaxTokens = 8192;
 constexpr size_t kStaticScratchBytes =
     2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + 3 * static_cast<size_t>(kStaticMaxTokens) * 4 + 4096 +
-    2 * 1024 /* tile flags */ + 8 * 1024 /* per-section rounding */;
+    2 * 32 * 1024 /* tile flags: up to 8192 query tiles (a batch of one-token sequences) */ +
+    8 * 1024 /* per-section rounding */;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks,
@@ -1049,18 +1052,20 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
   if (workspace_layout(B, Tq, Tk).flags3_off > kStaticScratchBytes) return SWV_ERR_TOO_LARGE;
   // In host code `g_static_scratch` names a host-side stand-in, not device memory: the device
   // address has to be asked for, once per device, with that device current.
+  // The address is cached per device in an atomic slot: host threads that make their first calls
+  // at the same time each look it up and store the same value.
   constexpr int kMaxDevices = 64;
-  static void* dev_ptr[kMaxDevices] = {nullptr};
+  static std::atomic<void*> dev_ptr[kMaxDevices];
   int dev = 0;
   SWV_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return SWV_ERR_UNSUPPORTED;
-  if (dev_ptr[dev] == nullptr) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || ptr == nullptr) return SWV_ERR_CUDA;
-    dev_ptr[dev] = ptr;
+  void* scratch = dev_ptr[dev].load(std::memory_order_acquire);
+  if (scratch == nullptr) {
+    if (cudaGetSymbolAddress(&scratch, g_static_scratch) != cudaSuccess || scratch == nullptr) return SWV_ERR_CUDA;
+    dev_ptr[dev].store(scratch, std::memory_order_release);
   }
   return dsa_indexer_topk_impl(q_idx, qs, k_idx, ks, dtype, w, B, Tq, Tk, IH, ID, top_k, idx, valid, scores, maskbits,
-                               dev_ptr[dev], kStaticScratchBytes, status, st, /*allow_split=*/false);
+                               scratch, kStaticScratchBytes, status, st, /*allow_split=*/false);
 }
 
 }  // namespace swv

@@ -1,6 +1,6 @@
 """NSA-style attention forward (compressed, selected and sliding-window branches with a sigmoid
 gate) assembled from this library's CUDA kernels.  The reference has no NSA code; the semantics
-are the builder-defined ones frozen in ``oracle/nsa.py`` (parity unpinned).
+are the library-defined ones frozen in ``oracle/nsa.py`` (parity unpinned).
 
   compressed : `swv_pool_tokens` (mean pooling) + the block-sparse tensor-core kernel over ALL
                compressed tokens, grouped-query (kv_group), returning the log-sum-exp per row;

@@ -37,10 +37,11 @@ def _check_vs_oracle(swv, q, k, v, rp, ci, block, rows=None, **kw):
     swv.check_status(DEV)
     if kw.get("mode", 0) == 1:
         mask = S.static_window_mask(q.shape[2], kw["num_cls"], kw["window"], kw["dilation"])
+        mask = mask if rows is None else mask[rows]
     else:
-        mask = S.expand_block_mask(rp, ci, block, q.shape[2], k.shape[2])
+        mask = S.expand_block_mask(rp, ci, block, q.shape[2], k.shape[2], rows=rows)
     r = slice(None) if rows is None else rows
-    ref = S.masked_attention(q[0, :, r].float(), k[0].float(), v[0].float(), mask[r])
+    ref = S.masked_attention(q[0, :, r].float(), k[0].float(), v[0].float(), mask)
     diff = (o[0, :, r].cpu() - ref).abs()
     assert torch.isfinite(o).all()
     assert diff.max() < 2e-2 and diff.mean() < 1e-3, (float(diff.max()), float(diff.mean()))
@@ -147,4 +148,17 @@ def test_sweep_configuration_sampled_blocks(swv):
     rp, ci = swv.patterns.band_random_blocks(T // block, band=2, n_global=1, p=0.05, seed=7)
     q, k, v = _qkv(T, H, D, seed=21)
     rows = torch.cat([torch.arange(0, 256), torch.arange(4000, 4200), torch.arange(T - 128, T)])
+    _check_vs_oracle(swv, q, k, v, rp, ci, block, rows=rows)
+
+
+@pytest.mark.parametrize("T,p", [(32768, 0.25), (131072, 0.05)])
+def test_sweep_sizes_sampled_rows(swv, T, p):
+    """The block-sparse sweep at the sizes that are timed (band +-2, one global block, Bernoulli(p)
+    extras, head_dim 128, block 128): full GPU run, oracle on sampled query rows (the first and
+    last blocks and random rows) against exactly the key blocks their row lists name."""
+    H, D, block = 2, 128, 128
+    rp, ci = swv.patterns.band_random_blocks(T // block, band=2, n_global=1, p=p, seed=9)
+    q, k, v = _qkv(T, H, D, seed=31)
+    g = torch.Generator().manual_seed(T)
+    rows = torch.cat([torch.arange(0, 64), torch.randperm(T, generator=g)[:128].sort().values, torch.arange(T - 64, T)])
     _check_vs_oracle(swv, q, k, v, rp, ci, block, rows=rows)

@@ -213,10 +213,12 @@ def test_module_matches_reference_fixture(swv, golden_dir):
     _check(swv)
 
 
-def test_benchmark_config_sampled_rows(swv):
-    """N=16384, 8 heads x 64, 4x64 indexer, top-2048, bf16 (the single-layer DSA configuration):
-    full GPU run, oracle on 192 sampled query rows; own-score bit-exactness on the same rows."""
-    T, H, K = 16384, 8, 2048
+@pytest.mark.parametrize("T", [16384, 65536])
+def test_benchmark_config_sampled_rows(swv, T):
+    """8 heads x 64, 4x64 indexer, top-2048, bf16 at 16384 tokens (the single-layer DSA
+    configuration) and at 65536 tokens (the workload the benchmark times): full GPU run, oracle on
+    192 sampled query rows; own-score bit-exactness on the same rows."""
+    H, K = 8, 2048
     rows = torch.randperm(T, generator=torch.Generator().manual_seed(0))[:192].sort().values
     diff, o, idx, valid, scores, (q, k, v, qi, ki, w) = _masked_vs_oracle(swv, T, H, K, seed=1234, rows=rows)
     assert diff.max() < 2e-2 and diff.mean() < 1e-3, (float(diff.max()), float(diff.mean()))
