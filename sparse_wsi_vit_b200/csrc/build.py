@@ -1,10 +1,11 @@
 """Builds libswv_b200.so (sm_100a only) in-tree with nvcc.
 
-    python sparse_wsi_vit_b200/csrc/build.py [--force] [--verbose] [--checks]
+    python sparse_wsi_vit_b200/csrc/build.py [--force] [--verbose] [--checks] [--profile]
 
 --checks builds libswv_b200_checked.so with -DSWV_CHECKS (indices read from caller-supplied lists
 are range-checked on the device and reported through the status word); run the tests against it
-with SWV_B200_LIB=<that file>.
+with SWV_B200_LIB=<that file>.  --profile builds libswv_b200_prof.so with -DSWV_PROFILE (phase
+timers inside dsa_attn_masked_kernel, read with swv_debug_attn_profile).
 
 (run it by path: importing it through the package would first try to load the library)
 
@@ -33,16 +34,20 @@ def _stale() -> bool:
     return any(os.path.getmtime(os.path.join(HERE, f)) > t for f in SOURCES + HEADERS + ["build.py"])
 
 
-def build(force: bool = False, verbose: bool = False, checks: bool = False) -> str:
-    lib = LIB.replace(".so", "_checked.so") if checks else LIB
-    if not checks and not force and not _stale():
+def build(force: bool = False, verbose: bool = False, checks: bool = False, defines=(), suffix: str = "") -> str:
+    """`checks`: the range-checked library; `defines` + `suffix`: any other variant, e.g. the phase-timer
+    build `build(defines=["SWV_PROFILE"], suffix="_prof")` -> libswv_b200_prof.so."""
+    if checks:
+        defines, suffix = [*defines, "SWV_CHECKS"], suffix + "_checked"
+    lib = LIB.replace(".so", suffix + ".so")
+    if not suffix and not force and not _stale():
         return LIB
     nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
     objs = []
     procs = []
     for src in SOURCES:
-        obj = os.path.join(HERE, src.replace(".cu", "_checked.o" if checks else ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, *(["-DSWV_CHECKS"] if checks else []), "-c", os.path.join(HERE, src), "-o", obj]
+        obj = os.path.join(HERE, src.replace(".cu", suffix + ".o"))
+        cmd = [nvcc, *NVCC_FLAGS, *[f"-D{d}" for d in defines], "-c", os.path.join(HERE, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -58,4 +63,7 @@ def build(force: bool = False, verbose: bool = False, checks: bool = False) -> s
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, checks="--checks" in sys.argv))
+    if "--profile" in sys.argv:
+        print(build(defines=["SWV_PROFILE"], suffix="_prof", verbose="--verbose" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, checks="--checks" in sys.argv))

@@ -124,6 +124,38 @@ struct ProgressClock {
   }
 };
 
+// Phase timers of the profiling build (-DSWV_PROFILE, `build.py --profile`, a library of its own):
+// lane 0 of every role adds the cycles it spent per phase to a table in device memory that
+// swv_debug_attn_profile() reads.  In the regular build every member is an empty inline function.
+#ifdef SWV_PROFILE
+__device__ unsigned long long g_attn_prof[64];
+struct Prof {
+  long long last;
+  unsigned long long acc[8];
+  __device__ __forceinline__ void start() {
+    last = clock64();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0;
+  }
+  __device__ __forceinline__ void tick(int k) {
+    const long long t = clock64();
+    acc[k] += static_cast<unsigned long long>(t - last);
+    last = t;
+  }
+  __device__ __forceinline__ void flush(int base, bool on) {
+    if (!on) return;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) atomicAdd(&g_attn_prof[base + i], acc[i]);
+  }
+};
+#else
+struct Prof {
+  __device__ __forceinline__ void start() {}
+  __device__ __forceinline__ void tick(int) {}
+  __device__ __forceinline__ void flush(int, bool) {}
+};
+#endif
+
 // ------------------------------------------------------------ softmax helpers
 // r >= thr ? r : 0 on the FMA pipe (compare and select run at half rate on the ALU pipe, which
 // bounds the weight conversion).  With t = the float just below thr, r >= thr <=> r - t > 0, and
@@ -158,11 +190,13 @@ struct SoftmaxRow {
 // released as soon as it has been read.
 __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, int j, int lane, float neg_c,
                                                 uint32_t (&w)[kSliceCols / 2], int* status,
-                                                volatile uint32_t* abort_flag) {
+                                                volatile uint32_t* abort_flag, Prof& prof) {
+  prof.tick(7);
   if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
     record_status(status, kDevWaitAccFull);
     return false;
   }
+  prof.tick(0);
   tc_fence_after();
   uint32_t ra[16], rb[16];
   tmem_ld16(r_col, ra);
@@ -183,6 +217,7 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(&ctl->r_free);
+  prof.tick(1);
   return true;
 }
 
@@ -190,11 +225,13 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
 // pairs over the first 32 of those columns, always behind this thread's own reads.
 __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x, int j, int lane, float sc,
                                              float neg_b, const uint32_t (&wpk)[kSliceCols / 2], float& l0, float& l1,
-                                             int* status, volatile uint32_t* abort_flag) {
+                                             int* status, volatile uint32_t* abort_flag, Prof& prof) {
+  prof.tick(7);
   if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
     record_status(status, kDevWaitAccFull);
     return false;
   }
+  prof.tick(2 + 2 * x);
   tc_fence_after();
   uint32_t sa[16], sb[16];
   tmem_ld16(s_col, sa);
@@ -223,6 +260,7 @@ __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+  prof.tick(3 + 2 * x);
   return true;
 }
 
@@ -234,6 +272,8 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
                                                     int lane, float thr, float sc, const float (&bound)[2],
                                                     float (&l_out)[2], int* status,
                                                     volatile uint32_t* abort_flag) {
+  Prof prof;
+  prof.start();
   const uint32_t r_col = lane_base + kColR + slice * kSliceCols;
   const uint32_t s_col0 = lane_base + kColS + slice * kSliceCols;   // this slice's score columns of head 0
   // -(float just below the threshold) * 2^60; a +inf threshold (tail rows) gives -inf: nothing selected
@@ -241,13 +281,13 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   const bool skew = (slice & 1) != 0;
   uint32_t wa[kSliceCols / 2], wb[kSliceCols / 2];
-  if (skew && !convert_weights(ctl, r_col, 0, lane, neg_c, wa, status, abort_flag)) return false;
+  if (skew && !convert_weights(ctl, r_col, 0, lane, neg_c, wa, status, abort_flag, prof)) return false;
   for (int j = 0; j < nKT; ++j) {
-    if (!skew && !convert_weights(ctl, r_col, j, lane, neg_c, wa, status, abort_flag)) return false;
-    if (!softmax_pass(ctl, s_col0, 0, j, lane, sc, -bound[0], wa, l[0][0], l[0][1], status, abort_flag)) return false;
-    if (skew && j + 1 < nKT && !convert_weights(ctl, r_col, j + 1, lane, neg_c, wb, status, abort_flag)) return false;
+    if (!skew && !convert_weights(ctl, r_col, j, lane, neg_c, wa, status, abort_flag, prof)) return false;
+    if (!softmax_pass(ctl, s_col0, 0, j, lane, sc, -bound[0], wa, l[0][0], l[0][1], status, abort_flag, prof)) return false;
+    if (skew && j + 1 < nKT && !convert_weights(ctl, r_col, j + 1, lane, neg_c, wb, status, abort_flag, prof)) return false;
     if (nh == 2 &&
-        !softmax_pass(ctl, s_col0 + kTile, 1, j, lane, sc, -bound[1], wa, l[1][0], l[1][1], status, abort_flag))
+        !softmax_pass(ctl, s_col0 + kTile, 1, j, lane, sc, -bound[1], wa, l[1][0], l[1][1], status, abort_flag, prof))
       return false;
     if (skew) {
 #pragma unroll
@@ -256,6 +296,7 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   }
   l_out[0] = l[0][0] + l[0][1];
   l_out[1] = l[1][0] + l[1][1];
+  prof.flush(skew ? 8 : 0, lane == 0);
   return true;
 }
 
@@ -513,11 +554,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const uint32_t wk_addr = smem_u32(smem + kOffWk);
       bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
       if (!ok) record_status(p.status, kDevWaitQ);
+      Prof prof;
+      prof.start();
       for (int j = 0; ok && j < nKT; ++j) {
         const int s = j & 1;
         // needs the indexer key tile and every softmax warp done with R(j-1)
-        if (!mbar_wait_bounded(&ctl->wk_full[s], (j >> 1) & 1, abort_flag) ||
-            (j > 0 && !mbar_wait_bounded(&ctl->r_free, (j - 1) & 1, abort_flag))) {
+        bool got = mbar_wait_bounded(&ctl->wk_full[s], (j >> 1) & 1, abort_flag);
+        prof.tick(0);
+        got = got && (j == 0 || mbar_wait_bounded(&ctl->r_free, (j - 1) & 1, abort_flag));
+        prof.tick(1);
+        if (!got) {
           record_status(p.status, kDevWaitTmaFull);
           break;
         }
@@ -531,7 +577,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         }
         umma_commit(&ctl->wk_empty[s]);
         umma_commit(&ctl->r_full);
+        prof.tick(2);
       }
+      prof.flush(16, true);
     }
   } else if (warp >= 2 + kSoftWarps) {
     // ------------------------------------- MMA issuer of one head: S_x(j) and O_x += P_x(j) V_x(j)
@@ -545,14 +593,19 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       const uint64_t dq = smem_desc_sw128(q_addr), dv = smem_desc_sw128(v_addr);
       bool ok = mbar_wait_bounded(&ctl->q_full, 0, abort_flag);
       if (!ok) record_status(p.status, kDevWaitQ);
+      Prof prof;
+      prof.start();
       // S_x(j) overwrites P_x(j-1), so it is issued behind PV_x(j-1): the tensor pipe executes
       // one thread's MMAs in issue order.
       for (int j = 0; ok && j <= nKT; ++j) {
         if (j > 0) {
           // PV_x(j-1): needs P_x(j-1) in TMEM and V_x(j-1) in smem
           const int jp = j - 1;
-          if (!mbar_wait_bounded(&ctl->p_full[x], jp & 1, abort_flag) ||
-              !mbar_wait_bounded(&ctl->v_full[x], jp & 1, abort_flag)) {
+          bool got = mbar_wait_bounded(&ctl->p_full[x], jp & 1, abort_flag);
+          prof.tick(0);
+          got = got && mbar_wait_bounded(&ctl->v_full[x], jp & 1, abort_flag);
+          prof.tick(1);
+          if (!got) {
             record_status(p.status, kDevWaitPReady);
             break;
           }
@@ -562,10 +615,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
             umma_f16_ts(o_col, s_col + p_col_of_key(ks * 16), dv + ks * 128, kIdescPV, (jp > 0 || ks > 0));
           umma_commit(&ctl->v_empty[x]);
           umma_commit(&ctl->pv_done[x]);
+          prof.tick(2);
         }
         if (j < nKT) {
           const int s = j & 1;
-          if (!mbar_wait_bounded(&ctl->k_full[x][s], (j >> 1) & 1, abort_flag)) {
+          const bool got = mbar_wait_bounded(&ctl->k_full[x][s], (j >> 1) & 1, abort_flag);
+          prof.tick(3);
+          if (!got) {
             record_status(p.status, kDevWaitTmaFull);
             break;
           }
@@ -575,8 +631,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
           for (int ks = 0; ks < 4; ++ks) umma_f16_ss(s_col, dq + ks * 2, dk + ks * 2, kIdescQK, ks > 0);
           umma_commit(&ctl->k_empty[x][s]);
           umma_commit(&ctl->s_full[x]);
+          prof.tick(4);
         }
       }
+      prof.flush(24 + 8 * x, true);
+#ifdef SWV_PROFILE
+      if (x == 0) atomicAdd(&g_attn_prof[63], static_cast<unsigned long long>(nKT));
+#endif
     }
   } else {
     // ----------------------------------------------------------------- softmax
@@ -925,3 +986,19 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
 }
 
 }  // namespace swv
+
+#ifdef SWV_PROFILE
+// Profiling build only: copies the 64 phase counters of dsa_attn_masked_kernel to `out_host`
+// (synchronises the device) and clears them when `reset` is non-zero.
+extern "C" int swv_debug_attn_profile(unsigned long long* out_host, int reset) {
+  if (cudaDeviceSynchronize() != cudaSuccess) return SWV_ERR_CUDA;
+  if (out_host != nullptr &&
+      cudaMemcpyFromSymbol(out_host, swv::g_attn_prof, sizeof(unsigned long long) * 64) != cudaSuccess)
+    return SWV_ERR_CUDA;
+  if (reset) {
+    static const unsigned long long zeros[64] = {0};
+    if (cudaMemcpyToSymbol(swv::g_attn_prof, zeros, sizeof(zeros)) != cudaSuccess) return SWV_ERR_CUDA;
+  }
+  return SWV_OK;
+}
+#endif
