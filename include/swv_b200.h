@@ -158,6 +158,19 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream);
 
+/* Diagnostic twin of swv_dsa_attn_masked_fwd (no counterpart in the reference): the same kernel,
+ * never split over the key range, that also writes `member_count` (B, Tq) int32 = the number of
+ * keys every query row treated as selected while it swept the key tiles (rows on the one-pass
+ * path: keys whose recomputed score >= the row threshold; rows on the two-pass path: bits set in
+ * the membership mask).  It must equal min(top_k, Tk) on every row: that is the bit-level check
+ * that the score tile recomputed inside the attention kernel equals the scores the indexer
+ * selected on.  Output `o` as swv_dsa_attn_masked_fwd.
+ */
+int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                                  const void* v, const int64_t v_strides[4], const uint32_t* maskbits, void* workspace,
+                                  void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
+                                  int32_t* member_count, int* status, void* stream);
+
 /* Static block-sparse flash attention forward driven by a CSR list of key blocks per
  * query block (shared by all batches and heads):
  *   o[q] = softmax_j( q.k_j / sqrt(D) ) v_j   over the keys j the pattern lets q see;

@@ -17,7 +17,7 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
-                         size_t scratch_bytes, int* status, cudaStream_t st);
+                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count);
 int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes);
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
@@ -126,7 +126,17 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream) {
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, scratch, scratch_bytes, status,
-                                   static_cast<cudaStream_t>(stream));
+                                   static_cast<cudaStream_t>(stream), nullptr);
+}
+
+int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                                  const void* v, const int64_t v_strides[4], const uint32_t* maskbits, void* workspace,
+                                  void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
+                                  int32_t* member_count, int* status, void* stream) {
+  if (member_count == nullptr) return SWV_ERR_NULL;
+  return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
+                                   o_dtype, B, H, Tq, Tk, D, nullptr, 0, status, static_cast<cudaStream_t>(stream),
+                                   member_count);
 }
 
 int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],

@@ -85,6 +85,9 @@ struct AttnParams {
   int split;
   float* scratch;        // [CTAs][split][2 heads][128 rows][kPartRec floats]
   uint32_t* tickets;     // [CTAs]
+  // Diagnostic instantiation only: [B*Tq] number of keys each query row treated as selected (summed
+  // over the column slices; counted once, by head pair 0).
+  int* member_count;
 };
 constexpr int kPartRec = kHeadDim + 4;                // output row + (l, m_used, m_true, pad)
 
@@ -102,27 +105,6 @@ struct AttnCtl {
 };
 
 constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
-
-// For the polling threads: gives up (and raises the CTA's abort flag) after kWaitLimitNs
-// without progress.  The clock is read only every 1024 idle polls.
-struct ProgressClock {
-  uint64_t t0;
-  uint32_t idle;
-  __device__ void reset() { idle = 0; }
-  __device__ bool expired(volatile uint32_t* abort_flag) {
-    if ((++idle & 1023u) != 0u) return false;
-    if (*abort_flag != 0u) return true;
-    if (idle == 1024u) {
-      t0 = globaltimer_ns();
-      return false;
-    }
-    if (globaltimer_ns() - t0 > kWaitLimitNs) {
-      *abort_flag = 1u;
-      return true;
-    }
-    return false;
-  }
-};
 
 // Phase timers of the profiling build (-DSWV_PROFILE, `build.py --profile`, a library of its own):
 // lane 0 of every role adds the cycles it spent per phase to a table in device memory that
@@ -157,15 +139,24 @@ struct Prof {
 #endif
 
 // ------------------------------------------------------------ softmax helpers
-// r >= thr ? r : 0 on the FMA pipe (compare and select run at half rate on the ALU pipe, which
-// bounds the weight conversion).  With t = the float just below thr, r >= thr <=> r - t > 0, and
+// Membership and weight on the FMA pipe (compare and select run at half rate on the ALU pipe, which
+// would bound the weight conversion).  With t = the float just below thr, r >= thr <=> r - t > 0, and
 // the smallest positive r - t (one ulp of a threshold >= 4e-6) times 2^60 is far above 1:
 //   step = saturate(r * 2^60 - t * 2^60)  is exactly 0 or 1;   weight = r * step.
 // `neg_c` = -t * 2^60 (-inf for rows that select nothing).
-__device__ __forceinline__ float keep_where_ge(float r, float neg_c) {
-  float step;
-  asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(step) : "f"(r), "f"(neg_c));   // 0x5D800000 = 2^60
-  return r * step;
+// (s0, s1) * sc + neg_b as one packed fp32x2 instruction
+__device__ __forceinline__ void scale_shift2(float s0, float s1, float sc, float neg_b, float& x0, float& x1) {
+  asm("{\n\t.reg .b64 a, b, c, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmov.b64 c, {%5, %5};\n\t"
+      "fma.rn.f32x2 d, a, b, c;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(x0), "=f"(x1)
+      : "f"(s0), "f"(s1), "f"(sc), "f"(neg_b));
+}
+// (a0 * b0, a1 * b1) as one packed fp32x2 instruction
+__device__ __forceinline__ void mul2(float a0, float a1, float b0, float b1, float& x0, float& x1) {
+  asm("{\n\t.reg .b64 a, b, d;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t"
+      "mul.rn.f32x2 d, a, b;\n\tmov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(x0), "=f"(x1)
+      : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
 }
 
 struct SoftmaxRow {
@@ -175,21 +166,44 @@ struct SoftmaxRow {
   float sc;
   uint32_t lane_base, s_col, o_col;
   const uint4* mask_tile;
+  int members;             // two-pass path: bits set in the row's mask words so far
 };
 
 // One-pass per-tile loop, column-split: the warp owns 32 query rows x 64 key columns
-// (`half` = which 64) of every tile, for BOTH heads of the CTA.  Every logit of a row is bounded
+// (`slice` = which 64) of every tile, for BOTH heads of the CTA.  Every logit of a row is bounded
 // by the row's `bound` (Cauchy-Schwarz on q and the largest key norm of the head), so
 // 2^(s*sc - bound) never overflows and the accumulator never needs rescaling.  Membership:
-// recomputed score >= row threshold.  Per tile: the routing weights (score >= thr ? score : 0)
-// of the 64 columns are packed to bf16 pairs in registers ONCE for both heads and R is released;
-// then, per head, p = 2^(s*c - bound) * weight goes to TMEM as bf16.  With eight warps on one
-// head's tile at a time, a head's S -> P -> PV -> next S chain is short enough to hide behind
-// the other head's pass.
-// Routing weights of tile j for the warp's 64 columns: (score >= thr ? score : 0) as bf16 pairs; R is
-// released as soon as it has been read.
+// recomputed score >= row threshold.  The routing weights (score >= thr ? score : 0) of a tile's 64
+// columns are packed to bf16 pairs in registers ONCE for both heads and R is released; per head,
+// p = 2^(s*c - bound) * weight goes to TMEM as bf16.  With eight warps on one head's tile at a
+// time, a head's S -> P -> PV -> next S chain is short enough to hide behind the other head's pass.
+//
+// Measured with the phase timers of the profiling build: a pass runs at the exp unit's rate (two
+// warps share a scheduler's 4 exp lanes: 2 x 64 instructions x 8 cycles), with a quarter of the
+// issue slots in use; a weight conversion on its own costs another 400 cycles per tile during
+// which the exp unit idles.  So the conversion of the NEXT tile's weights rides inside head 1's
+// pass (FUSE), as independent FMA-pipe work between the exponentials.
+
+// 16 raw scores -> 8 packed bf16 weight pairs; COUNT also adds the number of selected ones to `cnt`
+template <bool COUNT>
+__device__ __forceinline__ void convert_chunk(const uint32_t (&r)[16], float neg_c, uint32_t* w8, float& cnt) {
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    const float r0 = __uint_as_float(r[i]), r1 = __uint_as_float(r[i + 1]);
+    float st0, st1, w0, w1;
+    asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(st0) : "f"(r0), "f"(neg_c));   // 0x5D800000 = 2^60
+    asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(st1) : "f"(r1), "f"(neg_c));
+    mul2(r0, r1, st0, st1, w0, w1);
+    if (COUNT) cnt += st0 + st1;
+    w8[i >> 1] = pack_bf16x2(w0, w1);
+  }
+}
+
+// Routing weights of tile j for the warp's 64 columns on their own (the first tile, and CTAs with
+// one head); R is released as soon as it has been read.
+template <bool COUNT>
 __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, int j, int lane, float neg_c,
-                                                uint32_t (&w)[kSliceCols / 2], int* status,
+                                                uint32_t (&w)[kSliceCols / 2], float& cnt, int* status,
                                                 volatile uint32_t* abort_flag, Prof& prof) {
   prof.tick(7);
   if (!mbar_wait_bounded(&ctl->r_full, j & 1, abort_flag)) {
@@ -207,12 +221,8 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
       if (u & 1) tmem_ld16(r_col + (u + 1) * 16, ra);
       else tmem_ld16(r_col + (u + 1) * 16, rb);
     }
-#pragma unroll
-    for (int i = 0; i < 16; i += 2) {
-      const float r0 = __uint_as_float((u & 1) ? rb[i] : ra[i]);
-      const float r1 = __uint_as_float((u & 1) ? rb[i + 1] : ra[i + 1]);
-      w[u * 8 + (i >> 1)] = pack_bf16x2(keep_where_ge(r0, neg_c), keep_where_ge(r1, neg_c));
-    }
+    if (u & 1) convert_chunk<COUNT>(rb, neg_c, &w[u * 8], cnt);
+    else convert_chunk<COUNT>(ra, neg_c, &w[u * 8], cnt);
   }
   tc_fence_before();
   __syncwarp();
@@ -222,55 +232,80 @@ __device__ __forceinline__ bool convert_weights(AttnCtl* ctl, uint32_t r_col, in
 }
 
 // One head's pass over the warp's 64 columns of tile j: p = 2^(s*c - bound) * weight -> TMEM as bf16
-// pairs over the first 32 of those columns, always behind this thread's own reads.
-__device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, int x, int j, int lane, float sc,
-                                             float neg_b, const uint32_t (&wpk)[kSliceCols / 2], float& l0, float& l1,
-                                             int* status, volatile uint32_t* abort_flag, Prof& prof) {
+// pairs over the first 32 of those columns, always behind this thread's own reads.  FUSE (the
+// tile's last pass): the weights of tile j + 1 are converted from R(j + 1) in the same loop and
+// replace those of tile j in `wpk`, 16 columns at a time, as soon as this pass has used them.
+template <bool FUSE, bool COUNT>
+__device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, uint32_t r_col, int x, int j, int lane,
+                                             float sc, float neg_b, float neg_c, uint32_t (&wpk)[kSliceCols / 2],
+                                             float& cnt, float& l0, float& l1, int* status,
+                                             volatile uint32_t* abort_flag, Prof& prof) {
   prof.tick(7);
   if (!mbar_wait_bounded(&ctl->s_full[x], j & 1, abort_flag)) {
     record_status(status, kDevWaitAccFull);
     return false;
   }
   prof.tick(2 + 2 * x);
+  if (FUSE) {
+    if (!mbar_wait_bounded(&ctl->r_full, (j + 1) & 1, abort_flag)) {
+      record_status(status, kDevWaitAccFull);
+      return false;
+    }
+    prof.tick(0);
+  }
   tc_fence_after();
-  uint32_t sa[16], sb[16];
+  // One 16-column chunk of S per step.  Plain pass: the next chunk is requested before the
+  // current one is used (two register buffers).  Fused pass: one buffer -- the next S chunk is
+  // requested as soon as the current one has been consumed and arrives while the R chunk is
+  // converted, which keeps the pass within the register budget.
+  uint32_t sa[16], sb[FUSE ? 1 : 16], ra[FUSE ? 16 : 1];
   tmem_ld16(s_col, sa);
+  if constexpr (FUSE) tmem_ld16(r_col, ra);
 #pragma unroll
   for (int u = 0; u < kSliceCols / 16; ++u) {
     tc_wait_ld();
-    if (u + 1 < kSliceCols / 16) {
-      if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
-      else tmem_ld16(s_col + (u + 1) * 16, sb);
+    if constexpr (!FUSE) {
+      if (u + 1 < kSliceCols / 16) {
+        if (u & 1) tmem_ld16(s_col + (u + 1) * 16, sa);
+        else tmem_ld16(s_col + (u + 1) * 16, sb);
+      }
     }
     uint32_t packed[8];
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-      const float s0 = __uint_as_float((u & 1) ? sb[i] : sa[i]);
-      const float s1 = __uint_as_float((u & 1) ? sb[i + 1] : sa[i + 1]);
+      const bool odd = !FUSE && (u & 1);
+      const float s0 = __uint_as_float(odd ? sb[FUSE ? 0 : i] : sa[i]);
+      const float s1 = __uint_as_float(odd ? sb[FUSE ? 0 : i + 1] : sa[i + 1]);
       // both exponentials rounded to bf16, times the packed weights; the row sum adds exactly
       // the bf16 products the tensor core will see
-      const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(fmaf(s0, sc, neg_b)), ex2_approx(fmaf(s1, sc, neg_b))),
-                                     wpk[u * 8 + (i >> 1)]);
+      float x0, x1;
+      scale_shift2(s0, s1, sc, neg_b, x0, x1);
+      const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(x0), ex2_approx(x1)), wpk[u * 8 + (i >> 1)]);
       add_bf16x2_to_f32(l0, l1, pp);
       packed[i >> 1] = pp;
+    }
+    if constexpr (FUSE) {
+      if (u + 1 < kSliceCols / 16) tmem_ld16(s_col + (u + 1) * 16, sa);
+      convert_chunk<COUNT>(ra, neg_c, &wpk[u * 8], cnt);
+      if (u + 1 < kSliceCols / 16) tmem_ld16(r_col + (u + 1) * 16, ra);
     }
     tmem_st8(s_col + u * 8, packed);
   }
   tc_wait_st();
   tc_fence_before();
   __syncwarp();
-  if (lane == 0) mbar_arrive(&ctl->p_full[x]);
+  if (lane == 0) {
+    mbar_arrive(&ctl->p_full[x]);
+    if (FUSE) mbar_arrive(&ctl->r_free);
+  }
   prof.tick(3 + 2 * x);
   return true;
 }
 
-// The warps of a scheduler (column slices of the same rows) run the tile in two different orders, so
-// that some convert weights (FMA pipe) while the others compute exponentials (exp unit):
-//   even slices:  weights(j)  pass0(j)  pass1(j)
-//   odd slices :  pass0(j)  weights(j+1)  pass1(j)
+template <bool COUNT>
 __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int slice, int nh, int nKT,
                                                     int lane, float thr, float sc, const float (&bound)[2],
-                                                    float (&l_out)[2], int* status,
+                                                    float (&l_out)[2], float& cnt, int* status,
                                                     volatile uint32_t* abort_flag) {
   Prof prof;
   prof.start();
@@ -279,24 +314,28 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   // -(float just below the threshold) * 2^60; a +inf threshold (tail rows) gives -inf: nothing selected
   const float neg_c = -__uint_as_float(__float_as_uint(thr) - 1u) * 0x1p60f;
   float l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  const bool skew = (slice & 1) != 0;
-  uint32_t wa[kSliceCols / 2], wb[kSliceCols / 2];
-  if (skew && !convert_weights(ctl, r_col, 0, lane, neg_c, wa, status, abort_flag, prof)) return false;
+  uint32_t w[kSliceCols / 2];
+  cnt = 0.f;
+  if (!convert_weights<COUNT>(ctl, r_col, 0, lane, neg_c, w, cnt, status, abort_flag, prof)) return false;
   for (int j = 0; j < nKT; ++j) {
-    if (!skew && !convert_weights(ctl, r_col, j, lane, neg_c, wa, status, abort_flag, prof)) return false;
-    if (!softmax_pass(ctl, s_col0, 0, j, lane, sc, -bound[0], wa, l[0][0], l[0][1], status, abort_flag, prof)) return false;
-    if (skew && j + 1 < nKT && !convert_weights(ctl, r_col, j + 1, lane, neg_c, wb, status, abort_flag, prof)) return false;
-    if (nh == 2 &&
-        !softmax_pass(ctl, s_col0 + kTile, 1, j, lane, sc, -bound[1], wa, l[1][0], l[1][1], status, abort_flag, prof))
+    const bool more = j + 1 < nKT;
+    if (!softmax_pass<false, COUNT>(ctl, s_col0, r_col, 0, j, lane, sc, -bound[0], neg_c, w, cnt, l[0][0], l[0][1],
+                                    status, abort_flag, prof))
       return false;
-    if (skew) {
-#pragma unroll
-      for (int i = 0; i < kSliceCols / 2; ++i) wa[i] = wb[i];
+    bool ok;
+    if (nh == 2) {
+      ok = more ? softmax_pass<true, COUNT>(ctl, s_col0 + kTile, r_col, 1, j, lane, sc, -bound[1], neg_c, w, cnt,
+                                            l[1][0], l[1][1], status, abort_flag, prof)
+                : softmax_pass<false, COUNT>(ctl, s_col0 + kTile, r_col, 1, j, lane, sc, -bound[1], neg_c, w, cnt,
+                                             l[1][0], l[1][1], status, abort_flag, prof);
+    } else {
+      ok = !more || convert_weights<COUNT>(ctl, r_col, j + 1, lane, neg_c, w, cnt, status, abort_flag, prof);
     }
+    if (!ok) return false;
   }
   l_out[0] = l[0][0] + l[0][1];
   l_out[1] = l[1][0] + l[1][1];
-  prof.flush(skew ? 8 : 0, lane == 0);
+  prof.flush(slice & 1 ? 8 : 0, lane == 0);
   return true;
 }
 
@@ -392,6 +431,7 @@ __device__ __forceinline__ bool softmax_tiles_exact(SoftmaxRow& st, AttnCtl* ctl
     tc_fence_before();
     __syncwarp();
     if (lane < kSlices) mbar_arrive(&ctl->p_full[x]);
+    st.members += __popc(mw.x) + __popc(mw.y) + __popc(mw.z) + __popc(mw.w);
     mw = mw_next;
   }
   return true;
@@ -431,7 +471,8 @@ __global__ void key_norm_max_kernel(const __nv_bfloat16* __restrict__ k, int64_t
   }
 }
 
-template <bool kSplit>      // the key range of a (query tile, head pair) is shared by p.split CTAs
+template <bool kSplit,      // the key range of a (query tile, head pair) is shared by p.split CTAs
+          bool kCount = false>   // diagnostic: also write how many keys every row treated as selected
 __global__ void __launch_bounds__(kAttnThreads, 1)
     dsa_attn_masked_kernel(const __grid_constant__ CUtensorMap tm_wq, const __grid_constant__ CUtensorMap tm_wk,
                            const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -501,49 +542,51 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       for (int x = 0; x < nh; ++x)
         tma_load_4d(smem + kOffQ + x * kQTileBytes, &tm_q, &ctl->q_full, 0, qt * kTile, h0 + x, b);
 
-      // five independent streams, each issued as soon as its slot is free
-      int n_wk = 0, n_k[2] = {0, 0}, n_v[2] = {0, 0};
-      ProgressClock clk;
-      clk.reset();
-      for (;;) {
-        bool done = n_wk == nKT, progress = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) done = done && (x >= nh || (n_k[x] == nKT && n_v[x] == nKT));
-        if (done) break;
-        if (n_wk < nKT && mbar_test_wait(&ctl->wk_empty[n_wk & 1], ((n_wk >> 1) & 1) ^ 1)) {
-          uint8_t* dst = smem + kOffWk + (n_wk & 1) * kWTileBytes;
-          mbar_expect_tx(&ctl->wk_full[n_wk & 1], kWTileBytes);
-          tma_load_3d(dst, &tm_wk, &ctl->wk_full[n_wk & 1], 0, (kt0 + n_wk) * kTile, b);
-          tma_load_3d(dst + kWTileBytes / 2, &tm_wk, &ctl->wk_full[n_wk & 1], 32, (kt0 + n_wk) * kTile, b);
-          ++n_wk;
-          progress = true;
+      // The slots are freed in a fixed order in time -- within tile i: K_x(i) (its QK retired), the
+      // indexer keys, then V_0(i), V_1(i) (their PV retired) -- so one thread refills them in that
+      // order with suspending waits instead of polling five barriers in a busy loop, which costs
+      // the scheduler it shares with two softmax warps a quarter of its issue slots.
+      bool ok = true;
+      auto load_wk = [&](int j) {
+        if (!ok) return;
+        if (!mbar_wait_bounded(&ctl->wk_empty[j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
+        uint8_t* dst = smem + kOffWk + (j & 1) * kWTileBytes;
+        mbar_expect_tx(&ctl->wk_full[j & 1], kWTileBytes);
+        tma_load_3d(dst, &tm_wk, &ctl->wk_full[j & 1], 0, (kt0 + j) * kTile, b);
+        tma_load_3d(dst + kWTileBytes / 2, &tm_wk, &ctl->wk_full[j & 1], 32, (kt0 + j) * kTile, b);
+      };
+      auto load_k = [&](int x, int j) {
+        if (!ok || x >= nh) return;
+        if (!mbar_wait_bounded(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1, abort_flag)) { ok = false; return; }
+        mbar_expect_tx(&ctl->k_full[x][j & 1], kQTileBytes);
+        tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, (kt0 + j) * kTile,
+                    h0 + x, b);
+      };
+      auto load_v = [&](int x, int j) {
+        if (!ok || x >= nh) return;
+        if (!mbar_wait_bounded(&ctl->v_empty[x], (j & 1) ^ 1, abort_flag)) { ok = false; return; }
+        mbar_expect_tx(&ctl->v_full[x], kQTileBytes);
+        tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, (kt0 + j) * kTile, h0 + x, b);
+      };
+      for (int j = 0; j < 2 && j < nKT; ++j) {
+        load_wk(j);
+        load_k(0, j);
+        load_k(1, j);
+      }
+      load_v(0, 0);
+      load_v(1, 0);
+      for (int i = 0; i < nKT && ok; ++i) {
+        if (i + 2 < nKT) {
+          load_k(0, i + 2);
+          load_k(1, i + 2);
+          load_wk(i + 2);
         }
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          if (x >= nh) continue;
-          int j = n_k[x];
-          if (j < nKT && mbar_test_wait(&ctl->k_empty[x][j & 1], ((j >> 1) & 1) ^ 1)) {
-            mbar_expect_tx(&ctl->k_full[x][j & 1], kQTileBytes);
-            tma_load_4d(smem + kOffK + (x * 2 + (j & 1)) * kQTileBytes, &tm_k, &ctl->k_full[x][j & 1], 0, (kt0 + j) * kTile,
-                        h0 + x, b);
-            ++n_k[x];
-            progress = true;
-          }
-          j = n_v[x];
-          if (j < nKT && mbar_test_wait(&ctl->v_empty[x], (j & 1) ^ 1)) {
-            mbar_expect_tx(&ctl->v_full[x], kQTileBytes);
-            tma_load_4d(smem + kOffV + x * kQTileBytes, &tm_v, &ctl->v_full[x], 0, (kt0 + j) * kTile, h0 + x, b);
-            ++n_v[x];
-            progress = true;
-          }
-        }
-        if (progress) {
-          clk.reset();
-        } else if (clk.expired(abort_flag)) {
-          record_status(p.status, kDevWaitStageEmpty);
-          break;
+        if (i + 1 < nKT) {
+          load_v(0, i + 1);
+          load_v(1, i + 1);
         }
       }
+      if (!ok) record_status(p.status, kDevWaitStageEmpty);
     }
   } else if (warp == 1) {
     // ------------------------------------------- MMA issuer of the routing-weight tiles R(j)
@@ -700,9 +743,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     float inv = 0.f;
     float row_l = 0.f, row_mu = 0.f, row_mt = 0.f;   // row statistics of this CTA's key range (for the split merge)
     if (!exact) {
-      float l_part[2];
-      ok = softmax_tiles_split(ctl, lane_base, slice, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, p.status,
-                               abort_flag);
+      float l_part[2], cnt = 0.f;
+      ok = softmax_tiles_split<kCount>(ctl, lane_base, slice, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, cnt,
+                                       p.status, abort_flag);
+      if (kCount && hp == 0 && row_ok) atomicAdd(p.member_count + static_cast<int64_t>(b) * p.Tq + qrow, static_cast<int>(cnt));
       // The column slices of a row add their partial sums through the indexer-query tile:
       // every routing-weight MMA that read it has retired once any warp has left its loop.
       float* lsum = reinterpret_cast<float*>(smem + kOffWq);      // [2 heads][128 rows][kSlices]
@@ -725,7 +769,9 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
       st.sc = p.scale_log2;
       st.m_true = st.m_used = -__int_as_float(0x7f800000);
       st.l = 0.f;
+      st.members = 0;
       ok = softmax_tiles_exact(st, ctl, x, nKT, lane, kSoftWarps / (4 * nh), p.status, abort_flag);
+      if (kCount && hp == 0 && x == 0 && row_ok) atomicAdd(p.member_count + static_cast<int64_t>(b) * p.Tq + qrow, st.members);
       // the reference's clamp: out = O c / max(l c, 1e-6), c = 2^(m_used - m_true)
       const float corr = (st.m_used == st.m_true) ? 1.f : ex2_approx(st.m_used - st.m_true);
       inv = corr / fmaxf(st.l * corr, 1e-6f);
@@ -898,7 +944,7 @@ int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes) {
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
-                         size_t scratch_bytes, int* status, cudaStream_t st) {
+                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count) {
   if (!q || !k || !v || !maskbits || !workspace || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (D != kHeadDim) return SWV_ERR_UNSUPPORTED;
@@ -957,7 +1003,8 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   {
     size_t need = 0;
     dsa_attn_scratch_bytes_impl(B, H, Tq, Tk, &need);
-    if (need > 0 && scratch != nullptr && scratch_bytes >= need && (reinterpret_cast<uintptr_t>(scratch) & 255) == 0) {
+    if (need > 0 && member_count == nullptr && scratch != nullptr && scratch_bytes >= need &&
+        (reinterpret_cast<uintptr_t>(scratch) & 255) == 0) {
       const size_t ctas = static_cast<size_t>(B) * p.nQT * p.nHP;
       p.split = attn_split_factor(B, H, Tq, Tk);
       p.tickets = static_cast<uint32_t*>(scratch);
@@ -972,7 +1019,13 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
         static_cast<const __nv_bfloat16*>(k), ks[0], ks[1], ks[2], B, H, Tk, kmax2);
   }
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP * p.split;
-  if (p.split == 1) {
+  p.member_count = member_count;
+  if (member_count != nullptr) {
+    SWV_CUDA_OK(cudaMemsetAsync(member_count, 0, static_cast<size_t>(B) * Tq * sizeof(int), st));
+    SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(attn_smem_bytes())));
+    dsa_attn_masked_kernel<false, true><<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);
+  } else if (p.split == 1) {
     SWV_CUDA_OK(cudaFuncSetAttribute(dsa_attn_masked_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(attn_smem_bytes())));
     dsa_attn_masked_kernel<false><<<grid, kAttnThreads, attn_smem_bytes(), st>>>(tm_wq, tm_wk, tm_q, tm_k, tm_v, p);

@@ -168,6 +168,26 @@ def dsa_attention_masked(q, k, v, selection, o):
     return o
 
 
+def dsa_attention_masked_count(q, k, v, selection, o):
+    """Diagnostic: ``dsa_attention_masked`` (unsplit) that also returns, per query row, how many keys
+    the kernel treated as selected, int32 (B, Tq); must equal min(top_k, Tk) everywhere."""
+    mask, ws = selection
+    _require_cuda(q, k, v, mask, ws, o)
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    if q.dtype != torch.bfloat16 or D != 64:
+        raise SwvError("dsa_attention_masked needs bf16 q/k/v with head_dim 64")
+    q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+    dev = q.device
+    cnt = torch.empty((B, Tq), dtype=torch.int32, device=dev)
+    rc = lib.swv_dsa_attn_masked_count_fwd(
+        q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), mask.data_ptr(),
+        ws.data_ptr(), o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D, cnt.data_ptr(),
+        status_word(dev).data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_attn_masked_count_fwd")
+    return cnt
+
+
 def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False, kv_ready=None):
     """Indexer + top-k + routing-weighted attention (deepseek_sparse_attention.py:59-85).
 

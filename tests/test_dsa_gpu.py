@@ -365,3 +365,33 @@ def test_random_shapes(swv, seed):
     assert torch.isfinite(o).all(), tag
     assert float((o - o2).abs().max()) < 2e-2, tag
     assert float((o - o2).abs().mean()) < 1e-3, tag
+
+
+@pytest.mark.parametrize("T,H,K,mode", [(16384, 8, 2048, "bench"), (65536, 2, 2048, "bench"), (1500, 2, 300, "ties"),
+                                        (900, 3, 800, "fewpos")])
+def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode):
+    """The dense attention sweep recomputes every score tile on the tensor cores and, on its one-pass
+    path, treats a key as selected iff that score >= the row threshold the indexer found.  The
+    diagnostic entry point counts those keys per row: exactly min(K, T) everywhere <=> the
+    recomputed tiles are bit-identical to the scores the selection was made on (one flipped key
+    would be invisible in the output tolerance).  Benchmark-distributed inputs at 16384 and 65536
+    tokens (one-pass path), heavily tied scores and rows with fewer than K positive scores (the
+    two-pass bitmask path)."""
+    q, k, v, qi, ki, w = make_dsa_inputs(T, H, 64, 4, 64, seed=77 + T, dtype=torch.bfloat16, device=_dev())
+    if mode == "ties":
+        qi, ki = (qi.float() * 32).round() / 32, (ki.float() * 32).round() / 32
+        qi, ki = qi.to(torch.bfloat16), ki.to(torch.bfloat16)
+    if mode == "fewpos":
+        qi, ki = qi.abs(), -ki.abs()
+        ki[:, ::5] = ki[:, ::5].abs()
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    o = torch.empty((1, H, T, 64), dtype=torch.float32, device=_dev())
+    from sparse_wsi_vit_b200.ops import dsa_attention_masked_count
+    cnt = dsa_attention_masked_count(q, k, v, sel, o)
+    _check(swv)
+    assert int(cnt.min()) == min(K, T) and int(cnt.max()) == min(K, T), (int(cnt.min()), int(cnt.max()))
+    # and the output of the counting instantiation is the regular kernel's
+    o2 = torch.empty_like(o)
+    swv.dsa_attention_masked(q, k, v, sel, o2)
+    _check(swv)
+    assert float((o - o2).abs().max()) < 1e-5
