@@ -184,3 +184,72 @@ def dsa_forward(q, k, v, q_idx, k_idx, w, top_k, dtype=torch.float32):
     rw = sel * valid                                      # M:73
     o = dsa_attention(q, k, v, idx, valid, rw, dtype=dtype)
     return o, idx, valid, sel
+
+
+# --------------------------------------------------------------------------- #
+# backward  (K:128-339 indexer, K:569-762 attention; K:388-445, K:812-853 the Functions)
+# --------------------------------------------------------------------------- #
+def dsa_attention_bwd(d_out, q, k, v, o, idx, valid, rw, dtype=torch.float32):
+    """Gradients of the routing-weighted attention as the reference's `_dsa_attention_bwd`
+    computes them (K:569-762), one batch element: q, k, v, o, d_out (H, T, D); idx/valid/rw (T, K).
+
+      logit_j = q.k[idx_j]/sqrt(D); m = max over valid j; l = sum_j exp(logit_j - m) rw_j;
+      l_safe = max(l, 1e-6); sm_j = exp(logit_j - m)/l_safe; P_j = sm_j rw_j      (K:596-637, K:676-678)
+      Di = sum_d dO O (K:641-656);  dP_j = dO.v[idx_j]                              (K:693)
+      dV[idx_j] += P_j valid_j dO (K:694-700);  dRW_j = sum_h sm_j (dP_j - Di)     (K:702-708)
+      dS_j = rw_j sm_j (dP_j - Di)/sqrt(D) (K:710); dQ += sum_j dS_j k[idx_j]; dK[idx_j] += dS_j q (K:735-748)
+
+    Returns dq, dk, dv (H, T, D) and drw (T, K).  Equal to autograd through ``dsa_attention``
+    wherever the 1e-6 clamp is not active.
+    """
+    H, T, D = q.shape
+    scale = 1.0 / math.sqrt(D)
+    qf, kf, vf, of, dof = (t.to(dtype) for t in (q, k, v, o, d_out))
+    dq, dk, dv = torch.zeros_like(qf), torch.zeros_like(kf), torch.zeros_like(vf)
+    drw = torch.zeros(idx.shape, dtype=dtype)
+    ii = idx.long()
+    vm = valid > 0
+    w = rw.to(dtype)
+    for h in range(H):
+        kg, vg = kf[h][ii], vf[h][ii]                                     # (T, K, D)
+        logit = torch.einsum("td,tkd->tk", qf[h], kg) * scale
+        logit = torch.where(vm, logit, torch.full_like(logit, -float("inf")))
+        m = logit.max(dim=1, keepdim=True).values
+        e = torch.where(vm, torch.exp(logit - m), torch.zeros_like(logit))
+        l_safe = torch.clamp((e * w).sum(dim=1, keepdim=True), min=1e-6)
+        sm = e / l_safe
+        di = (dof[h] * of[h]).sum(dim=1, keepdim=True)
+        dp = torch.einsum("td,tkd->tk", dof[h], vg)
+        g = torch.where(vm, sm * (dp - di), torch.zeros_like(sm))
+        drw += g
+        ds = w * g * scale
+        dq[h] = torch.einsum("tk,tkd->td", ds, kg)
+        dk[h].index_add_(0, ii.reshape(-1), (ds[:, :, None] * qf[h][:, None, :]).reshape(-1, D))
+        pv = torch.where(vm, sm * w, torch.zeros_like(sm))
+        dv[h].index_add_(0, ii.reshape(-1), (pv[:, :, None] * dof[h][:, None, :]).reshape(-1, D))
+    return dq, dk, dv, drw
+
+
+def indexer_bwd(d_scores, q_idx, k_idx, w, idx, valid, dtype=torch.float32):
+    """Gradients of the indexer as the reference's three backward kernels compute them
+    (K:128-339), one batch element: q_idx, k_idx (T, IH, ID); d_scores, idx, valid (T, K).
+
+      g = d_scores * valid
+      dQ[t,h,:] = sum_j g[t,j] W[h] K[idx[t,j],h,:]          (K:128-203)
+      dK[idx[t,j],h,:] += g[t,j] W[h] Q[t,h,:]                (K:206-270)
+      dW[h] = sum_{t,j} g[t,j] (Q[t,h,:] . K[idx[t,j],h,:])   (K:273-339)
+
+    This is the gradient of  sum_h W[h] q_h.k_h  (the form the reference's backward assumes,
+    K:116), NOT of the forward's relu((sum_h W_h q_h).(sum_h W_h k_h)) (K:66-70): the reference
+    is inconsistent with itself here, and a drop-in follows what its training loop runs.
+    """
+    qf, kf, wf = q_idx.to(dtype), k_idx.to(dtype), w.to(dtype)
+    g = (d_scores.to(dtype) * valid.to(dtype))
+    ii = idx.long()
+    T, IH, ID = qf.shape
+    kg = kf[ii]                                                            # (T, K, IH, ID)
+    dq = torch.einsum("tj,h,tjhd->thd", g, wf, kg)
+    dk = torch.zeros_like(kf)
+    dk.index_add_(0, ii.reshape(-1), (g[:, :, None, None] * wf[None, None, :, None] * qf[:, None, :, :]).reshape(-1, IH, ID))
+    dw = torch.einsum("tj,thd,tjhd->h", g, qf, kg)
+    return dq, dk, dw

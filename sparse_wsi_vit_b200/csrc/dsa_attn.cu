@@ -45,9 +45,10 @@ constexpr int kQTileBytes = kTile * kHeadDim * 2;     // 16 KiB bf16 tile
 constexpr int kWTileBytes = kTile * kIdxDim * 4;      // 32 KiB fp32 indexer tile (two K halves)
 constexpr int kAttnTmemCols = 512;
 constexpr uint32_t kColR = 0, kColS = 128, kColO = 384;
-constexpr int kSlices = 2;                            // one-pass path: column slices of a tile (warps per row quarter);
-                                                      // 4 (16 softmax warps) measures the same: the tile period is set by
-                                                      // the MMA streams and the exp unit, not by softmax latency
+#ifndef SWV_ATTN_SLICES
+#define SWV_ATTN_SLICES 2
+#endif
+constexpr int kSlices = SWV_ATTN_SLICES;              // one-pass path: column slices of a tile (warps per row quarter)
 constexpr int kSoftWarps = 4 * kSlices;               // softmax warps
 constexpr int kSliceCols = kTile / kSlices;
 constexpr int kAttnThreads = 64 + 32 * kSoftWarps + 64;   // TMA, R issuer, softmax warps, two head issuers
@@ -178,11 +179,15 @@ struct SoftmaxRow {
 // p = 2^(s*c - bound) * weight goes to TMEM as bf16.  With eight warps on one head's tile at a
 // time, a head's S -> P -> PV -> next S chain is short enough to hide behind the other head's pass.
 //
-// Measured with the phase timers of the profiling build: a pass runs at the exp unit's rate (two
-// warps share a scheduler's 4 exp lanes: 2 x 64 instructions x 8 cycles), with a quarter of the
-// issue slots in use; a weight conversion on its own costs another 400 cycles per tile during
-// which the exp unit idles.  So the conversion of the NEXT tile's weights rides inside head 1's
-// pass (FUSE), as independent FMA-pipe work between the exponentials.
+// Measured with the phase timers of the profiling build (65536 tokens, cycles per tile and
+// scheduler): a plain pass takes 1080-1220 cycles against the exp unit's 1024 (two warps share a
+// scheduler's 4 exp lanes: 2 x 64 instructions x 8 cycles), whether 2 or 4 warps share the
+// scheduler; a weight conversion on its own costs another 400 cycles during which the exp unit
+// idles.  With the conversion of the NEXT tile's weights inside head 1's pass (FUSE) that pass
+// takes 1430-1490 cycles: about 17 dispatch cycles per column pair (half-rate ALU / conversion
+// instructions count twice) beside 16 exp cycles, i.e. the scheduler's dispatch port and the exp
+// unit are both close to saturated and the tile period (3230 cycles, of which ~350 are waits for
+// the tensor pipe) sits ~1.5x above either floor.
 
 // 16 raw scores -> 8 packed bf16 weight pairs; COUNT also adds the number of selected ones to `cnt`
 template <bool COUNT>
@@ -283,11 +288,23 @@ __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, uint3
       const uint32_t pp = mul_bf16x2(pack_bf16x2(ex2_approx(x0), ex2_approx(x1)), wpk[u * 8 + (i >> 1)]);
       add_bf16x2_to_f32(l0, l1, pp);
       packed[i >> 1] = pp;
+      if constexpr (FUSE) {
+        // The next tile's weight pair takes the register of the pair just used (written pair by
+        // pair between the exponentials: a warp issues in order).
+        const float r0 = __uint_as_float(ra[i]), r1 = __uint_as_float(ra[i + 1]);
+        float st0, st1, w0, w1;
+        asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(st0) : "f"(r0), "f"(neg_c));
+        asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(st1) : "f"(r1), "f"(neg_c));
+        mul2(r0, r1, st0, st1, w0, w1);
+        if (COUNT) cnt += st0 + st1;
+        wpk[u * 8 + (i >> 1)] = pack_bf16x2(w0, w1);
+      }
     }
     if constexpr (FUSE) {
-      if (u + 1 < kSliceCols / 16) tmem_ld16(s_col + (u + 1) * 16, sa);
-      convert_chunk<COUNT>(ra, neg_c, &wpk[u * 8], cnt);
-      if (u + 1 < kSliceCols / 16) tmem_ld16(r_col + (u + 1) * 16, ra);
+      if (u + 1 < kSliceCols / 16) {
+        tmem_ld16(s_col + (u + 1) * 16, sa);
+        tmem_ld16(r_col + (u + 1) * 16, ra);
+      }
     }
     tmem_st8(s_col + u * 8, packed);
   }

@@ -2,7 +2,9 @@
 
 Run once, in a container that has the reference checkout:
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [group ...]
+
+(groups: rope static dsa dsa_bwd dsa_module; default all)
 
 The DSA Triton kernels are executed on CPU tensors by Triton's interpreter
 (``TRITON_INTERPRET=1``); the static attention and the 2-D RoPE are plain
@@ -72,6 +74,45 @@ def make_dsa(ref_kernels):
     np.savez_compressed(os.path.join(HERE, "dsa_reference.npz"), **out)
 
 
+def dsa_bwd_cases():
+    """(name, B, T, H, D, IH, ID, K, tile)"""
+    return [
+        ("bwd_rand", 1, 48, 2, 16, 2, 16, 8, 16),
+        ("bwd_batch2", 2, 40, 2, 32, 4, 16, 16, 16),
+        ("bwd_short", 1, 6, 1, 16, 2, 16, 8, 16),
+    ]
+
+
+def make_dsa_bwd(ref_kernels):
+    """Forward + backward of the reference's two autograd Functions (the op sequence of
+    DeepSeekSparseAttention.forward) with a seeded upstream gradient; stores every gradient the
+    reference produces: dq, dk, dv, the routing-weight gradient, and the indexer's dq_idx, dk_idx, dW."""
+    out = {}
+    for name, B, T, H, D, IH, ID, K, tile in dsa_bwd_cases():
+        g = torch.Generator().manual_seed(sum(map(ord, name)))
+        q = (torch.randn(B, H, T, D, generator=g) / D ** 0.5).requires_grad_()
+        k = torch.randn(B, H, T, D, generator=g).requires_grad_()
+        v = torch.randn(B, H, T, D, generator=g).requires_grad_()
+        qi = (torch.randn(B, T, IH, ID, generator=g) / ID ** 0.5).requires_grad_()
+        ki = (torch.randn(B, T, IH, ID, generator=g) / ID ** 0.5).requires_grad_()
+        w = torch.randn(IH, generator=g).requires_grad_()
+        d_out = torch.randn(B, H, T, D, generator=g)
+        idx, valid, scores = ref_kernels.LightningIndexerFunction.apply(qi, ki, w, B, T, IH, ID, K, tile, tile, tile, IH)
+        rw = scores * valid
+        rw.retain_grad()
+        o = torch.zeros(B, H, T, D)
+        res = ref_kernels.DSAAttentionFunction.apply(q, k, v, idx.detach(), valid.detach(), rw, o, B, H, T, D, K,
+                                                     tile, tile, H, tile)
+        (res * d_out).sum().backward()
+        for key, val in dict(q=q, k=k, v=v, qi=qi, ki=ki, w=w, d_out=d_out, idx=idx, valid=valid, scores=scores,
+                             o=res, dq=q.grad, dk=k.grad, dv=v.grad, drw=rw.grad, dqi=qi.grad, dki=ki.grad,
+                             dw=w.grad).items():
+            out[f"{name}.{key}"] = _np(val)
+        out[f"{name}.dims"] = np.array([B, T, H, D, IH, ID, K], dtype=np.int64)
+        print(name, "done", flush=True)
+    np.savez_compressed(os.path.join(HERE, "dsa_bwd_reference.npz"), **out)
+
+
 def make_dsa_module(ref_mod):
     """Whole attention module (projections included) with its state_dict."""
     torch.manual_seed(1234)
@@ -129,10 +170,17 @@ def main():
     from sparse_wsi_vit.models import deepseek_sparse_attention as ref_mod
     from sparse_wsi_vit.models import static_sparse_attention as ref_static
     from sparse_wsi_vit.models.vit_5 import rope as ref_rope
-    make_rope(ref_rope)
-    make_static(ref_static)
-    make_dsa(ref_kernels)
-    make_dsa_module(ref_mod)
+    only = sys.argv[2:]                      # optional: names of the fixture groups to regenerate
+    if not only or "rope" in only:
+        make_rope(ref_rope)
+    if not only or "static" in only:
+        make_static(ref_static)
+    if not only or "dsa" in only:
+        make_dsa(ref_kernels)
+    if not only or "dsa_bwd" in only:
+        make_dsa_bwd(ref_kernels)
+    if not only or "dsa_module" in only:
+        make_dsa_module(ref_mod)
 
 
 if __name__ == "__main__":

@@ -390,8 +390,9 @@ def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode
     cnt = dsa_attention_masked_count(q, k, v, sel, o)
     _check(swv)
     assert int(cnt.min()) == min(K, T) and int(cnt.max()) == min(K, T), (int(cnt.min()), int(cnt.max()))
-    # and the output of the counting instantiation is the regular kernel's
+    # and the output of the counting instantiation is the regular kernel's (which may split the key
+    # range over several CTAs and add the parts up in another order)
     o2 = torch.empty_like(o)
     swv.dsa_attention_masked(q, k, v, sel, o2)
     _check(swv)
-    assert float((o - o2).abs().max()) < 1e-5
+    assert float((o - o2).abs().max()) < 1e-3
