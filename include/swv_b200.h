@@ -158,6 +158,43 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             void* workspace, void* o, const int64_t o_strides[4], int o_dtype, int B, int H,
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream);
 
+/* Backward of the routing-weighted attention over explicit key lists.
+ * Replaces DSAAttentionFunction.backward and its kernel (K:812-853, K:569-762), same arithmetic:
+ *   sm_j = exp(logit_j - m) / max(l, 1e-6),  Di = sum_d dO O,  dP_j = dO . v[idx_j],
+ *   dV[idx_j] += sm_j rw_j dO,   dRW_j = sum_heads sm_j (dP_j - Di),
+ *   dS_j = rw_j sm_j (dP_j - Di) / sqrt(D),   dQ = sum_j dS_j k[idx_j],   dK[idx_j] += dS_j q.
+ *   d_out, o (B,H,Tq,D) in o_dtype, q (B,H,Tq,D), k, v (B,H,Tk,D) in qkv_dtype, strides (b,h,t,d),
+ *   k and v with unit inner stride; idx / valid / rw (B,Tq,top_k) as in swv_dsa_attn_gather_fwd.
+ * Outputs are fp32 and contiguous (the reference accumulates in the storage dtype of q, k, v; the
+ * caller rounds once): dq (B,H,Tq,D), dk, dv (B,H,Tk,D), drw (B,Tq,top_k).  dk, dv and drw are
+ * zeroed by the call and accumulated with reductions, so their low bits depend on the order of
+ * arrival.  D even, <= 256.
+ */
+int swv_dsa_attn_bwd(const void* d_out, const int64_t d_out_strides[4], const void* q, const int64_t q_strides[4],
+                     const void* k, const int64_t k_strides[4], const void* v, const int64_t v_strides[4], int qkv_dtype,
+                     const void* o, const int64_t o_strides[4], int o_dtype, const int32_t* idx,
+                     const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3], const float* rw,
+                     const int64_t rw_strides[3], float* dq, float* dk, float* dv, float* drw, int B, int H, int Tq,
+                     int Tk, int D, int top_k, int* status, void* stream);
+
+/* Backward of the lightning indexer.
+ * Replaces LightningIndexerFunction.backward and its three kernels (K:388-445, K:128-339), same
+ * arithmetic, with g = d_scores * valid:
+ *   dQ[t,h,:] = sum_j g[t,j] W[h] K[idx[t,j],h,:],   dK[idx[t,j],h,:] += g[t,j] W[h] Q[t,h,:],
+ *   dW[h] = sum_{t,j} g[t,j] (Q[t,h,:] . K[idx[t,j],h,:]).
+ * (This is the gradient of sum_h W[h] q_h.k_h, the form the reference's backward assumes, K:116;
+ * its forward computes relu((sum_h W_h q_h).(sum_h W_h k_h)), K:66-70.  A drop-in follows what the
+ * reference's training loop runs.)
+ *   d_scores (B,Tq,top_k) f32 with strides; q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID) as in the forward.
+ * Outputs fp32 contiguous: dq_idx (B,Tq,IH,ID), dk_idx (B,Tk,IH,ID), dw (IH); dk_idx and dw are
+ * zeroed by the call.  ID even, IH <= 64, IH*ID <= 512.
+ */
+int swv_dsa_indexer_bwd(const float* d_scores, const int64_t d_scores_strides[3], const void* q_idx,
+                        const int64_t q_strides[4], const void* k_idx, const int64_t k_strides[4], int idx_dtype,
+                        const float* w, const int32_t* idx, const int64_t idx_strides[3], const float* valid,
+                        const int64_t valid_strides[3], float* dq_idx, float* dk_idx, float* dw, int B, int Tq, int Tk,
+                        int IH, int ID, int top_k, int* status, void* stream);
+
 /* Diagnostic twin of swv_dsa_attn_masked_fwd (no counterpart in the reference): the same kernel,
  * never split over the key range, that also writes `member_count` (B, Tq) int32 = the number of
  * keys every query row treated as selected while it swept the key tiles (rows on the one-pass

@@ -43,6 +43,15 @@ int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, cons
                            int sel_block, int n_sel, float* o, cudaStream_t st);
 int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
                      int out_dtype, int B, int Hq, int T, int D, cudaStream_t st);
+int dsa_attn_bwd_impl(const void* d_out, const int64_t* dos, const void* q, const int64_t* qs, const void* k,
+                      const int64_t* ks, const void* v, const int64_t* vs, int dtype, const void* o,
+                      const int64_t* os, int o_dtype, const int32_t* idx, const int64_t* is, const float* valid,
+                      const int64_t* vls, const float* rw, const int64_t* rs, float* dq, float* dk, float* dv,
+                      float* drw, int B, int H, int Tq, int Tk, int D, int top_k, int* status, cudaStream_t st);
+int dsa_indexer_bwd_impl(const float* d_scores, const int64_t* dss, const void* q_idx, const int64_t* qs,
+                         const void* k_idx, const int64_t* ks, int dtype, const float* w, const int32_t* idx,
+                         const int64_t* is, const float* valid, const int64_t* vls, float* dq, float* dk, float* dw,
+                         int B, int Tq, int Tk, int IH, int ID, int top_k, int* status, cudaStream_t st);
 int nsa_workspace_bytes_impl(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
                              int n_sel, int window, size_t* bytes);
 int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
@@ -114,6 +123,27 @@ int swv_dsa_attn_gather_fwd(const void* q, const int64_t q_strides[4], const voi
   return swv::dsa_attn_gather_impl(q, q_strides, k, k_strides, v, v_strides, qkv_dtype, idx, idx_strides, valid,
                                    valid_strides, rw, rw_strides, o, o_strides, o_dtype, B, H, Tq, Tk, D, top_k,
                                    kv_group, status, static_cast<cudaStream_t>(stream));
+}
+
+int swv_dsa_attn_bwd(const void* d_out, const int64_t d_out_strides[4], const void* q, const int64_t q_strides[4],
+                     const void* k, const int64_t k_strides[4], const void* v, const int64_t v_strides[4], int qkv_dtype,
+                     const void* o, const int64_t o_strides[4], int o_dtype, const int32_t* idx,
+                     const int64_t idx_strides[3], const float* valid, const int64_t valid_strides[3], const float* rw,
+                     const int64_t rw_strides[3], float* dq, float* dk, float* dv, float* drw, int B, int H, int Tq,
+                     int Tk, int D, int top_k, int* status, void* stream) {
+  return swv::dsa_attn_bwd_impl(d_out, d_out_strides, q, q_strides, k, k_strides, v, v_strides, qkv_dtype, o, o_strides,
+                                o_dtype, idx, idx_strides, valid, valid_strides, rw, rw_strides, dq, dk, dv, drw, B, H,
+                                Tq, Tk, D, top_k, status, static_cast<cudaStream_t>(stream));
+}
+
+int swv_dsa_indexer_bwd(const float* d_scores, const int64_t d_scores_strides[3], const void* q_idx,
+                        const int64_t q_strides[4], const void* k_idx, const int64_t k_strides[4], int idx_dtype,
+                        const float* w, const int32_t* idx, const int64_t idx_strides[3], const float* valid,
+                        const int64_t valid_strides[3], float* dq_idx, float* dk_idx, float* dw, int B, int Tq, int Tk,
+                        int IH, int ID, int top_k, int* status, void* stream) {
+  return swv::dsa_indexer_bwd_impl(d_scores, d_scores_strides, q_idx, q_strides, k_idx, k_strides, idx_dtype, w, idx,
+                                   idx_strides, valid, valid_strides, dq_idx, dk_idx, dw, B, Tq, Tk, IH, ID, top_k,
+                                   status, static_cast<cudaStream_t>(stream));
 }
 
 int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes) {

@@ -6,7 +6,8 @@ src/sparse_wsi_vit/models/deepseek_sparse_attention.py of the reference
 DSAViTSlideEncoder :169-305) so that a reference ``state_dict`` loads unchanged
 and configs that name these classes keep working.  The attention itself runs on
 the sm_100a kernels (``ops.dsa_sparse_attention``); projections, LayerNorm and
-the MLP stay PyTorch/cuBLAS.  Forward only.
+the MLP stay PyTorch/cuBLAS.  With gradients enabled the attention is one
+differentiable op backed by the backward kernels (``ops.DSAModuleFunction``).
 """
 from __future__ import annotations
 
@@ -14,7 +15,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
-from .ops import dsa_sparse_attention, rope2d
+from .ops import DSAModuleFunction, Rope2dFunction, dsa_sparse_attention, rope2d
 
 
 def rope_qk_(qkv: Tensor, coords: Tensor, coord_high: float, num_cls: int = 0, theta: float = 10000.0) -> None:
@@ -87,12 +88,26 @@ class DeepSeekSparseAttention(nn.Module):
         # [q | k | v] outermost, then head, then head-dim; the kernels take the
         # (B, H, T, D) views as they are (strided), no contiguous copies.
         qkv = self.qkv_proj(x).view(B, T, 3, H, D)
+        if coords is not None and coord_high is None:
+            raise ValueError("coords need coord_high (the coordinate that maps to one radian per unit frequency)")
+        q_idx, k_idx = self.indexer_proj(x)
+        if torch.is_grad_enabled() and (qkv.requires_grad or q_idx.requires_grad or
+                                        self.indexer_head_weights.requires_grad):
+            # training: one differentiable op (fused forward, the two backward kernels chained)
+            qt, kt, vt = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]            # (B, T, H, D)
+            if coords is not None:
+                if B != 1:
+                    raise ValueError("2-D RoPE handles one slide at a time (batch 1), like the reference")
+                c = coords.reshape(-1, 2).to(torch.float32)
+                c = torch.cat([c.new_zeros((num_cls, 2)), c], dim=0) if num_cls else c
+                qt = Rope2dFunction.apply(qt, c, coord_high, rope_theta, num_cls)
+                kt = Rope2dFunction.apply(kt, c, coord_high, rope_theta, num_cls)
+            o = DSAModuleFunction.apply(qt.transpose(1, 2), kt.transpose(1, 2), vt.transpose(1, 2), q_idx, k_idx,
+                                        self.indexer_head_weights, self.top_k, x.dtype)
+            return self.out_proj(o.transpose(1, 2).reshape(B, T, H * D).to(x.dtype))
         if coords is not None:
-            if coord_high is None:
-                raise ValueError("coords need coord_high (the coordinate that maps to one radian per unit frequency)")
             rope_qk_(qkv, coords, coord_high, num_cls, rope_theta)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
-        q_idx, k_idx = self.indexer_proj(x)
         o = dsa_sparse_attention(q, k, v, q_idx, k_idx, self.indexer_head_weights, self.top_k, out_dtype=x.dtype)
         return self.out_proj(o.transpose(1, 2).reshape(B, T, H * D).to(x.dtype))
 

@@ -7,7 +7,7 @@ Mirrors  src/sparse_wsi_vit/models/deepseek_sparse_attention_kernels/kernels.py
 and the op sequence of DeepSeekSparseAttention.forward
   (src/sparse_wsi_vit/models/deepseek_sparse_attention.py:59-85) -> dsa_sparse_attention.
 
-Forward only.  All work runs on the current CUDA stream of the inputs' device.
+Forward and backward.  All work runs on the current CUDA stream of the inputs' device.
 """
 from __future__ import annotations
 
@@ -215,6 +215,64 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
     return (o, idx, valid, scores) if return_topk else o
 
 
+def dsa_attention_bwd(d_out, q, k, v, o, idx, valid, rw):
+    """Gradients of the routing-weighted attention (kernels.py:569-762): returns fp32
+    ``dq (B,H,Tq,D), dk, dv (B,H,Tk,D), drw (B,Tq,top_k)``."""
+    _require_cuda(d_out, q, k, v, o, idx, valid, rw)
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    top_k = idx.shape[-1]
+    if k.dtype != q.dtype or v.dtype != q.dtype:
+        k, v = k.to(q.dtype), v.to(q.dtype)
+    k = k if k.stride(-1) == 1 else k.contiguous()
+    v = v if v.stride(-1) == 1 else v.contiguous()
+    d_out = d_out if d_out.dtype == o.dtype else d_out.to(o.dtype)
+    idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
+    valid, rw = valid.to(torch.float32), rw.detach().to(torch.float32)
+    dev = q.device
+    dq = torch.empty((B, H, Tq, D), dtype=torch.float32, device=dev)
+    dk = torch.empty((B, H, Tk, D), dtype=torch.float32, device=dev)
+    dv = torch.empty((B, H, Tk, D), dtype=torch.float32, device=dev)
+    drw = torch.empty((B, Tq, top_k), dtype=torch.float32, device=dev)
+    rc = lib.swv_dsa_attn_bwd(
+        d_out.data_ptr(), strides(d_out), q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v),
+        dtype_code(q.dtype), o.data_ptr(), strides(o), dtype_code(o.dtype), idx.data_ptr(), strides(idx),
+        valid.data_ptr(), strides(valid), rw.data_ptr(), strides(rw), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+        drw.data_ptr(), B, H, Tq, Tk, D, top_k, status_word(dev).data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_attn_bwd")
+    if _CHECK:
+        check_status(dev, "swv_dsa_attn_bwd")
+    return dq, dk, dv, drw
+
+
+def dsa_indexer_bwd(d_scores, q_idx, k_idx, w, idx, valid):
+    """Gradients of the indexer as the reference's backward defines them (kernels.py:128-339): returns
+    fp32 ``dq_idx (B,Tq,IH,ID), dk_idx (B,Tk,IH,ID), dw (IH,)``."""
+    _require_cuda(d_scores, q_idx, k_idx, w, idx, valid)
+    B, Tq, IH, ID = q_idx.shape
+    Tk = k_idx.shape[1]
+    top_k = idx.shape[-1]
+    if k_idx.dtype != q_idx.dtype:
+        k_idx = k_idx.to(q_idx.dtype)
+    d_scores = d_scores.to(torch.float32)
+    idx = idx if idx.dtype == torch.int32 else idx.to(torch.int32)
+    valid = valid.to(torch.float32)
+    w32 = w.detach().to(torch.float32).contiguous()
+    dev = q_idx.device
+    dq = torch.empty((B, Tq, IH, ID), dtype=torch.float32, device=dev)
+    dk = torch.empty((B, Tk, IH, ID), dtype=torch.float32, device=dev)
+    dw = torch.empty((IH,), dtype=torch.float32, device=dev)
+    rc = lib.swv_dsa_indexer_bwd(
+        d_scores.data_ptr(), strides(d_scores), q_idx.data_ptr(), strides(q_idx), k_idx.data_ptr(), strides(k_idx),
+        dtype_code(q_idx.dtype), w32.data_ptr(), idx.data_ptr(), strides(idx), valid.data_ptr(), strides(valid),
+        dq.data_ptr(), dk.data_ptr(), dw.data_ptr(), B, Tq, Tk, IH, ID, top_k, status_word(dev).data_ptr(),
+        _stream(dev))
+    check(rc, "swv_dsa_indexer_bwd")
+    if _CHECK:
+        check_status(dev, "swv_dsa_indexer_bwd")
+    return dq, dk, dw
+
+
 class LightningIndexerFunction(torch.autograd.Function):
     """Same positional signature as the reference (kernels.py:346-352).  The tile
     sizes are accepted and ignored; outputs are allocated here (kernels.py:355-357)."""
@@ -226,11 +284,17 @@ class LightningIndexerFunction(torch.autograd.Function):
             raise SwvError(f"q_proj has shape {tuple(q_proj.shape)}, expected {(B, T, H, D)}")
         idx, valid, scores = dsa_indexer_topk(q_proj.detach(), k_proj.detach(), W.detach(), TOP_K)
         ctx.mark_non_differentiable(idx, valid)
+        ctx.save_for_backward(q_proj, k_proj, W, idx, valid)
         return idx, valid, scores
 
     @staticmethod
-    def backward(ctx, *grads):
-        raise NotImplementedError("sparse_wsi_vit_b200 implements the forward path only")
+    def backward(ctx, d_idx, d_valid, d_scores):
+        """kernels.py:388-445: gradients for q_proj, k_proj, W; none for the sizes and tile arguments."""
+        q_proj, k_proj, W, idx, valid = ctx.saved_tensors
+        if d_scores is None:
+            d_scores = torch.zeros_like(valid)
+        dq, dk, dw = dsa_indexer_bwd(d_scores, q_proj, k_proj, W, idx, valid)
+        return (dq.to(q_proj.dtype), dk.to(k_proj.dtype), dw.to(W.dtype)) + (None,) * 9
 
 
 class DSAAttentionFunction(torch.autograd.Function):
@@ -244,11 +308,56 @@ class DSAAttentionFunction(torch.autograd.Function):
             raise SwvError(f"q has shape {tuple(q.shape)}, expected {(B, H, T, D)}")
         dsa_attention_gather(q.detach(), k.detach(), v.detach(), idx, valid, routing_weights.detach(), o)
         ctx.mark_dirty(o)
+        ctx.save_for_backward(q, k, v, idx, valid, routing_weights, o)
         return o
 
     @staticmethod
-    def backward(ctx, *grads):
-        raise NotImplementedError("sparse_wsi_vit_b200 implements the forward path only")
+    def backward(ctx, d_out):
+        """kernels.py:812-853: gradients for q, k, v and the routing weights."""
+        q, k, v, idx, valid, rw, o = ctx.saved_tensors
+        dq, dk, dv, drw = dsa_attention_bwd(d_out, q, k, v, o, idx, valid, rw)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None, drw.to(rw.dtype), None) + (None,) * 9
+
+
+class DSAModuleFunction(torch.autograd.Function):
+    """The module's whole attention step as ONE differentiable op: the forward is the fused path
+    (indexer + top-k + dense tensor-core attention, ``dsa_sparse_attention``), the backward chains
+    the two backward kernels the way autograd chains the reference's two Functions through
+    ``routing_weights = scores * valid`` (deepseek_sparse_attention.py:63-85)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, q_idx, k_idx, w, top_k, out_dtype):
+        o, idx, valid, scores = dsa_sparse_attention(q.detach(), k.detach(), v.detach(), q_idx.detach(),
+                                                     k_idx.detach(), w.detach(), top_k, out_dtype=out_dtype,
+                                                     return_topk=True)
+        ctx.save_for_backward(q, k, v, q_idx, k_idx, w, idx, valid, scores, o)
+        return o
+
+    @staticmethod
+    def backward(ctx, d_out):
+        q, k, v, q_idx, k_idx, w, idx, valid, scores, o = ctx.saved_tensors
+        dq, dk, dv, drw = dsa_attention_bwd(d_out.contiguous(), q, k, v, o, idx, valid, scores * valid)
+        # d scores = d rw * valid; the indexer backward multiplies by valid itself (valid is 0 or 1)
+        dqi, dki, dw = dsa_indexer_bwd(drw, q_idx, k_idx, w, idx, valid)
+        return (dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), dqi.to(q_idx.dtype), dki.to(k_idx.dtype),
+                dw.to(w.dtype), None, None)
+
+
+class Rope2dFunction(torch.autograd.Function):
+    """``rope2d`` with its gradient: the rotation is orthogonal, so the gradient of the input is the
+    upstream gradient turned by the opposite angles (the same kernel on negated coordinates)."""
+
+    @staticmethod
+    def forward(ctx, x, coords, coord_high, theta, skip_tokens):
+        ctx.save_for_backward(coords)
+        ctx.cfg = (coord_high, theta, skip_tokens)
+        return rope2d(x.detach(), coords, coord_high, theta, skip_tokens)
+
+    @staticmethod
+    def backward(ctx, g):
+        (coords,) = ctx.saved_tensors
+        coord_high, theta, skip_tokens = ctx.cfg
+        return rope2d(g.contiguous(), -coords, coord_high, theta, skip_tokens), None, None, None, None
 
 
 # --------------------------------------------------------------------------- #

@@ -126,7 +126,6 @@ def test_product_code_never_touches_the_oracle():
         for f in files:
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
-                assert "oracle" not in text.replace("oracle/", "oracle/") or "import oracle" not in text, f
                 assert "from oracle" not in text and "import oracle" not in text, f
 
 
@@ -149,6 +148,13 @@ def test_modules_keep_reference_parameter_names(swv, golden_dir):
         swv.DSAViTSlideEncoder(embed_dim=100, num_heads=3)
 
 
-def test_forward_only(swv):
-    with pytest.raises(NotImplementedError):
-        swv.LightningIndexerFunction.backward(None, None, None, None)
+def test_backward_has_no_cpu_path(swv):
+    """The backward operators are CUDA kernels like the forward ones: CPU tensors are refused."""
+    z = torch.zeros(1, 4, 2, 8)
+    i = torch.zeros(1, 4, 2, dtype=torch.int32)
+    f = torch.zeros(1, 4, 2)
+    with pytest.raises(swv._lib.SwvError):
+        swv.ops.dsa_indexer_bwd(f, z, z, torch.ones(2), i, f)
+    with pytest.raises(swv._lib.SwvError):
+        swv.ops.dsa_attention_bwd(z.transpose(1, 2), z.transpose(1, 2), z.transpose(1, 2), z.transpose(1, 2),
+                                  z.transpose(1, 2), i, f, f)

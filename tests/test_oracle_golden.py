@@ -131,3 +131,50 @@ def test_block_sparse_oracle_is_dense_under_full_list():
     o = S.block_sparse_attention(q, k, v, row_ptr, col, 32)
     ref = torch.nn.functional.scaled_dot_product_attention(q[None], k[None], v[None])[0]
     assert torch.allclose(o, ref, atol=1e-5)
+
+
+@pytest.mark.parametrize("case", ["bwd_rand", "bwd_batch2", "bwd_short"])
+def test_backward_restatements_match_reference_gradients(golden_dir, case):
+    """The oracle's backward formulas against gradients produced by the reference's own backward
+    kernels (Triton interpreter, fixtures from make_golden.py): attention dq/dk/dv/d(routing
+    weights) and the indexer's dq/dk/dW, fed with the routing-weight gradient the reference itself
+    propagated."""
+    import numpy as np
+    g = np.load(os.path.join(golden_dir, "dsa_bwd_reference.npz"))
+    B, T, H, D, IH, ID, K = [int(x) for x in g[f"{case}.dims"]]
+    t = lambda n: torch.from_numpy(g[f"{case}.{n}"])
+    dw_sum = torch.zeros(IH)
+    for b in range(B):
+        rw = (t("scores") * t("valid"))[b]
+        dq, dk, dv, drw = O.dsa_attention_bwd(t("d_out")[b], t("q")[b], t("k")[b], t("v")[b], t("o")[b], t("idx")[b],
+                                              t("valid")[b], rw)
+        for mine, name in ((dq, "dq"), (dk, "dk"), (dv, "dv"), (drw, "drw")):
+            ref = t(name)[b]
+            assert (mine - ref).abs().max() <= 2e-5 * max(1.0, float(ref.abs().max())), (case, name)
+        dqi, dki, dw = O.indexer_bwd(t("drw")[b] * t("valid")[b], t("qi")[b], t("ki")[b], t("w"), t("idx")[b],
+                                     t("valid")[b])
+        assert (dqi - t("dqi")[b]).abs().max() <= 1e-5 * max(1.0, float(t("dqi").abs().max()))
+        assert (dki - t("dki")[b]).abs().max() <= 1e-5 * max(1.0, float(t("dki").abs().max()))
+        dw_sum += dw
+    assert (dw_sum - t("dw")).abs().max() <= 1e-4 * max(1.0, float(t("dw").abs().max()))
+
+
+def test_attention_backward_is_the_gradient_of_the_forward():
+    """Off the 1e-6 clamp the reference's hand-written attention backward equals autograd through
+    the forward restatement."""
+    g = torch.Generator().manual_seed(3)
+    H, T, D, K = 2, 20, 8, 6
+    q = torch.randn(H, T, D, generator=g, dtype=torch.float64).requires_grad_()
+    k = torch.randn(H, T, D, generator=g, dtype=torch.float64).requires_grad_()
+    v = torch.randn(H, T, D, generator=g, dtype=torch.float64).requires_grad_()
+    idx = torch.stack([torch.randperm(T, generator=g)[:K] for _ in range(T)]).to(torch.int32)
+    valid = torch.ones(T, K)
+    valid[:, -1] = 0
+    rw = torch.rand(T, K, generator=g, dtype=torch.float64).requires_grad_()
+    d_out = torch.randn(H, T, D, generator=g, dtype=torch.float64)
+    o = O.dsa_attention(q, k, v, idx, valid, rw * valid, dtype=torch.float64)
+    (o * d_out).sum().backward()
+    dq, dk, dv, drw = O.dsa_attention_bwd(d_out, q.detach(), k.detach(), v.detach(), o.detach(), idx, valid,
+                                          (rw * valid).detach(), dtype=torch.float64)
+    assert torch.allclose(dq, q.grad, atol=1e-10) and torch.allclose(dk, k.grad, atol=1e-10)
+    assert torch.allclose(dv, v.grad, atol=1e-10) and torch.allclose(drw * valid, rw.grad, atol=1e-10)
