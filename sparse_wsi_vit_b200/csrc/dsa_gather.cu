@@ -141,6 +141,197 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
   }
 }
 
+// ------------------------------------------------------- 16-bit fast path
+// bf16 / fp16 q, k, v with unit inner stride and 16-byte aligned rows, D in {32, 64, 128}.
+// One CTA per (batch, query) and up to eight heads, one warp per head: the row of idx / valid /
+// rw is read ONCE for all heads (256 slots at a time through shared memory).  A lane owns a
+// slot: it reads that key's row with 16-byte loads and accumulates the dot product with
+// mixed-precision FMAs (bf16 x bf16 products are exact in fp32), then reads the value row and
+// adds p * v into its OWN fp32 accumulators (p split into two 16-bit halves so that the
+// products stay exact to 2^-17); the 32 partial output rows are folded once at the end.  The
+// running maximum is exact (the accumulators are rescaled whenever it rises, a handful of times
+// per row).  Every selected row crosses the L2 -> SM path once per head: 2 * top_k * D * 2 bytes
+// per (query, head), one byte per FLOP -- the bound of this operator.
+template <bool BF16>
+__device__ __forceinline__ void fma_mixed2(float& acc0, float& acc1, uint32_t a, uint32_t b) {
+  if (BF16) {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\tmov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.bf16 %0, al, bl, %0;\n\tfma.rn.f32.bf16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(a), "r"(b));
+  } else {
+    asm("{\n\t.reg .b16 al, ah, bl, bh;\n\tmov.b32 {al, ah}, %2;\n\tmov.b32 {bl, bh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, al, bl, %0;\n\tfma.rn.f32.f16 %1, ah, bh, %1;\n\t}"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(a), "r"(b));
+  }
+}
+// x as (hi, lo) with hi = x rounded to 16 bits and lo = the rounded remainder, both halves of one
+// word duplicated: {hi, hi} and {lo, lo}
+template <bool BF16>
+__device__ __forceinline__ void split16(float x, uint32_t& hi2, uint32_t& lo2) {
+  if (BF16) {
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    const __nv_bfloat16 l = __float2bfloat16_rn(x - __bfloat162float(h));
+    const uint32_t hb = __bfloat16_as_ushort(h), lb = __bfloat16_as_ushort(l);
+    hi2 = hb | (hb << 16);
+    lo2 = lb | (lb << 16);
+  } else {
+    const __half h = __float2half_rn(x);
+    const __half l = __float2half_rn(x - __half2float(h));
+    const uint32_t hb = __half_as_ushort(h), lb = __half_as_ushort(l);
+    hi2 = hb | (hb << 16);
+    lo2 = lb | (lb << 16);
+  }
+}
+
+constexpr int kRowsSlots = 256;      // slots staged per round
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(256) dsa_attn_gather_rows_kernel(const GatherParams p) {
+  constexpr int W = D / 2;           // 32-bit words per row
+  __shared__ int s_idx[kRowsSlots];
+  __shared__ float s_w[kRowsSlots];  // routing weight (s_idx < 0 marks a slot that is not valid)
+  __shared__ uint4 s_q[8][W / 4];
+  const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nwarps = blockDim.x >> 5;
+  const int qi = blockIdx.x % p.Tq;
+  const int b = blockIdx.x / p.Tq;
+  const int h = blockIdx.y * nwarps + wib;
+  const bool head_ok = h < p.H;
+  const uint16_t* q16 = static_cast<const uint16_t*>(p.q);
+  const uint16_t* k16 = static_cast<const uint16_t*>(p.k);
+  const uint16_t* v16 = static_cast<const uint16_t*>(p.v);
+  if (head_ok) {
+    const uint4* qrow = reinterpret_cast<const uint4*>(q16 + b * p.qs[0] + h * p.qs[1] + qi * p.qs[2]);
+    if (lane < W / 4) s_q[wib][lane] = __ldg(qrow + lane);
+  }
+  const int hk = head_ok ? h / p.kv_group : 0;
+  const uint16_t* kbase = k16 + b * p.ks[0] + hk * p.ks[1];
+  const uint16_t* vbase = v16 + b * p.vs[0] + hk * p.vs[1];
+  const int32_t* idx_row = p.idx + b * p.is[0] + qi * p.is[1];
+  const float* val_row = p.valid + b * p.vls[0] + qi * p.vls[1];
+  const float* rw_row = p.rw + b * p.rs[0] + qi * p.rs[1];
+  const float ninf = -__int_as_float(0x7f800000);
+
+  float o[D];
+#pragma unroll
+  for (int i = 0; i < D; ++i) o[i] = 0.f;
+  float m = ninf, l = 0.f;
+
+  for (int base = 0; base < p.top_k; base += kRowsSlots) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < kRowsSlots; i += blockDim.x) {
+      const int slot = base + i;
+      int id = -1;
+      float w = 0.f;
+      if (slot < p.top_k && val_row[slot * p.vls[2]] > 0.f) {
+        id = idx_row[slot * p.is[2]];
+        w = rw_row[slot * p.rs[2]];
+        if (id < 0 || id >= p.Tk) {
+          // a valid slot that names no key: reported through the status word, the slot is dropped
+          record_status(p.status, kDevBadIndex);
+          id = -1;
+        }
+      }
+      s_idx[i] = id;
+      s_w[i] = w;
+    }
+    __syncthreads();
+    if (!head_ok) continue;
+    const int n_here = min(kRowsSlots, p.top_k - base);
+    for (int c0 = 0; c0 < n_here; c0 += 32) {
+      const int id = s_idx[c0 + lane];
+      const float w = s_w[c0 + lane];
+      const bool ok = id >= 0;
+      float logit = ninf;
+      if (ok) {
+        const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<int64_t>(id) * p.ks[2]);
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int i = 0; i < W / 4; ++i) {
+          const uint4 kv = __ldg(kr + i);
+          const uint4 qv = s_q[wib][i];
+          fma_mixed2<BF16>(a0, a1, qv.x, kv.x);
+          fma_mixed2<BF16>(a0, a1, qv.y, kv.y);
+          fma_mixed2<BF16>(a0, a1, qv.z, kv.z);
+          fma_mixed2<BF16>(a0, a1, qv.w, kv.w);
+        }
+        logit = (a0 + a1) * p.scale;
+      }
+      float cmax = logit;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, off));
+      if (cmax > m) {                                    // warp-uniform
+        if (m != ninf) {
+          const float f = __expf(m - cmax);
+          l *= f;
+#pragma unroll
+          for (int i = 0; i < D; ++i) o[i] *= f;
+        }
+        m = cmax;
+      }
+      const float pj = ok ? __expf(logit - m) * w : 0.f;
+      if (pj != 0.f) {
+        l += pj;
+        uint32_t ph, pl;
+        split16<BF16>(pj, ph, pl);
+        const uint4* vr = reinterpret_cast<const uint4*>(vbase + static_cast<int64_t>(id) * p.vs[2]);
+#pragma unroll
+        for (int i = 0; i < W / 4; ++i) {
+          const uint4 vv = __ldg(vr + i);
+          const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            fma_mixed2<BF16>(o[i * 8 + 2 * c], o[i * 8 + 2 * c + 1], ph, vw[c]);
+            fma_mixed2<BF16>(o[i * 8 + 2 * c], o[i * 8 + 2 * c + 1], pl, vw[c]);
+          }
+        }
+      }
+    }
+  }
+  if (!head_ok) return;
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
+  // fold the 32 partial rows: after the step with stride s a lane keeps the half of its channels
+  // selected by that bit of its index; lane L ends with channels [L * D/32, (L+1) * D/32)
+#pragma unroll
+  for (int s = 16, n = D / 2; s >= 1; s >>= 1, n >>= 1) {
+    const bool up = (lane & s) != 0;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const float send = up ? o[i] : o[i + n];
+      const float keep = up ? o[i + n] : o[i];
+      o[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+    }
+  }
+  const float inv = 1.f / fmaxf(l, 1e-6f);
+  constexpr int PER = D / 32;
+  const int64_t obase = b * p.os[0] + h * p.os[1] + qi * p.os[2];
+#pragma unroll
+  for (int i = 0; i < PER; ++i) st_out(p.o, p.o_dtype, obase + (lane * PER + i) * p.os[3], o[i] * inv);
+}
+
+static bool rows_path_ok(const GatherParams& p, int dtype, int D) {
+  if (dtype == SWV_F32 || (D != 32 && D != 64 && D != 128)) return false;
+  auto a16 = [](const void* x) { return (reinterpret_cast<uintptr_t>(x) & 15) == 0; };
+  if (!a16(p.q) || !a16(p.k) || !a16(p.v)) return false;
+  if (p.qs[3] != 1 || p.ks[3] != 1 || p.vs[3] != 1) return false;
+  for (int i = 0; i < 3; ++i)
+    if ((p.qs[i] * 2) % 16 || (p.ks[i] * 2) % 16 || (p.vs[i] * 2) % 16) return false;
+  return true;
+}
+
+template <bool BF16>
+static int launch_gather_rows(const GatherParams& p, int D, cudaStream_t st) {
+  const int warps = p.H < 8 ? p.H : 8;
+  const dim3 grid(static_cast<unsigned>(p.B) * p.Tq, static_cast<unsigned>((p.H + warps - 1) / warps));
+  if (D == 32) dsa_attn_gather_rows_kernel<32, BF16><<<grid, 32 * warps, 0, st>>>(p);
+  else if (D == 64) dsa_attn_gather_rows_kernel<64, BF16><<<grid, 32 * warps, 0, st>>>(p);
+  else dsa_attn_gather_rows_kernel<128, BF16><<<grid, 32 * warps, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? SWV_OK : SWV_ERR_CUDA;
+}
+
 template <typename T>
 static int launch_gather(const GatherParams& p, int D, cudaStream_t st) {
   const int64_t total = static_cast<int64_t>(p.B) * p.H * p.Tq;
@@ -172,6 +363,8 @@ int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const 
   p.B = B; p.H = H; p.Tq = Tq; p.Tk = Tk; p.D = D; p.top_k = top_k; p.kv_group = kv_group;
   p.scale = 1.0f / sqrtf(static_cast<float>(D));
   p.status = status;
+  if (rows_path_ok(p, dtype, D))
+    return dtype == SWV_BF16 ? launch_gather_rows<true>(p, D, st) : launch_gather_rows<false>(p, D, st);
   if (dtype == SWV_F32) return launch_gather<float>(p, D, st);
   if (dtype == SWV_BF16) return launch_gather<__nv_bfloat16>(p, D, st);
   return launch_gather<__half>(p, D, st);

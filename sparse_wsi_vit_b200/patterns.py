@@ -40,6 +40,29 @@ def static_window_blocks(seq_len: int, num_cls: int, window: int, dilation: int,
     return _to_csr(rows)
 
 
+def static_window_lists(seq_len: int, num_cls: int, window: int, dilation: int):
+    """Explicit key lists of the PATCH rows of the reference's static pattern
+    (static_sparse_attention.py:105-188): for patch row i (token num_cls + i) the CLS keys followed
+    by the window keys i - W*d ... i + W*d step d, out-of-range neighbours marked invalid (they are
+    masked, not wrapped, :159-168).  Returns (idx int32, valid float32), each (1, n_patches, C + 2W + 1)
+    with token indices (patch position + num_cls).  With window 0 a patch sees the CLS keys only."""
+    n = seq_len - num_cls
+    width = num_cls + (2 * window + 1 if window > 0 else 0)
+    idx = np.zeros((1, max(n, 0), max(width, 1)), dtype=np.int32)
+    valid = np.zeros((1, max(n, 0), max(width, 1)), dtype=np.float32)
+    if n <= 0:
+        return idx, valid
+    if num_cls > 0:
+        idx[0, :, :num_cls] = np.arange(num_cls, dtype=np.int32)[None, :]
+        valid[0, :, :num_cls] = 1.0
+    if window > 0:
+        pos = np.arange(n)[:, None] + (np.arange(-window, window + 1) * dilation)[None, :]
+        ok = (pos >= 0) & (pos < n)
+        idx[0, :, num_cls:] = np.where(ok, pos + num_cls, 0).astype(np.int32)
+        valid[0, :, num_cls:] = ok.astype(np.float32)
+    return idx, valid
+
+
 def chebyshev_grid_blocks(grid_h: int, grid_w: int, radius: int = 1, global_blocks=()):
     """2-D pattern: the tokens of one block are one spatial tile; block (r, c) has index r*grid_w + c.
     Every block attends the blocks within Chebyshev distance `radius` plus the `global_blocks`

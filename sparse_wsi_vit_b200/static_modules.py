@@ -3,8 +3,10 @@
 Constructor arguments, forward signatures and parameter names follow
 src/sparse_wsi_vit/models/static_sparse_attention.py (StaticSparseAttention :11-103,
 StaticSparseViTBlock :191-236, StaticSparseViTSlideEncoder :239-345).  The attention runs on the
-block-sparse tensor-core kernel with the reference's token pattern applied inside the blocks the
-pattern touches, instead of the reference's dense (N, N*ctx) masked SDPA.  Forward only; attention
+block-sparse tensor-core kernel (bf16 / fp16 activations, e.g. under autocast) with the reference's
+token pattern applied inside the blocks the pattern touches, or -- for fp32 activations -- on the
+exact list kernel over the pattern's explicit key lists, instead of the reference's dense
+(N, N*ctx) masked SDPA.  Forward only; attention
 dropout is not applied (the reference applies it in training mode only).
 
 ``BlockSparseAttention2D`` is the 2-D block pattern with optional 2-D RoPE the target asks for; the
@@ -16,8 +18,8 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
-from .ops import block_sparse_attention, rope2d
-from .patterns import static_window_blocks
+from .ops import block_sparse_attention, dsa_attention_gather, rope2d
+from .patterns import static_window_blocks, static_window_lists
 
 _BLOCK = 128
 
@@ -44,11 +46,38 @@ class StaticSparseAttention(nn.Module):
             self._lists[key] = (torch.from_numpy(rp).to(device), torch.from_numpy(ci).to(device))
         return self._lists[key]
 
+    def _key_lists(self, seq_len, device):
+        key = ("lists", seq_len, device)
+        if key not in self._lists:
+            idx_p, val_p = static_window_lists(seq_len, self.num_cls, self.window_size, self.dilation)
+            self._lists[key] = (torch.from_numpy(idx_p).to(device), torch.from_numpy(val_p).to(device))
+        return self._lists[key]
+
+    def _forward_fp32(self, q, k, v):
+        """fp32 inputs keep fp32 arithmetic: the pattern is small explicit key lists (the CLS keys and
+        the 2W+1 window keys of every patch row; all keys for the CLS rows), so the exact CUDA-core
+        list kernel serves it (softmax weights 1).  Within 1e-4 of the reference's fp32 module."""
+        B, H, L, D = q.shape
+        C = self.num_cls
+        o = torch.empty((B, H, L, D), dtype=q.dtype, device=q.device)
+        if C > 0:
+            idx_c = torch.arange(L, dtype=torch.int32, device=q.device).expand(B, C, L)
+            ones = torch.ones((1, 1, 1), device=q.device).expand(B, C, L)
+            dsa_attention_gather(q[:, :, :C], k, v, idx_c, ones, ones, o[:, :, :C])
+        if L > C:
+            idx_p, val_p = self._key_lists(L, q.device)
+            idx_p, val_p = idx_p.expand(B, -1, -1), val_p.expand(B, -1, -1)
+            dsa_attention_gather(q[:, :, C:], k, v, idx_p, val_p, val_p, o[:, :, C:])
+        return o
+
     def forward(self, x: Tensor) -> Tensor:
         B, L, E = x.shape
         H, D = self.num_heads, self.head_dim
         qkv = self.qkv(x).view(B, L, 3, H, D)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        if qkv.dtype == torch.float32:
+            o = self._forward_fp32(q, k, v)
+            return self.out_proj(o.transpose(1, 2).reshape(B, L, E))
         rp, ci = self._block_list(L, x.device)
         o = block_sparse_attention(q, k, v, rp, ci, _BLOCK, mode=1, num_cls=self.num_cls, window=self.window_size,
                                    dilation=self.dilation, out_dtype=x.dtype)

@@ -33,16 +33,16 @@ def test_nsa_vs_oracle(T, Hq, Hkv, D, topk, window):
 def _compare(Hq, Hkv, out, o_cmp, o_sel, o_win, blocks, ref, r_cmp, r_sel, r_win, r_blocks, margin):
     """The oracle pools from the same bf16-rounded values as the library, so the block importances
     agree to fp32 round-off: the selected blocks must be IDENTICAL on every row whose last selected
-    and first rejected importance differ by more than 1e-4 relative (a smaller gap is a near-tie
+    and first rejected importance differ by more than 1e-5 relative (ten times the fp32 round-off of the sums) (a smaller gap is a near-tie
     that another summation order may legitimately break the other way), and such near-tie rows
     must be rare."""
     tol = dict(atol=3e-2, rtol=0)
     assert torch.allclose(o_cmp, r_cmp, **tol)
     assert torch.allclose(o_win, r_win, **tol)
     same = (blocks.long() == r_blocks).all(dim=-1)                     # (Hkv, R)
-    clear = margin > 1e-4
+    clear = margin > 1e-5
     assert bool(same[clear].all()), f"{int((~same & clear).sum())} rows with a clear margin selected other blocks"
-    assert clear.float().mean() > 0.95
+    assert clear.float().mean() > 0.9
     rows = same.repeat_interleave(Hq // Hkv, dim=0)                    # (Hq, R)
     assert (o_sel - r_sel)[rows].abs().max() < 3e-2
     assert (out - ref)[rows].abs().max() < 3e-2

@@ -39,3 +39,18 @@ def test_band_random_blocks_are_seeded_and_contain_band_and_global():
         assert 0 in row and all(x in row for x in range(max(0, qb - 2), min(64, qb + 3)))
     dense = S.expand_block_mask(rp, ci, 4, 256, 256)
     assert 0.08 < float(dense.float().mean()) < 0.2
+
+
+def test_static_window_lists_equal_the_reference_mask():
+    """The explicit per-row key lists (used for fp32 activations) name exactly the keys the
+    reference's static pattern lets every patch row see."""
+    from sparse_wsi_vit_b200.patterns import static_window_lists
+    for (L, C, W, d) in [(37, 2, 3, 2), (20, 1, 0, 1), (50, 3, 5, 1), (9, 0, 2, 1), (12, 2, 4, 3)]:
+        idx, val = static_window_lists(L, C, W, d)
+        mask = S.static_window_mask(L, C, W, d)
+        got = torch.zeros(L - C, L, dtype=torch.bool)
+        for i in range(L - C):
+            keys = idx[0, i][val[0, i] > 0]
+            assert len(set(keys.tolist())) == len(keys)          # no key listed twice
+            got[i, torch.from_numpy(keys).long()] = True
+        assert torch.equal(got, mask[C:]), (L, C, W, d)
