@@ -1,7 +1,7 @@
 """Benchmark of the DSA sparse-attention forward (indexer + top-k + attention).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--tokens T]
-    python bench.py --workload {block_sparse,nsa,encoder,static}     # other configurations, 1 GPU
+    python bench.py --workload {dsa_variants,block_sparse,nsa,encoder,static,static2d}     # other configurations
 
 Workload ("dsa_fwd_64k"): one DSA attention layer, 65536 tokens, 8 heads x 64,
 4 x 64 indexer, top-2048, bf16, batch 1, non-causal; seeded synthetic inputs with
@@ -505,15 +505,19 @@ def main():
                     "block_sparse / nsa: run only this size)")
     ap.add_argument("--reference-src", default=None, help="with --impl reference: `src` directory of a "
                     "sparse-wsi-vit checkout; its own Triton kernels are then timed too (interpreter, 1024 tokens)")
-    ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "block_sparse", "nsa", "encoder", "static"])
+    ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "dsa_variants", "block_sparse", "nsa", "encoder", "static", "static2d"])
     args = ap.parse_args()
     if args.workload != "dsa_fwd":
         from sparse_wsi_vit_b200.benchmarks import WORKLOADS
         kw = {}
-        if args.tokens is not None and args.workload == "block_sparse":
+        if args.tokens is not None and args.workload in ("block_sparse", "dsa_variants"):
             kw["sizes"] = (args.tokens,)
         elif args.tokens is not None and args.workload in ("nsa", "static"):
             kw["tokens"] = args.tokens
+        if args.workload == "static2d":
+            # the CPU baseline of this workload: the oracle's fp32 restatement, timed on the host cores
+            from oracle import encoder as E
+            kw["cpu_forward"] = lambda sd, x, c, rp, ci: E.block2d_encoder_forward(sd, x, c, rp, ci, 64, 2, 6, 1, 64.0)
         WORKLOADS[args.workload](**kw)
         return
     if args.tokens is None:

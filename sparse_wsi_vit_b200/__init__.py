@@ -8,13 +8,13 @@ from .ops import (DSAAttentionFunction, LightningIndexerFunction, check_status, 
                   dsa_attention_masked, dsa_indexer_topk, dsa_sparse_attention)
 from .ops import block_sparse_attention, rope2d
 from .modules import DeepSeekSparseAttention, DSAViTBlock, DSAViTSlideEncoder, IndexerProjection
-from .static_modules import (BlockSparseAttention2D, StaticSparseAttention, StaticSparseViTBlock,
-                             StaticSparseViTSlideEncoder)
+from .static_modules import (BlockSparse2DViTBlock, BlockSparse2DViTSlideEncoder, BlockSparseAttention2D,
+                             StaticSparseAttention, StaticSparseViTBlock, StaticSparseViTSlideEncoder)
 from . import patterns
 
 __all__ = [
     "DSAAttentionFunction", "LightningIndexerFunction", "check_status", "dsa_attention_gather",
     "dsa_attention_masked", "dsa_indexer_topk", "dsa_sparse_attention", "DeepSeekSparseAttention",
     "DSAViTBlock", "DSAViTSlideEncoder", "IndexerProjection", "block_sparse_attention", "rope2d", "patterns",
-    "BlockSparseAttention2D", "StaticSparseAttention", "StaticSparseViTBlock", "StaticSparseViTSlideEncoder",
+    "BlockSparseAttention2D", "BlockSparse2DViTBlock", "BlockSparse2DViTSlideEncoder", "StaticSparseAttention", "StaticSparseViTBlock", "StaticSparseViTSlideEncoder",
 ]

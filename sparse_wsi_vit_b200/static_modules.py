@@ -167,3 +167,69 @@ class BlockSparseAttention2D(nn.Module):
         o = block_sparse_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), row_ptr, col_idx,
                                    self.block, mode=0, out_dtype=x.dtype)
         return self.out_proj(o.transpose(1, 2).reshape(B, L, E))
+
+
+class BlockSparse2DViTBlock(nn.Module):
+    """The reference's pre-norm block (static_sparse_attention.py:191-236) around ``BlockSparseAttention2D``."""
+
+    def __init__(self, embed_dim: int, num_heads: int, block: int = 64, coord_high: float = 1.0, theta: float = 10000.0,
+                 expansion_factor: float = 4.0, proj_dropout: float = 0.0) -> None:
+        super().__init__()
+        hidden = int(embed_dim * expansion_factor)
+        self.norm1 = nn.LayerNorm(embed_dim)
+        self.attn = BlockSparseAttention2D(embed_dim, num_heads, block, coord_high, theta)
+        self.drop1 = nn.Dropout(proj_dropout)
+        self.norm2 = nn.LayerNorm(embed_dim)
+        self.mlp = nn.Sequential(nn.Linear(embed_dim, hidden), nn.GELU(), nn.Dropout(proj_dropout),
+                                 nn.Linear(hidden, embed_dim), nn.Dropout(proj_dropout))
+
+    def forward(self, x: Tensor, row_ptr: Tensor, col_idx: Tensor, coords: Tensor | None, num_global: int) -> Tensor:
+        x = x + self.drop1(self.attn(self.norm1(x), row_ptr, col_idx, coords, num_global))
+        return x + self.mlp(self.norm2(x))
+
+
+class BlockSparse2DViTSlideEncoder(nn.Module):
+    """Slide encoder over a 2-D block pattern: the skeleton of ``StaticSparseViTSlideEncoder`` (same
+    parameter names: cls_tokens, input_proj, blocks.i.{norm1, attn.qkv, attn.out_proj, norm2, mlp},
+    norm, cls_pool, head) with block-sparse attention and 2-D RoPE on the patch tokens.  The
+    reference has no such model; it is the composite the 4096-patch / 64x64-grid configuration asks
+    for.  Token order: patches first (block-major, one spatial tile per block), the CLS tokens in a
+    trailing global block.  ``pool``: "cls" = the reference's softmax-weighted CLS pooling, "mean" =
+    mean over the patch tokens."""
+
+    def __init__(self, in_features: int = 1280, out_features: int = 1, embed_dim: int = 384, num_heads: int = 6,
+                 num_layers: int = 2, num_cls: int = 1, block: int = 64, coord_high: float = 1.0,
+                 rope_theta: float = 10000.0, expansion_factor: float = 4.0, proj_dropout: float = 0.0,
+                 pool: str = "cls") -> None:
+        super().__init__()
+        if pool not in ("cls", "mean"):
+            raise ValueError(f"pool must be 'cls' or 'mean', got {pool!r}")
+        self.num_cls, self.embed_dim, self.out_features, self.block, self.pool = num_cls, embed_dim, out_features, block, pool
+        self.input_proj = nn.Linear(in_features, embed_dim)
+        self.cls_tokens = nn.Parameter(torch.zeros(1, num_cls, embed_dim))
+        nn.init.trunc_normal_(self.cls_tokens, std=0.02)
+        self.blocks = nn.ModuleList(
+            BlockSparse2DViTBlock(embed_dim, num_heads, block, coord_high, rope_theta, expansion_factor, proj_dropout)
+            for _ in range(num_layers))
+        self.norm = nn.LayerNorm(embed_dim)
+        self.cls_pool = nn.Linear(embed_dim, 1, bias=False)
+        self.head = nn.Linear(embed_dim, out_features)
+        nn.init.xavier_uniform_(self.input_proj.weight)
+        nn.init.zeros_(self.input_proj.bias)
+        nn.init.zeros_(self.head.bias)
+
+    def forward(self, x: Tensor, coords: Tensor, row_ptr: Tensor, col_idx: Tensor) -> dict[str, Tensor]:
+        """x (N, in_features) or (1, N, in_features); coords (N, 2); row_ptr / col_idx: the CSR key-block
+        list over the N + num_cls tokens (int32, on x's device)."""
+        if x.dim() == 2:
+            x = x.unsqueeze(0)
+        n = x.shape[1]
+        x = torch.cat([self.input_proj(x), self.cls_tokens.expand(x.shape[0], -1, -1).to(x.dtype)], dim=1)
+        for blk in self.blocks:
+            x = blk(x, row_ptr, col_idx, coords, self.num_cls)
+        x = self.norm(x)
+        if self.pool == "mean":
+            return {"logits": self.head(x[:, :n].mean(dim=1))}
+        cls = x[:, n:]
+        pooled = (torch.softmax(self.cls_pool(cls), dim=1) * cls).sum(dim=1)
+        return {"logits": self.head(pooled)}
