@@ -58,6 +58,23 @@ def _worker(rank, world, port, out):
             whole = enc(x)["logits"]
         swv.check_status(dev)
         assert torch.allclose(got.float(), whole.float(), atol=2e-2), (got, whole)
+
+        # ragged batch with 2-D RoPE: every slide split over both ranks == the same slides on one GPU;
+        # the 5-patch slide leaves rank 1 an empty shard, which still joins every collective
+        from sparse_wsi_vit_b200.dist import sharded_ragged_forward
+        torch.manual_seed(2)
+        renc = swv.DSAViTSlideEncoder(in_features=96, out_features=2, embed_dim=128, num_heads=2, num_layers=2,
+                                      num_cls=2, indexer_heads=4, indexer_dim=32, top_k=64,
+                                      rope_coord_high=224.0 * 64).to(dev).eval()
+        gg = torch.Generator().manual_seed(3)
+        slides = [torch.randn(n, 96, generator=gg).to(dev) for n in (900, 5, 1300)]
+        coords = [(torch.randint(0, 64, (s_.shape[0], 2), generator=gg) * 224).float().to(dev) for s_ in slides]
+        with torch.no_grad(), torch.autocast("cuda", dtype=torch.bfloat16):
+            sharded = sharded_ragged_forward(renc, slides, world, rank, coords=coords, comm_stream=comm)["logits"]
+            single = sharded_ragged_forward(renc, slides, 1, 0, coords=coords)["logits"]
+        swv.check_status(dev)
+        assert sharded.shape == (3, 2)
+        assert torch.allclose(sharded.float(), single.float(), atol=2e-2), (sharded, single)
         out[rank] = True
     finally:
         dist.destroy_process_group()
