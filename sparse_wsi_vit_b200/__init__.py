@@ -10,11 +10,11 @@ from .ops import block_sparse_attention, rope2d
 from .modules import DeepSeekSparseAttention, DSAViTBlock, DSAViTSlideEncoder, IndexerProjection
 from .static_modules import (BlockSparse2DViTBlock, BlockSparse2DViTSlideEncoder, BlockSparseAttention2D,
                              StaticSparseAttention, StaticSparseViTBlock, StaticSparseViTSlideEncoder)
-from . import patterns
+from . import ingest, patterns, training
 
 __all__ = [
     "DSAAttentionFunction", "LightningIndexerFunction", "check_status", "dsa_attention_gather",
     "dsa_attention_masked", "dsa_indexer_topk", "dsa_sparse_attention", "DeepSeekSparseAttention",
-    "DSAViTBlock", "DSAViTSlideEncoder", "IndexerProjection", "block_sparse_attention", "rope2d", "patterns",
+    "DSAViTBlock", "DSAViTSlideEncoder", "IndexerProjection", "block_sparse_attention", "rope2d", "patterns", "ingest", "training",
     "BlockSparseAttention2D", "BlockSparse2DViTBlock", "BlockSparse2DViTSlideEncoder", "StaticSparseAttention", "StaticSparseViTBlock", "StaticSparseViTSlideEncoder",
 ]

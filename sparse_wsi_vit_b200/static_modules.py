@@ -120,7 +120,10 @@ class StaticSparseViTSlideEncoder(nn.Module):
         nn.init.zeros_(self.input_proj.bias)
         nn.init.zeros_(self.head.bias)
 
-    def forward(self, x: Tensor) -> dict[str, Tensor]:
+    def forward(self, x: Tensor, coords=None) -> dict[str, Tensor]:
+        """``coords`` is accepted and ignored: the reference's wrapper calls ``network(inputs, coords)``
+        (experiments/lightning_wrappers/wsi_attn_wrapper.py:96) although this encoder, like the
+        reference's, has no positional term."""
         if x.dim() == 2:
             x = x.unsqueeze(0)
         x = self.input_proj(x)
