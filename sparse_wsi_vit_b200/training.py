@@ -29,9 +29,8 @@ def slide_step(network, batch, multiclass: bool = True, use_bce_loss: bool = Fal
         loss = F.binary_cross_entropy_with_logits(logits, labels.float(), reduction="none")
         preds = (torch.sigmoid(logits) >= 0.5).int()
     else:
-        loss = F.cross_entropy(logits, labels, reduction="none") if multiclass else \\
-            F.binary_cross_entropy_with_logits(logits, labels.float(), reduction="none")
-        preds = torch.argmax(logits, dim=-1) if multiclass else (logits >= 0).int()
+        loss = F.cross_entropy(logits, labels, reduction="none")
+        preds = torch.argmax(logits, dim=-1)
     if "class_weight" in batch:
         loss = loss * torch.as_tensor(batch["class_weight"], device=loss.device, dtype=loss.dtype)
     return loss.mean(), preds, logits
