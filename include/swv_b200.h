@@ -284,8 +284,9 @@ int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_w
  *   q (B,Hq,T,D), k, v (B,Hkv,T,D) bf16, unit inner stride, 16-byte aligned rows; D = 64 or 128;
  *   gate (B,T,Hq,3) fp32 contiguous, logits in the order [compressed, selected, window];
  *   out (B,Hq,T,D) contiguous in out_dtype;
- *   workspace: swv_nsa_workspace_bytes() bytes, 256-byte aligned (pooled keys / values, the three
- *   branch outputs in fp32, row statistics, block scores, key-block lists);
+ *   workspace: swv_nsa_workspace_bytes() bytes, 256-byte aligned (pooled keys / values, ONE fp32
+ *   accumulator of the gated branch sum -- every branch kernel applies its gate in its epilogue and
+ *   adds its rows to it, the last one writes `out` -- row statistics, block scores, key-block lists);
  *   blocks_out: optional (B,Hkv,T,min(n_sel, ceil(T/sel_block))) int32, the selected block ids.
  * Limits as for the entry points it is built from (Hq / Hkv <= 8, sel_block a multiple of 32 and of
  * cmp_stride with sel_block / cmp_stride in {1,2,4,8}).

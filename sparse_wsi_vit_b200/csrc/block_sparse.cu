@@ -37,6 +37,12 @@ struct BsaParams {
   int mode, num_cls, window, dilation;
   int kv_group;             // query heads per key/value head (grouped-query attention), >= 1
   float* lse;               // optional (B,H,Tq): natural-log sum of exponentials per row, -inf for empty rows
+  // Optional gated epilogue (the NSA branches): the rows are scaled by sigmoid(gate[b,t,h,gate_idx])
+  // (gate (B,Tq,H,3) fp32) and added to `acc_in` (fp32 contiguous (B,H,Tq,D), may be null) before
+  // they are written to `o`.
+  const float* gate;
+  int gate_idx;
+  const float* acc_in;
   void* o;
   int64_t osb, osh, ost;
   int o_dtype;
@@ -398,13 +404,28 @@ __global__ void __launch_bounds__(320, 1)
           for (int i = 0; i < 16; ++i) o[i] = 0u;
         }
         if (!row_ok) continue;
+        if (p.gate != nullptr) {
+          // gated accumulate: value = acc_in + sigmoid(g) * (o * inv), the order the stand-alone
+          // gate kernel adds the branches in
+          const float gl = p.gate[((static_cast<int64_t>(b) * p.Tq + qrow) * p.H + h) * 3 + p.gate_idx];
+          const float gs = 1.f / (1.f + __expf(-gl));
+          const float* arow = p.acc_in == nullptr ? nullptr
+                                                  : p.acc_in + ((static_cast<int64_t>(b) * p.H + h) * p.Tq + qrow) * D +
+                                                        half * DH + c * 16;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float a = __uint_as_float(o[i]) * inv;
+            o[i] = __float_as_uint(arow == nullptr ? gs * a : fmaf(gs, a, arow[i]));
+          }
+        }
+        const float inv_w = p.gate != nullptr ? 1.f : inv;      // (already applied above)
         if (p.o_dtype == SWV_F32) {
           float* orow = static_cast<float*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + half * DH + c * 16;
 #pragma unroll
           for (int i = 0; i < 16; i += 4) {
             *reinterpret_cast<float4*>(orow + i) =
-                make_float4(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv,
-                            __uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+                make_float4(__uint_as_float(o[i]) * inv_w, __uint_as_float(o[i + 1]) * inv_w,
+                            __uint_as_float(o[i + 2]) * inv_w, __uint_as_float(o[i + 3]) * inv_w);
           }
         } else {
           uint16_t* orow = static_cast<uint16_t*>(p.o) + b * p.osb + h * p.osh + qrow * p.ost + half * DH + c * 16;
@@ -413,7 +434,7 @@ __global__ void __launch_bounds__(320, 1)
             uint32_t w4[4];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              const float a0 = __uint_as_float(o[i + 2 * q]) * inv, a1 = __uint_as_float(o[i + 2 * q + 1]) * inv;
+              const float a0 = __uint_as_float(o[i + 2 * q]) * inv_w, a1 = __uint_as_float(o[i + 2 * q + 1]) * inv_w;
               if (p.o_dtype == SWV_BF16) {
                 w4[q] = pack_bf16x2(a0, a1);
               } else {
@@ -531,7 +552,7 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
                            const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
                            int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
                            const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
-                           cudaStream_t st) {
+                           cudaStream_t st, const float* gate, int gate_idx, const float* acc_in) {
   if (!q || !k || !v || !row_ptr || !col_idx || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (kv_group < 1 || H % kv_group != 0) return SWV_ERR_SHAPE;
@@ -565,6 +586,7 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   p.row_ptr = row_ptr; p.col_idx = col_idx;
   p.mode = mode; p.num_cls = num_cls; p.window = window; p.dilation = dilation;
   p.kv_group = kv_group; p.lse = lse;
+  p.gate = gate; p.gate_idx = gate_idx; p.acc_in = acc_in;
   p.o = o; p.osb = os[0]; p.osh = os[1]; p.ost = os[2]; p.o_dtype = o_dtype;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   p.status = status;

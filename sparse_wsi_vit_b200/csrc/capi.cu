@@ -28,7 +28,7 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
                            const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
                            int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
                            const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
-                           cudaStream_t st);
+                           cudaStream_t st, const float* gate, int gate_idx, const float* acc_in);
 int pool_tokens_impl(const void* x, const int64_t* xs, void* y, int B, int H, int T, int D, int win, int stride,
                      cudaStream_t st);
 int rope2d_impl(const void* x, const int64_t* xs, void* y, const int64_t* ys, int dtype, const float* coords,
@@ -40,7 +40,7 @@ int nsa_select_blocks_impl(const void* q, const int64_t* qs, const void* kc, con
                            cudaStream_t st);
 int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                            const int64_t* vs, const int32_t* blocks, int B, int Hq, int Hkv, int Tq, int Tk, int D,
-                           int sel_block, int n_sel, float* o, cudaStream_t st);
+                           int sel_block, int n_sel, float* o, cudaStream_t st, const float* gate);
 int nsa_combine_impl(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,
                      int out_dtype, int B, int Hq, int T, int D, cudaStream_t st);
 int dsa_attn_bwd_impl(const void* d_out, const int64_t* dos, const void* q, const int64_t* qs, const void* k,
@@ -176,7 +176,7 @@ int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const v
                               int H, int Tq, int Tk, int D, int* status, void* stream) {
   return swv::block_sparse_attn_impl(q, q_strides, k, k_strides, v, v_strides, row_ptr, col_idx, block, mode, num_cls,
                                      window, dilation, kv_group, lse, o, o_strides, o_dtype, B, H, Tq, Tk, D, status,
-                                     static_cast<cudaStream_t>(stream));
+                                     static_cast<cudaStream_t>(stream), nullptr, 0, nullptr);
 }
 
 int swv_pool_tokens(const void* x, const int64_t x_strides[4], void* y, int B, int H, int T, int D, int window,
@@ -208,7 +208,7 @@ int swv_nsa_selected_attn_fwd(const void* q, const int64_t q_strides[4], const v
                               const void* v, const int64_t v_strides[4], const int32_t* blocks, int B, int Hq,
                               int Hkv, int Tq, int Tk, int D, int sel_block, int n_sel, float* o, void* stream) {
   return swv::nsa_selected_attn_impl(q, q_strides, k, k_strides, v, v_strides, blocks, B, Hq, Hkv, Tq, Tk, D,
-                                     sel_block, n_sel, o, static_cast<cudaStream_t>(stream));
+                                     sel_block, n_sel, o, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int swv_nsa_combine_fwd(const float* o_cmp, const float* o_sel, const float* o_win, const float* gate, void* out,

@@ -937,7 +937,7 @@ void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, flo
 static int attn_split_factor(int B, int H, int Tq, int Tk) {
   const int64_t ctas = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile) * ((H + 1) / 2);
   const int n_kt = (Tk + kTile - 1) / kTile;
-  const int n_sm = 148;
+  const int n_sm = sm_count();
   if (ctas >= 4 * n_sm) return 1;
   int best = 1;
   double best_cost = static_cast<double>((ctas + n_sm - 1) / n_sm);

@@ -834,13 +834,13 @@ struct WorkspaceLayout {
 // with few query tiles (one rank of a sequence-sharded run: 64 tiles on 148 SMs) or when the last
 // wave of whole-tile CTAs would be far from full (512 tiles = 3.46 waves), provided the key range
 // is long enough to be worth merging.
-constexpr int kSplitSms = 148;
 constexpr int kSplitMinKeyTiles = 64;
 static int split_factor(int B, int Tq, int Tk) {
   const int64_t tiles = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile);
   if ((Tk + kTile - 1) / kTile < kSplitMinKeyTiles) return 1;
-  const double whole = static_cast<double>((tiles + kSplitSms - 1) / kSplitSms);
-  const double halves = static_cast<double>((2 * tiles + kSplitSms - 1) / kSplitSms) / 2 + 0.05;   // + merge
+  const int n_sm = sm_count();
+  const double whole = static_cast<double>((tiles + n_sm - 1) / n_sm);
+  const double halves = static_cast<double>((2 * tiles + n_sm - 1) / n_sm) / 2 + 0.05;   // + merge
   return halves < whole ? 2 : 1;
 }
 static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {

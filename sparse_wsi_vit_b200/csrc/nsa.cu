@@ -289,6 +289,9 @@ struct NsaSelParams {
   int64_t qs[4], ks[4], vs[4];
   const int32_t* blocks;    // (B, Hkv, Tq, n_sel)
   float* o;                 // (B, Hq, Tq, D) fp32 contiguous
+  // Gated form (whole-pass call): o is the running gated sum of the branches and this branch adds
+  // sigmoid(gate[b,t,h,1]) * (its rows) to it; gate (B,Tq,Hq,3) fp32, null = plain store.
+  const float* gate;
   int B, Hq, Hkv, G, Tq, Tk, n_sel, sel_block;
   float scale_log2;
 };
@@ -414,8 +417,15 @@ __global__ void __launch_bounds__(128) nsa_selected_attn_kernel(const NsaSelPara
     if (hh < G) {
       const float inv = l[hh] > 0.f ? 1.f / l[hh] : 0.f;
       float* dst = p.o + ((static_cast<int64_t>(b) * p.Hq + g * G + hh) * p.Tq + t) * D + lane * DPL;
+      if (p.gate != nullptr) {
+        const float gl = p.gate[((static_cast<int64_t>(b) * p.Tq + t) * p.Hq + g * G + hh) * 3 + 1];
+        const float gs = 1.f / (1.f + __expf(-gl));
 #pragma unroll
-      for (int i = 0; i < DPL; ++i) dst[i] = o[hh][i] * inv;
+        for (int i = 0; i < DPL; ++i) dst[i] = fmaf(gs, o[hh][i] * inv, dst[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) dst[i] = o[hh][i] * inv;
+      }
     }
   }
 }
@@ -578,8 +588,18 @@ __global__ void __launch_bounds__(128) nsa_selected_attn_mma_kernel(const NsaSel
   if (g4 < G) {
     const float inv = l > 0.f ? 1.f / l : 0.f;
     float* dst = p.o + ((static_cast<int64_t>(b) * p.Hq + g * G + g4) * p.Tq + t) * D + 2 * t4;
+    if (p.gate != nullptr) {
+      const float gl = p.gate[((static_cast<int64_t>(b) * p.Tq + t) * p.Hq + g * G + g4) * 3 + 1];
+      const float gs = 1.f / (1.f + __expf(-gl));
 #pragma unroll
-    for (int n = 0; n < D / 8; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0] * inv, o[n][1] * inv);
+      for (int n = 0; n < D / 8; ++n) {
+        const float2 a = *reinterpret_cast<const float2*>(dst + n * 8);
+        *reinterpret_cast<float2*>(dst + n * 8) = make_float2(fmaf(gs, o[n][0] * inv, a.x), fmaf(gs, o[n][1] * inv, a.y));
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < D / 8; ++n) *reinterpret_cast<float2*>(dst + n * 8) = make_float2(o[n][0] * inv, o[n][1] * inv);
+    }
   }
 }
 
@@ -689,7 +709,7 @@ int nsa_select_blocks_impl(const void* q, const int64_t* qs, const void* kc, con
 
 int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                            const int64_t* vs, const int32_t* blocks, int B, int Hq, int Hkv, int Tq, int Tk, int D,
-                           int sel_block, int n_sel, float* o, cudaStream_t st) {
+                           int sel_block, int n_sel, float* o, cudaStream_t st, const float* gate) {
   if (!q || !k || !v || !blocks || !o || !qs || !ks || !vs) return SWV_ERR_NULL;
   if (B < 1 || Hq < 1 || Hkv < 1 || Hq % Hkv || Tq < 1 || Tk < 1 || n_sel < 1) return SWV_ERR_SHAPE;
   if (sel_block < 32 || sel_block % 32) return SWV_ERR_UNSUPPORTED;
@@ -703,7 +723,7 @@ int nsa_selected_attn_impl(const void* q, const int64_t* qs, const void* k, cons
   p.k = static_cast<const __nv_bfloat16*>(k);
   p.v = static_cast<const __nv_bfloat16*>(v);
   for (int i = 0; i < 4; ++i) { p.qs[i] = qs[i]; p.ks[i] = ks[i]; p.vs[i] = vs[i]; }
-  p.blocks = blocks; p.o = o;
+  p.blocks = blocks; p.o = o; p.gate = gate;
   p.B = B; p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.Tq = Tq; p.Tk = Tk; p.n_sel = n_sel; p.sel_block = sel_block;
   p.scale_log2 = 1.4426950408889634f / sqrtf(static_cast<float>(D));
   const int64_t total = static_cast<int64_t>(B) * Hkv * Tq;
@@ -778,10 +798,10 @@ int block_sparse_attn_impl(const void* q, const int64_t* qs, const void* k, cons
                            const int64_t* vs, const int32_t* row_ptr, const int32_t* col_idx, int block, int mode,
                            int num_cls, int window, int dilation, int kv_group, float* lse, void* o,
                            const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, int* status,
-                           cudaStream_t st);
+                           cudaStream_t st, const float* gate, int gate_idx, const float* acc_in);
 
 struct NsaLayout {
-  size_t kc, vc, o_cmp, o_sel, o_win, lse, imp, blocks, full_ptr, full_col, win_ptr, win_col, total;
+  size_t kc, vc, acc, lse, imp, blocks, full_ptr, full_col, win_ptr, win_col, total;
   int nC, n_qb, n_cb, k_eff, win_blocks;
 };
 static size_t nsa_up(size_t x) { return (x + 255) / 256 * 256; }
@@ -803,9 +823,7 @@ static int nsa_layout(int B, int Hq, int Hkv, int T, int D, int cmp_block, int c
   const size_t branch = static_cast<size_t>(B) * Hq * T * D * 4;
   L->kc = off; off += nsa_up(static_cast<size_t>(B) * Hkv * L->nC * D * 2);
   L->vc = off; off += nsa_up(static_cast<size_t>(B) * Hkv * L->nC * D * 2);
-  L->o_cmp = off; off += nsa_up(branch);
-  L->o_sel = off; off += nsa_up(branch);
-  L->o_win = off; off += nsa_up(branch);
+  L->acc = off; off += nsa_up(branch);      // the running gated sum of the branches, fp32
   L->lse = off; off += nsa_up(static_cast<size_t>(B) * Hq * T * 4);
   L->imp = off; off += nsa_up(imp_bytes);
   L->blocks = off; off += nsa_up(static_cast<size_t>(B) * Hkv * T * L->k_eff * 4);
@@ -839,9 +857,7 @@ int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   void* kc = ws + L.kc;
   void* vc = ws + L.vc;
-  float* o_cmp = reinterpret_cast<float*>(ws + L.o_cmp);
-  float* o_sel = reinterpret_cast<float*>(ws + L.o_sel);
-  float* o_win = reinterpret_cast<float*>(ws + L.o_win);
+  float* acc = reinterpret_cast<float*>(ws + L.acc);
   float* lse = reinterpret_cast<float*>(ws + L.lse);
   float* imp = reinterpret_cast<float*>(ws + L.imp);
   int32_t* blocks = reinterpret_cast<int32_t*>(ws + L.blocks);
@@ -860,9 +876,12 @@ int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t
   if (rc != SWV_OK) return rc;
   const int64_t cs[4] = {static_cast<int64_t>(Hkv) * L.nC * D, static_cast<int64_t>(L.nC) * D, D, 1};
   const int64_t os[4] = {static_cast<int64_t>(Hq) * T * D, static_cast<int64_t>(T) * D, D, 1};
+  // The gate is applied in the branch epilogues: acc = s(g0) cmp; acc += s(g1) sel; out = acc + s(g2) win
+  // (the order in which the stand-alone gate kernel adds them), so no branch output goes to HBM on
+  // its own.
   // compressed branch (all compressed tokens, log-sum-exp kept for the selection)
-  rc = block_sparse_attn_impl(q, qs, kc, cs, vc, cs, full_ptr, full_col, kTile, 0, 0, 0, 1, G, lse, o_cmp, os,
-                              SWV_F32, B, Hq, T, L.nC, D, status, st);
+  rc = block_sparse_attn_impl(q, qs, kc, cs, vc, cs, full_ptr, full_col, kTile, 0, 0, 0, 1, G, lse, acc, os,
+                              SWV_F32, B, Hq, T, L.nC, D, status, st, gate, 0, nullptr);
   if (rc != SWV_OK) return rc;
   // selection + selected branch
   size_t imp_bytes = 0;
@@ -870,13 +889,11 @@ int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t
   rc = nsa_select_blocks_impl(q, qs, kc, cs, lse, B, Hq, Hkv, T, T, L.nC, D, cmp_stride, sel_block, n_sel, imp,
                               imp_bytes, blocks, status, st);
   if (rc != SWV_OK) return rc;
-  rc = nsa_selected_attn_impl(q, qs, k, ks, v, vs, blocks, B, Hq, Hkv, T, T, D, sel_block, L.k_eff, o_sel, st);
+  rc = nsa_selected_attn_impl(q, qs, k, ks, v, vs, blocks, B, Hq, Hkv, T, T, D, sel_block, L.k_eff, acc, st, gate);
   if (rc != SWV_OK) return rc;
   // sliding-window branch: token pattern |i - j| <= window / 2 inside the listed blocks
-  rc = block_sparse_attn_impl(q, qs, k, ks, v, vs, win_ptr, win_col, kTile, 1, 0, reach, 1, G, nullptr, o_win, os,
-                              SWV_F32, B, Hq, T, T, D, status, st);
-  if (rc != SWV_OK) return rc;
-  rc = nsa_combine_impl(o_cmp, o_sel, o_win, gate, out, out_dtype, B, Hq, T, D, st);
+  rc = block_sparse_attn_impl(q, qs, k, ks, v, vs, win_ptr, win_col, kTile, 1, 0, reach, 1, G, nullptr, out, os,
+                              out_dtype, B, Hq, T, T, D, status, st, gate, 2, acc);
   if (rc != SWV_OK) return rc;
   if (blocks_out != nullptr)
     SWV_CUDA_OK(cudaMemcpyAsync(blocks_out, blocks, static_cast<size_t>(B) * Hkv * T * L.k_eff * 4,

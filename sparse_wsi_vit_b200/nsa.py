@@ -10,7 +10,10 @@ are the library-defined ones frozen in ``oracle/nsa.py`` (parity unpinned).
                key / value row once for all heads of the group (the heads are the rows of
                warp-level tensor-core tiles);
   window     : the block-sparse kernel in token-pattern mode (|i-j| <= window/2);
-  gate       : `swv_nsa_combine_fwd`, the sigmoid-weighted sum.
+  gate       : in the one-call form (`swv_nsa_attn_fwd`) every branch kernel applies its sigmoid gate
+               in its epilogue and adds its rows to one fp32 accumulator, the last branch writes
+               the output; the step-by-step form (`return_parts=True`) keeps the three branch
+               outputs and sums them with `swv_nsa_combine_fwd`.
 """
 from __future__ import annotations
 
@@ -20,7 +23,7 @@ import numpy as np
 import torch
 
 from ._lib import check, dtype_code, lib, strides
-from .ops import _require_cuda, _stream, block_sparse_attention, status_word
+from .ops import _buffer, _require_cuda, _stream, block_sparse_attention, status_word
 from .patterns import _to_csr, static_window_blocks
 
 
@@ -98,7 +101,7 @@ def nsa_attention(q, k, v, gate, cmp_block=32, cmp_stride=16, sel_block=64, sel_
         nbytes = ctypes.c_size_t()
         check(lib.swv_nsa_workspace_bytes(B, Hq, Hkv, T, D, cmp_block, cmp_stride, sel_block, sel_topk, window,
                                           ctypes.byref(nbytes)), "swv_nsa_workspace_bytes")
-        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        ws = _buffer("nsa_ws", dev, nbytes.value)         # kept between calls (the pass is stream-ordered)
         check(lib.swv_nsa_attn_fwd(q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v),
                                    gate.data_ptr(), out.data_ptr(), dtype_code(out_dtype), B, Hq, Hkv, T, D, cmp_block,
                                    cmp_stride, sel_block, sel_topk, window, ws.data_ptr(), nbytes.value, None,

@@ -61,7 +61,7 @@ def test_size_queries(swv):
     assert n.value == 2 * 65536 * 1024 * 4
     assert L.swv_nsa_importance_bytes(1, 2, 65536, 4095, 16, 40, ctypes.byref(n)) == -4
     assert L.swv_nsa_workspace_bytes(1, 16, 2, 65536, 128, 32, 16, 64, 16, 512, ctypes.byref(n)) == 0
-    assert n.value > 3 * 16 * 65536 * 128 * 4
+    assert n.value > 16 * 65536 * 128 * 4          # one fp32 accumulator of the gated branch sum
     assert L.swv_nsa_workspace_bytes(1, 16, 3, 65536, 128, 32, 16, 64, 16, 512, ctypes.byref(n)) == -4
 
 

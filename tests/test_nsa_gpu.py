@@ -66,7 +66,7 @@ def test_nsa_benchmark_size_sampled_rows():
                                                      out_dtype=torch.float32, return_parts=True)
     one = nsa_attention(q.to(DEV), k.to(DEV), v.to(DEV), gate.to(DEV), out_dtype=torch.float32)
     swv.check_status(DEV)
-    assert torch.equal(one, out)
+    assert (one - out).abs().max() < 1e-5
     ref, r_cmp, r_sel, r_win, r_blocks, margin = N.nsa_attention(q[0], k[0], v[0], gate[0], return_parts=True,
                                                                 rows=rows, pooled_dtype=torch.bfloat16)
     _compare(Hq, Hkv, out[0, :, rows].cpu(), o_cmp[0, :, rows].cpu(), o_sel[0, :, rows].cpu(), o_win[0, :, rows].cpu(),
@@ -74,8 +74,8 @@ def test_nsa_benchmark_size_sampled_rows():
 
 
 def test_nsa_single_call_equals_stepwise():
-    """`swv_nsa_attn_fwd` (one call, device-built block lists, caller workspace) runs the same kernels
-    as the step-by-step composition: identical output bits."""
+    """`swv_nsa_attn_fwd` (one call, device-built block lists, caller workspace, gates applied in the
+    branch epilogues) against the step-by-step composition (branch outputs + gate kernel)."""
     import sparse_wsi_vit_b200 as swv
     from sparse_wsi_vit_b200.nsa import nsa_attention
     T, Hq, Hkv, D = 1100, 8, 2, 128
@@ -87,4 +87,6 @@ def test_nsa_single_call_equals_stepwise():
     one = nsa_attention(q, k, v, gate, sel_topk=8, window=256, out_dtype=torch.float32)
     parts = nsa_attention(q, k, v, gate, sel_topk=8, window=256, out_dtype=torch.float32, return_parts=True)
     swv.check_status(DEV)
-    assert torch.equal(one, parts[0])
+    # same kernels and the same order of additions; the fused epilogues contract g * o + acc into one
+    # FMA where the stand-alone gate kernel may round the product first
+    assert (one - parts[0]).abs().max() < 1e-5
