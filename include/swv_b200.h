@@ -82,6 +82,7 @@ int swv_dsa_mask_bytes(int B, int Tq, int Tk, size_t* bytes);
  * histograms / candidate lists on chip; query tiles whose check fails or whose list
  * overflows redo the corresponding bytes with plain 8-bit histogram sweeps.
  *   q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID): strides (b,t,h,d); dtype SWV_F32/BF16/F16.
+ *   q_idx = k_idx = NULL: the workspace already holds the collapsed vectors (swv_dsa_prologue_fwd).
  *   w: (IH,) f32.   ID <= 64.   maskbits: optional (may be NULL) bitmask output
  *   (see swv_dsa_mask_bytes) consumed by swv_dsa_attn_masked_fwd.
  */
@@ -90,6 +91,24 @@ int swv_dsa_indexer_topk_fwd(const void* q_idx, const int64_t q_strides[4], cons
                              int IH, int ID, int top_k, int32_t* idx, float* valid, float* scores,
                              uint32_t* maskbits, void* workspace, size_t workspace_bytes, int* status,
                              void* stream);
+
+/* Token-local prologue of a DSA layer in one launch: (optionally) the 2-D rotary embedding of q and
+ * k, IN PLACE on the fused projection output, and the head collapse of the indexer projections
+ * written into the indexer workspace.  Replaces the separate steps between the projections and the
+ * indexer (M:54-59, the rotary placement of src/sparse_wsi_vit/models/vit_5/models_vit5.py:84-90) and
+ * the collapse step of swv_dsa_indexer_topk_fwd: call that entry afterwards with q_idx = k_idx = NULL
+ * and the same workspace, B, Tq = Tk = T.
+ *   q, k (B,T,H,D) TOKEN-major strides (b,t,h,d), unit inner stride, dtype F32 or BF16; ignored when
+ *   coords is NULL.  coords (B,T,2) f32 contiguous in the units of coord_high, one row per token
+ *   (rows of the first skip_tokens tokens of every sequence are not read: CLS tokens stay unrotated).
+ *   q_idx, k_idx (B,T,IH,ID) with strides, dtype F32/BF16/F16; w (IH,) f32; ID <= 64.
+ *   workspace: swv_dsa_workspace_bytes(B, T, T) bytes.
+ */
+int swv_dsa_prologue_fwd(void* q, const int64_t q_strides[4], void* k, const int64_t k_strides[4], int qk_dtype,
+                         const void* q_idx, const int64_t qi_strides[4], const void* k_idx, const int64_t ki_strides[4],
+                         int idx_dtype, const float* w, const float* coords, float coord_high, float theta,
+                         int skip_tokens, int B, int T, int H, int D, int IH, int ID, void* workspace,
+                         size_t workspace_bytes, void* stream);
 
 /* swv_dsa_indexer_topk_fwd without the workspace argument, for hosts that may not obtain
  * device memory for it.  It has no counterpart in the reference.

@@ -491,11 +491,13 @@ __global__ void rope2d_kernel(const T* __restrict__ x, T* __restrict__ y, const 
     const int f = pr - axis * half_pairs;             // frequency index
     const int dim = hd / 2;
     const float freq = exp2f(-log2_theta * (2.0f * f) / dim);
-    const float ang = coords[t * 2 + axis] * inv_high * freq;
+    const float ang = __fmul_rn(__fmul_rn(coords[t * 2 + axis], inv_high), freq);
     float sn, cs;
     sincosf(ang, &sn, &cs);
-    o0 = x0 * cs - x1 * sn;
-    o1 = x1 * cs + x0 * sn;
+    // explicit rounding order (the fused prologue kernel in indexer.cu computes the same expression
+    // and must give the same bits)
+    o0 = __fmaf_rn(x0, cs, -__fmul_rn(x1, sn));
+    o1 = __fmaf_rn(x1, cs, __fmul_rn(x0, sn));
   }
   if constexpr (sizeof(T) == 4) {
     yp[0] = o0;

@@ -52,6 +52,10 @@ int dsa_indexer_bwd_impl(const float* d_scores, const int64_t* dss, const void* 
                          const void* k_idx, const int64_t* ks, int dtype, const float* w, const int32_t* idx,
                          const int64_t* is, const float* valid, const int64_t* vls, float* dq, float* dk, float* dw,
                          int B, int Tq, int Tk, int IH, int ID, int top_k, int* status, cudaStream_t st);
+int dsa_prologue_impl(void* q, const int64_t* qs, void* k, const int64_t* ks, int qk_dtype, const void* q_idx,
+                      const int64_t* qis, const void* k_idx, const int64_t* kis, int idx_dtype, const float* w,
+                      const float* coords, float coord_high, float theta, int skip, int B, int T, int H, int D, int IH,
+                      int ID, void* workspace, size_t workspace_bytes, cudaStream_t st);
 int nsa_workspace_bytes_impl(int B, int Hq, int Hkv, int T, int D, int cmp_block, int cmp_stride, int sel_block,
                              int n_sel, int window, size_t* bytes);
 int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
@@ -144,6 +148,16 @@ int swv_dsa_indexer_bwd(const float* d_scores, const int64_t d_scores_strides[3]
   return swv::dsa_indexer_bwd_impl(d_scores, d_scores_strides, q_idx, q_strides, k_idx, k_strides, idx_dtype, w, idx,
                                    idx_strides, valid, valid_strides, dq_idx, dk_idx, dw, B, Tq, Tk, IH, ID, top_k,
                                    status, static_cast<cudaStream_t>(stream));
+}
+
+int swv_dsa_prologue_fwd(void* q, const int64_t q_strides[4], void* k, const int64_t k_strides[4], int qk_dtype,
+                         const void* q_idx, const int64_t qi_strides[4], const void* k_idx, const int64_t ki_strides[4],
+                         int idx_dtype, const float* w, const float* coords, float coord_high, float theta,
+                         int skip_tokens, int B, int T, int H, int D, int IH, int ID, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+  return swv::dsa_prologue_impl(q, q_strides, k, k_strides, qk_dtype, q_idx, qi_strides, k_idx, ki_strides, idx_dtype, w,
+                                coords, coord_high, theta, skip_tokens, B, T, H, D, IH, ID, workspace, workspace_bytes,
+                                static_cast<cudaStream_t>(stream));
 }
 
 int swv_dsa_attn_scratch_bytes(int B, int H, int Tq, int Tk, size_t* bytes) {

@@ -144,14 +144,14 @@ __global__ void __launch_bounds__(128) dsa_attn_gather_kernel(const GatherParams
 // ------------------------------------------------------- 16-bit fast path
 // bf16 / fp16 q, k, v with unit inner stride and 16-byte aligned rows, D in {32, 64, 128}.
 // One CTA per (batch, query) and up to eight heads, one warp per head: the row of idx / valid /
-// rw is read ONCE for all heads (256 slots at a time through shared memory).  A lane owns a
-// slot: it reads that key's row with 16-byte loads and accumulates the dot product with
-// mixed-precision FMAs (bf16 x bf16 products are exact in fp32), then reads the value row and
-// adds p * v into its OWN fp32 accumulators (p split into two 16-bit halves so that the
-// products stay exact to 2^-17); the 32 partial output rows are folded once at the end.  The
-// running maximum is exact (the accumulators are rescaled whenever it rises, a handful of times
-// per row).  Every selected row crosses the L2 -> SM path once per head: 2 * top_k * D * 2 bytes
-// per (query, head), one byte per FLOP -- the bound of this operator.
+// rw is read ONCE for all heads (256 slots at a time through shared memory).  D / 8 lanes share a
+// selected row, each reading one 16-byte chunk of the key row (mixed-precision FMAs: bf16 x bf16
+// products are exact in fp32; the partial dot products are added across the row's lanes) and then of
+// the value row (p split into two 16-bit halves so that the products stay exact to 2^-17, fp32
+// accumulators per lane, folded once at the end).  The running maximum is exact (the accumulators
+// are rescaled whenever it rises, a handful of times per row).  Every selected row crosses the
+// L2 -> SM path once per head: 2 * top_k * D * 2 bytes per (query, head), one byte per FLOP -- the
+// bound of this operator.
 template <bool BF16>
 __device__ __forceinline__ void fma_mixed2(float& acc0, float& acc1, uint32_t a, uint32_t b) {
   if (BF16) {
@@ -187,25 +187,28 @@ __device__ __forceinline__ void split16(float x, uint32_t& hi2, uint32_t& lo2) {
 
 constexpr int kRowsSlots = 256;      // slots staged per round
 
+// D / 8 lanes share one row (a lane reads ONE 16-byte chunk of it: 8 channels), so a warp-level load
+// touches 32 * 16 / (2 D) rows = whole 128-byte lines instead of 32 different lines -- the per-lane
+// form of this kernel ran at 99 % of the L1 pipe's tag rate.  G = 256 / D rows per step.
 template <int D, bool BF16>
 __global__ void __launch_bounds__(256) dsa_attn_gather_rows_kernel(const GatherParams p) {
-  constexpr int W = D / 2;           // 32-bit words per row
+  constexpr int LPR = D / 8;           // lanes per row
+  constexpr int G = 32 / LPR;          // rows per warp step
+  constexpr int STEPS = 32 / G;        // steps per 32 slots
   __shared__ int s_idx[kRowsSlots];
-  __shared__ float s_w[kRowsSlots];  // routing weight (s_idx < 0 marks a slot that is not valid)
-  __shared__ uint4 s_q[8][W / 4];
+  __shared__ float s_w[kRowsSlots];    // routing weight (s_idx < 0 marks a slot that is not valid)
   const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nwarps = blockDim.x >> 5;
   const int qi = blockIdx.x % p.Tq;
   const int b = blockIdx.x / p.Tq;
   const int h = blockIdx.y * nwarps + wib;
   const bool head_ok = h < p.H;
+  const int grp = lane / LPR, chunk = lane % LPR;
   const uint16_t* q16 = static_cast<const uint16_t*>(p.q);
   const uint16_t* k16 = static_cast<const uint16_t*>(p.k);
   const uint16_t* v16 = static_cast<const uint16_t*>(p.v);
-  if (head_ok) {
-    const uint4* qrow = reinterpret_cast<const uint4*>(q16 + b * p.qs[0] + h * p.qs[1] + qi * p.qs[2]);
-    if (lane < W / 4) s_q[wib][lane] = __ldg(qrow + lane);
-  }
+  uint4 qv = make_uint4(0, 0, 0, 0);   // this lane's 8 channels of q
+  if (head_ok) qv = __ldg(reinterpret_cast<const uint4*>(q16 + b * p.qs[0] + h * p.qs[1] + qi * p.qs[2]) + chunk);
   const int hk = head_ok ? h / p.kv_group : 0;
   const uint16_t* kbase = k16 + b * p.ks[0] + hk * p.ks[1];
   const uint16_t* vbase = v16 + b * p.vs[0] + hk * p.vs[1];
@@ -214,9 +217,9 @@ __global__ void __launch_bounds__(256) dsa_attn_gather_rows_kernel(const GatherP
   const float* rw_row = p.rw + b * p.rs[0] + qi * p.rs[1];
   const float ninf = -__int_as_float(0x7f800000);
 
-  float o[D];
+  float o[8];                          // channels [8 * chunk, +8) summed over this lane's rows
 #pragma unroll
-  for (int i = 0; i < D; ++i) o[i] = 0.f;
+  for (int i = 0; i < 8; ++i) o[i] = 0.f;
   float m = ninf, l = 0.f;
 
   for (int base = 0; base < p.top_k; base += kRowsSlots) {
@@ -241,50 +244,53 @@ __global__ void __launch_bounds__(256) dsa_attn_gather_rows_kernel(const GatherP
     if (!head_ok) continue;
     const int n_here = min(kRowsSlots, p.top_k - base);
     for (int c0 = 0; c0 < n_here; c0 += 32) {
-      const int id = s_idx[c0 + lane];
-      const float w = s_w[c0 + lane];
-      const bool ok = id >= 0;
-      float logit = ninf;
-      if (ok) {
-        const uint4* kr = reinterpret_cast<const uint4*>(kbase + static_cast<int64_t>(id) * p.ks[2]);
-        float a0 = 0.f, a1 = 0.f;
+      // logits of the 32 slots: step s handles slots c0 + s * G + grp (one per lane group)
+      float logit[STEPS];
+      int ids[STEPS];
+      float cmax = ninf;
 #pragma unroll
-        for (int i = 0; i < W / 4; ++i) {
-          const uint4 kv = __ldg(kr + i);
-          const uint4 qv = s_q[wib][i];
+      for (int s_ = 0; s_ < STEPS; ++s_) {
+        const int id = s_idx[c0 + s_ * G + grp];
+        ids[s_] = id;
+        float a0 = 0.f, a1 = 0.f;
+        if (id >= 0) {
+          const uint4 kv = __ldg(reinterpret_cast<const uint4*>(kbase + static_cast<int64_t>(id) * p.ks[2]) + chunk);
           fma_mixed2<BF16>(a0, a1, qv.x, kv.x);
           fma_mixed2<BF16>(a0, a1, qv.y, kv.y);
           fma_mixed2<BF16>(a0, a1, qv.z, kv.z);
           fma_mixed2<BF16>(a0, a1, qv.w, kv.w);
         }
-        logit = (a0 + a1) * p.scale;
-      }
-      float cmax = logit;
+        float a = a0 + a1;
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, off));
+        for (int off = LPR / 2; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        logit[s_] = id >= 0 ? a * p.scale : ninf;
+        cmax = fmaxf(cmax, logit[s_]);
+      }
+#pragma unroll
+      for (int off = 16; off >= LPR; off >>= 1) cmax = fmaxf(cmax, __shfl_xor_sync(0xffffffffu, cmax, off));
       if (cmax > m) {                                    // warp-uniform
         if (m != ninf) {
           const float f = __expf(m - cmax);
           l *= f;
 #pragma unroll
-          for (int i = 0; i < D; ++i) o[i] *= f;
+          for (int i = 0; i < 8; ++i) o[i] *= f;
         }
         m = cmax;
       }
-      const float pj = ok ? __expf(logit - m) * w : 0.f;
-      if (pj != 0.f) {
-        l += pj;
-        uint32_t ph, pl;
-        split16<BF16>(pj, ph, pl);
-        const uint4* vr = reinterpret_cast<const uint4*>(vbase + static_cast<int64_t>(id) * p.vs[2]);
 #pragma unroll
-        for (int i = 0; i < W / 4; ++i) {
-          const uint4 vv = __ldg(vr + i);
+      for (int s_ = 0; s_ < STEPS; ++s_) {
+        const int id = ids[s_];
+        const float pj = id >= 0 ? __expf(logit[s_] - m) * s_w[c0 + s_ * G + grp] : 0.f;
+        if (pj != 0.f) {                                  // uniform within the lane group
+          if (chunk == 0) l += pj;
+          uint32_t ph, pl;
+          split16<BF16>(pj, ph, pl);
+          const uint4 vv = __ldg(reinterpret_cast<const uint4*>(vbase + static_cast<int64_t>(id) * p.vs[2]) + chunk);
           const uint32_t vw[4] = {vv.x, vv.y, vv.z, vv.w};
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            fma_mixed2<BF16>(o[i * 8 + 2 * c], o[i * 8 + 2 * c + 1], ph, vw[c]);
-            fma_mixed2<BF16>(o[i * 8 + 2 * c], o[i * 8 + 2 * c + 1], pl, vw[c]);
+            fma_mixed2<BF16>(o[2 * c], o[2 * c + 1], ph, vw[c]);
+            fma_mixed2<BF16>(o[2 * c], o[2 * c + 1], pl, vw[c]);
           }
         }
       }
@@ -293,23 +299,18 @@ __global__ void __launch_bounds__(256) dsa_attn_gather_rows_kernel(const GatherP
   if (!head_ok) return;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) l += __shfl_xor_sync(0xffffffffu, l, off);
-  // fold the 32 partial rows: after the step with stride s a lane keeps the half of its channels
-  // selected by that bit of its index; lane L ends with channels [L * D/32, (L+1) * D/32)
+  // add up the lane groups: afterwards every lane of a chunk column holds the full sums
 #pragma unroll
-  for (int s = 16, n = D / 2; s >= 1; s >>= 1, n >>= 1) {
-    const bool up = (lane & s) != 0;
+  for (int off = 16; off >= LPR; off >>= 1) {
 #pragma unroll
-    for (int i = 0; i < n; ++i) {
-      const float send = up ? o[i] : o[i + n];
-      const float keep = up ? o[i + n] : o[i];
-      o[i] = keep + __shfl_xor_sync(0xffffffffu, send, s);
-    }
+    for (int i = 0; i < 8; ++i) o[i] += __shfl_xor_sync(0xffffffffu, o[i], off);
   }
-  const float inv = 1.f / fmaxf(l, 1e-6f);
-  constexpr int PER = D / 32;
-  const int64_t obase = b * p.os[0] + h * p.os[1] + qi * p.os[2];
+  if (grp == 0) {
+    const float inv = 1.f / fmaxf(l, 1e-6f);
+    const int64_t obase = b * p.os[0] + h * p.os[1] + qi * p.os[2];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) st_out(p.o, p.o_dtype, obase + (lane * PER + i) * p.os[3], o[i] * inv);
+    for (int i = 0; i < 8; ++i) st_out(p.o, p.o_dtype, obase + (chunk * 8 + i) * p.os[3], o[i] * inv);
+  }
 }
 
 static bool rows_path_ok(const GatherParams& p, int dtype, int D) {

@@ -59,6 +59,68 @@ __global__ void collapse_heads_kernel(const T* __restrict__ x, int64_t sb, int64
   out[gid] = acc;
 }
 
+// ------------------------------------------------------------------ prologue
+// Token-local prologue of a DSA layer in ONE launch (the reference runs these as separate ATen /
+// Triton steps: deepseek_sparse_attention.py:54-59 and, for the rotary term, vit_5/models_vit5.py:84-90):
+//   * 2-D rotary embedding of q and k, in place on the fused projection output (optional);
+//   * head collapse of the indexer projections, wq[t,:] = sum_h W[h] q_idx[t,h,:] (and wk), written
+//     straight into the indexer workspace, with exactly the arithmetic of collapse_heads_kernel.
+// One warp per token.
+template <typename TQ, typename TI>
+__global__ void __launch_bounds__(128)
+    dsa_prologue_kernel(TQ* __restrict__ q, int64_t qsb, int64_t qst, int64_t qsh, TQ* __restrict__ k, int64_t ksb,
+                        int64_t kst, int64_t ksh, const TI* __restrict__ qi, int64_t qib, int64_t qit, int64_t qih,
+                        int64_t qid, const TI* __restrict__ ki, int64_t kib, int64_t kit, int64_t kih, int64_t kid,
+                        const float* __restrict__ w, const float* __restrict__ coords, float inv_high,
+                        float log2_theta, int skip, float* __restrict__ wq, float* __restrict__ wk, int B, int T,
+                        int H, int D, int IH, int ID) {
+  const int lane = threadIdx.x & 31;
+  const int64_t tok = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (tok >= static_cast<int64_t>(B) * T) return;
+  const int t = static_cast<int>(tok % T);
+  const int b = static_cast<int>(tok / T);
+  if (coords != nullptr && t >= skip) {
+    const int pairs = D / 2, half_pairs = pairs / 2, dim = D / 2;
+    const float c0 = __fmul_rn(coords[tok * 2], inv_high), c1 = __fmul_rn(coords[tok * 2 + 1], inv_high);
+    for (int i = lane; i < H * pairs; i += 32) {
+      const int hh = i / pairs, pr = i - hh * pairs;
+      const int axis = pr >= half_pairs ? 1 : 0;
+      const int f = pr - axis * half_pairs;
+      const float freq = exp2f(-log2_theta * (2.0f * f) / dim);
+      const float ang = __fmul_rn(axis ? c1 : c0, freq);
+      float sn, cs;
+      sincosf(ang, &sn, &cs);
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        TQ* xp = which == 0 ? q + b * qsb + t * qst + hh * qsh + 2 * pr : k + b * ksb + t * kst + hh * ksh + 2 * pr;
+        const float x0 = to_f32<TQ>(xp[0]), x1 = to_f32<TQ>(xp[1]);
+        // (same expression and rounding order as rope2d_kernel in block_sparse.cu)
+        const float o0 = __fmaf_rn(x0, cs, -__fmul_rn(x1, sn)), o1 = __fmaf_rn(x1, cs, __fmul_rn(x0, sn));
+        if constexpr (sizeof(TQ) == 4) {
+          xp[0] = o0;
+          xp[1] = o1;
+        } else {
+          xp[0] = __float2bfloat16_rn(o0);
+          xp[1] = __float2bfloat16_rn(o1);
+        }
+      }
+    }
+  }
+  for (int d = lane; d < kIdxDim; d += 32) {
+    float aq = 0.f, ak = 0.f;
+    if (d < ID) {
+      const TI* pq = qi + b * qib + t * qit + d * qid;
+      const TI* pk = ki + b * kib + t * kit + d * kid;
+      for (int h = 0; h < IH; ++h) {
+        aq = __fadd_rn(aq, __fmul_rn(to_f32<TI>(pq[h * qih]), w[h]));
+        ak = __fadd_rn(ak, __fmul_rn(to_f32<TI>(pk[h * kih]), w[h]));
+      }
+    }
+    wq[tok * kIdxDim + d] = aq;
+    wk[tok * kIdxDim + d] = ak;
+  }
+}
+
 // --------------------------------------------------------------- tile kernel
 constexpr int kModeHist = 0;
 constexpr int kModeEmit = 1;
@@ -927,7 +989,10 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
                           const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
                           float* valid, float* scores, uint32_t* maskbits, void* workspace, size_t workspace_bytes,
                           int* status, cudaStream_t st, bool allow_split) {
-  if (!q_idx || !k_idx || !w || !idx || !valid || !scores || !workspace || !status || !qs || !ks)
+  // q_idx == k_idx == NULL: the workspace already holds the collapsed indexer vectors of these
+  // B x Tq queries and B x Tk keys (swv_dsa_prologue_fwd wrote them); the collapse step is skipped
+  const bool precollapsed = q_idx == nullptr && k_idx == nullptr;
+  if ((!precollapsed && (!q_idx || !k_idx || !w || !qs || !ks)) || !idx || !valid || !scores || !workspace || !status)
     return SWV_ERR_NULL;
   if (dtype != SWV_F32 && dtype != SWV_BF16 && dtype != SWV_F16) return SWV_ERR_DTYPE;
   if (B < 1 || Tq < 1 || Tk < 1 || IH < 1 || ID < 1 || top_k < 1) return SWV_ERR_SHAPE;
@@ -955,7 +1020,9 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
                     static_cast<uint64_t>(Tk) * kIdxDim * 4, 32, kTile);
   if (rc != SWV_OK) return rc;
 
-  if (dtype == SWV_F32) {
+  if (precollapsed) {
+    // nothing to do
+  } else if (dtype == SWV_F32) {
     launch_collapse<float>(q_idx, qs, w, wq, B, Tq, IH, ID, st);
     launch_collapse<float>(k_idx, ks, w, wk, B, Tk, IH, ID, st);
   } else if (dtype == SWV_BF16) {
@@ -1027,6 +1094,53 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   else
     fill_valid_kernel<1><<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(valid, idx, scores, total, top_k,
                                                                                       k_eff);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
+int dsa_prologue_impl(void* q, const int64_t* qs, void* k, const int64_t* ks, int qk_dtype, const void* q_idx,
+                      const int64_t* qis, const void* k_idx, const int64_t* kis, int idx_dtype, const float* w,
+                      const float* coords, float coord_high, float theta, int skip, int B, int T, int H, int D, int IH,
+                      int ID, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (!q_idx || !k_idx || !w || !workspace || !qis || !kis) return SWV_ERR_NULL;
+  if (coords != nullptr && (!q || !k || !qs || !ks)) return SWV_ERR_NULL;
+  if (B < 1 || T < 1 || IH < 1 || ID < 1) return SWV_ERR_SHAPE;
+  if (ID > kIdxDim) return SWV_ERR_UNSUPPORTED;
+  if (idx_dtype != SWV_F32 && idx_dtype != SWV_BF16 && idx_dtype != SWV_F16) return SWV_ERR_DTYPE;
+  if (coords != nullptr) {
+    if (qk_dtype != SWV_F32 && qk_dtype != SWV_BF16) return SWV_ERR_DTYPE;
+    if (H < 1 || D < 4 || (D % 4) != 0 || coord_high == 0.f || theta <= 0.f || skip < 0) return SWV_ERR_SHAPE;
+    if (qs[3] != 1 || ks[3] != 1) return SWV_ERR_ALIGN;
+  }
+  WorkspaceLayout L = workspace_layout(B, T, T);
+  if (workspace_bytes < L.flags3_off) return SWV_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SWV_ERR_ALIGN;
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  float* wq = reinterpret_cast<float*>(ws + L.wq_off);
+  float* wk = reinterpret_cast<float*>(ws + L.wk_off);
+  const unsigned grid = static_cast<unsigned>((static_cast<int64_t>(B) * T + 3) / 4);
+  const float inv_high = coords != nullptr ? 1.0f / coord_high : 0.f;
+  const float l2t = coords != nullptr ? log2f(theta) : 0.f;
+  const int64_t z[4] = {0, 0, 0, 1};
+  const int64_t* qq = coords != nullptr ? qs : z;
+  const int64_t* kk = coords != nullptr ? ks : z;
+#define SWV_PROLOGUE(TQ_, TI_)                                                                                 \
+  dsa_prologue_kernel<TQ_, TI_><<<grid, 128, 0, st>>>(                                                         \
+      static_cast<TQ_*>(q), qq[0], qq[1], qq[2], static_cast<TQ_*>(k), kk[0], kk[1], kk[2],                    \
+      static_cast<const TI_*>(q_idx), qis[0], qis[1], qis[2], qis[3], static_cast<const TI_*>(k_idx), kis[0],  \
+      kis[1], kis[2], kis[3], w, coords, inv_high, l2t, skip, wq, wk, B, T, H, D, IH, ID)
+  const bool q32 = coords != nullptr && qk_dtype == SWV_F32;
+  if (idx_dtype == SWV_F32) {
+    if (q32) SWV_PROLOGUE(float, float);
+    else SWV_PROLOGUE(__nv_bfloat16, float);
+  } else if (idx_dtype == SWV_BF16) {
+    if (q32) SWV_PROLOGUE(float, __nv_bfloat16);
+    else SWV_PROLOGUE(__nv_bfloat16, __nv_bfloat16);
+  } else {
+    if (q32) SWV_PROLOGUE(float, __half);
+    else SWV_PROLOGUE(__nv_bfloat16, __half);
+  }
+#undef SWV_PROLOGUE
   SWV_CUDA_OK(cudaGetLastError());
   return SWV_OK;
 }

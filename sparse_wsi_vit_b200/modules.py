@@ -78,6 +78,27 @@ class DeepSeekSparseAttention(nn.Module):
         self.indexer_proj = IndexerProjection(d_model, indexer_heads, indexer_dim)
         self.qkv_proj = nn.Linear(d_model, 3 * d_model)
         self.out_proj = nn.Linear(d_model, d_model)
+        self._cat = None                     # (key, weight, bias) of the fused projection, inference only
+
+    def _project(self, x):
+        """qkv (B,T,3,H,D) and the indexer projections (B,T,IH,ID).  Without gradients the three Linears
+        (qkv_proj, indexer q_proj, k_proj; deepseek_sparse_attention.py:54, :59) run as ONE GEMM over
+        the concatenated weights (cached until a parameter changes); the results are views of its
+        output."""
+        B, T, _ = x.shape
+        H, D, IH, ID = self.attention_heads, self.head_dim, self.indexer_heads, self.indexer_dim
+        lins = (self.qkv_proj, self.indexer_proj.q_proj, self.indexer_proj.k_proj)
+        if torch.is_grad_enabled() and any(p.requires_grad for l in lins for p in l.parameters()):
+            q_idx, k_idx = self.indexer_proj(x)
+            return self.qkv_proj(x).view(B, T, 3, H, D), q_idx, k_idx
+        key = tuple((p.data_ptr(), p._version, p.dtype) for l in lins for p in l.parameters())
+        if self._cat is None or self._cat[0] != key:
+            with torch.no_grad():
+                self._cat = (key, torch.cat([l.weight for l in lins], dim=0), torch.cat([l.bias for l in lins], dim=0))
+        y = torch.nn.functional.linear(x, self._cat[1], self._cat[2])
+        E3, n = 3 * self.d_model, IH * ID
+        return (y[..., :E3].unflatten(-1, (3, H, D)), y[..., E3:E3 + n].unflatten(-1, (IH, ID)),
+                y[..., E3 + n:].unflatten(-1, (IH, ID)))
 
     def forward(self, x, coords=None, coord_high=None, num_cls=0, rope_theta=10000.0):
         """``x (B, T, d_model)``.  The reference's layer has no positional term; with ``coords``
@@ -87,10 +108,9 @@ class DeepSeekSparseAttention(nn.Module):
         H, D = self.attention_heads, self.head_dim
         # [q | k | v] outermost, then head, then head-dim; the kernels take the
         # (B, H, T, D) views as they are (strided), no contiguous copies.
-        qkv = self.qkv_proj(x).view(B, T, 3, H, D)
         if coords is not None and coord_high is None:
             raise ValueError("coords need coord_high (the coordinate that maps to one radian per unit frequency)")
-        q_idx, k_idx = self.indexer_proj(x)
+        qkv, q_idx, k_idx = self._project(x)
         if torch.is_grad_enabled() and (qkv.requires_grad or q_idx.requires_grad or
                                         self.indexer_head_weights.requires_grad):
             # training: one differentiable op (fused forward, the two backward kernels chained)
@@ -105,10 +125,17 @@ class DeepSeekSparseAttention(nn.Module):
             o = DSAModuleFunction.apply(qt.transpose(1, 2), kt.transpose(1, 2), vt.transpose(1, 2), q_idx, k_idx,
                                         self.indexer_head_weights, self.top_k, x.dtype)
             return self.out_proj(o.transpose(1, 2).reshape(B, T, H * D).to(x.dtype))
+        rope = None
         if coords is not None:
-            rope_qk_(qkv, coords, coord_high, num_cls, rope_theta)
+            # rotated in place inside the prologue launch (one row of coordinates per token, zeros for CLS)
+            c = coords.reshape(B if coords.dim() == 3 else 1, -1, 2).to(torch.float32)
+            if c.shape[1] != T - num_cls:
+                raise ValueError(f"coords cover {c.shape[1]} tokens, the sequence has {T - num_cls} patch tokens")
+            c = torch.cat([c.new_zeros((c.shape[0], num_cls, 2)), c], dim=1) if num_cls else c
+            rope = (c, coord_high, rope_theta, num_cls)
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
-        o = dsa_sparse_attention(q, k, v, q_idx, k_idx, self.indexer_head_weights, self.top_k, out_dtype=x.dtype)
+        o = dsa_sparse_attention(q, k, v, q_idx, k_idx, self.indexer_head_weights, self.top_k, out_dtype=x.dtype,
+                                 rope=rope)
         return self.out_proj(o.transpose(1, 2).reshape(B, T, H * D).to(x.dtype))
 
 

@@ -72,11 +72,45 @@ def mask_bytes(B, Tq, Tk):
     return n.value
 
 
-def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=None):
+def dsa_prologue(qkv_q, qkv_k, q_idx, k_idx, w, coords=None, coord_high=1.0, theta=10000.0, skip_tokens=0):
+    """Token-local prologue in one launch: optional in-place 2-D RoPE of q and k (TOKEN-major
+    (B,T,H,D) views of the projection output; ``coords`` (B,T,2) or (T,2), one row per token) and the
+    indexer head collapse.  Returns the indexer workspace holding the collapsed vectors; pass it to
+    ``dsa_indexer_topk(..., workspace=ws, precollapsed=True)``."""
+    _require_cuda(q_idx, k_idx, w)
+    B, T, IH, ID = q_idx.shape
+    if k_idx.shape != q_idx.shape:
+        raise SwvError("the prologue needs as many keys as queries (self-attention layer)")
+    if k_idx.dtype != q_idx.dtype:
+        k_idx = k_idx.to(q_idx.dtype)
+    dev = q_idx.device
+    ws = torch.empty(workspace_bytes(B, T, T), dtype=torch.uint8, device=dev)
+    w32 = w.detach().to(torch.float32).contiguous()
+    cptr, qp, kp, qs, ks, qdt, H, D = None, None, None, None, None, 0, 1, 4
+    if coords is not None:
+        _require_cuda(qkv_q, qkv_k, coords)
+        if qkv_q.dtype != qkv_k.dtype or qkv_q.stride(-1) != 1 or qkv_k.stride(-1) != 1:
+            raise SwvError("q and k must share a dtype and have unit inner stride")
+        H, D = qkv_q.shape[2], qkv_q.shape[3]
+        c = coords.reshape(-1, T, 2).to(torch.float32)
+        c = (c.expand(B, T, 2) if c.shape[0] == 1 else c).contiguous()
+        cptr, qp, kp, qs, ks, qdt = c.data_ptr(), qkv_q.data_ptr(), qkv_k.data_ptr(), strides(qkv_q), strides(qkv_k), \
+            dtype_code(qkv_q.dtype)
+    rc = lib.swv_dsa_prologue_fwd(qp, qs, kp, ks, qdt, q_idx.data_ptr(), strides(q_idx), k_idx.data_ptr(),
+                                  strides(k_idx), dtype_code(q_idx.dtype), w32.data_ptr(), cptr, float(coord_high),
+                                  float(theta), int(skip_tokens), B, T, H, D, IH, ID, ws.data_ptr(), ws.numel(),
+                                  _stream(dev))
+    check(rc, "swv_dsa_prologue_fwd")
+    return ws
+
+
+def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=None, workspace=None,
+                     precollapsed=False):
     """q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID), w (IH,) -> idx int32, valid f32, scores f32,
     each (B,Tq,top_k), keys in ascending order.  With `want_mask` also the selection handle
     ``(bitmask, workspace)`` that ``dsa_attention_masked`` consumes; it owns both buffers, so it
-    stays valid across later indexer calls."""
+    stays valid across later indexer calls.  ``workspace`` + ``precollapsed``: the workspace
+    ``dsa_prologue`` returned (the collapse step is then skipped; q_idx / k_idx give the shapes)."""
     _require_cuda(q_idx, k_idx, w)
     if q_idx.dim() != 4 or k_idx.dim() != 4:
         raise SwvError("indexer projections must be (B, T, IH, ID)")
@@ -96,7 +130,10 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
         idx, valid, scores = out
     nws = workspace_bytes(B, Tq, Tk)
     # a selection handle keeps its own workspace (the attention reads it); plain calls share one
-    ws = torch.empty(nws, dtype=torch.uint8, device=dev) if want_mask else _buffer("ws", dev, nws)
+    if workspace is not None:
+        ws = workspace
+    else:
+        ws = torch.empty(nws, dtype=torch.uint8, device=dev) if want_mask else _buffer("ws", dev, nws)
     mptr = None
     if want_mask:
         if mask is None:
@@ -104,7 +141,8 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
         mptr = mask.data_ptr()
     st = status_word(dev)
     rc = lib.swv_dsa_indexer_topk_fwd(
-        q_idx.data_ptr(), strides(q_idx), k_idx.data_ptr(), strides(k_idx), dtype_code(q_idx.dtype),
+        None if precollapsed else q_idx.data_ptr(), strides(q_idx), None if precollapsed else k_idx.data_ptr(),
+        strides(k_idx), dtype_code(q_idx.dtype),
         w32.data_ptr(), B, Tq, Tk, IH, ID, top_k, idx.data_ptr(), valid.data_ptr(), scores.data_ptr(), mptr,
         ws.data_ptr(), ws.numel(), st.data_ptr(), _stream(dev))
     check(rc, "swv_dsa_indexer_topk_fwd")
@@ -188,8 +226,13 @@ def dsa_attention_masked_count(q, k, v, selection, o):
     return cnt
 
 
-def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False, kv_ready=None):
+def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return_topk=False, kv_ready=None,
+                         rope=None):
     """Indexer + top-k + routing-weighted attention (deepseek_sparse_attention.py:59-85).
+
+    ``rope`` = (coords (T,2) or (B,T,2) with one row per token, coord_high, theta, skip_tokens): q and k
+    (views of the projection output, rotated IN PLACE) get the 2-D rotary embedding first, in the same
+    launch that collapses the indexer heads (``dsa_prologue``).
 
     q (B,H,Tq,D), k, v (B,H,Tk,D); q_idx (B,Tq,IH,ID), k_idx (B,Tk,IH,ID); w (IH,).
     bf16 with D == 64 takes the dense tensor-core path; anything else the gather
@@ -202,13 +245,20 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
     out_dtype = out_dtype or q.dtype
     o = torch.empty((B, H, Tq, D), dtype=out_dtype, device=dev)
     dense = q.dtype == torch.bfloat16 and D == 64
+    ws, pre = None, False
+    if rope is not None or (dense and q_idx.shape == k_idx.shape and kv_ready is None):
+        # one launch for the token-local steps between the projections and the indexer
+        coords, coord_high, theta, skip = rope if rope is not None else (None, 1.0, 10000.0, 0)
+        ws = dsa_prologue(q.transpose(1, 2), k.transpose(1, 2), q_idx, k_idx, w, coords, coord_high, theta, skip)
+        pre = True
     if dense:
-        idx, valid, scores, sel = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True)
+        idx, valid, scores, sel = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True, workspace=ws,
+                                                   precollapsed=pre)
         if kv_ready is not None:
             torch.cuda.current_stream(dev).wait_event(kv_ready)
         dsa_attention_masked(q, k, v, sel, o)
     else:
-        idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k)
+        idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k, workspace=ws, precollapsed=pre)
         if kv_ready is not None:
             torch.cuda.current_stream(dev).wait_event(kv_ready)
         dsa_attention_gather(q, k, v, idx, valid, scores * valid, o)
