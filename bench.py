@@ -36,15 +36,15 @@ H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
 METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 # kernels of this library launched per forward on one GPU: 2 head collapses, 6 radix-select tile
 # passes (4 of them return at once unless a query tile asked for the fallback), emit, valid fill,
-# key-norm maximum, attention
+# key-norm maximum, attention (12; the sharded step launches the same on every rank)
 KERNELS_PER_STEP = 12
 
 # DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, from one-pass ncu captures
-# (dram__bytes_read.sum + dram__bytes_write.sum): 5.26 GB + 0.07 GB on the 65536-token workload -- K, V
+# (dram__bytes_read.sum + dram__bytes_write.sum): 3.15 GB + 0.07 GB on the 65536-token workload -- K, V
 # of all heads and the indexer keys, 144 MiB, do not fit the 126 MB L2, so key tiles are re-fetched;
-# 59.5 MB + 5.0 MB at 16384 tokens, where they fit.  A profiler figure cannot be taken inside a timed
+# 62.7 MB + 64.8 MB at 16384 tokens, where they fit.  A profiler figure cannot be taken inside a timed
 # run, so the JSON line carries it with `traffic_source` saying so.
-ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 5.327e9, 16384: 64.5e6}
+ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 3.225e9, 16384: 127.5e6}
 
 
 def workload_config(T, world):
