@@ -121,7 +121,7 @@ int swv_dsa_prologue_fwd(void* q, const int64_t q_strides[4], void* k, const int
  * Same arguments, outputs and arithmetic as swv_dsa_indexer_topk_fwd (the same kernels run).
  * Limits and rules:
  *   - B*Tq <= 8192 and B*Tk <= 8192 (any batch / length split of them); anything larger
- *     returns SWV_ERR_TOO_LARGE and launches nothing.  The array (about 4.4 MB) is held by every GPU
+ *     returns SWV_ERR_TOO_LARGE and launches nothing.  The array (about 4.5 MB) is held by every GPU
  *     that loads the library, until
  *     the process exits.
  *   - The first call on a device looks up the array's device address (with that device

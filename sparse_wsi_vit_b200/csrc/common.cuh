@@ -13,6 +13,8 @@ namespace swv {
 
 constexpr int kTile = 128;        // query rows and key columns per score tile
 constexpr int kIdxDim = 64;       // padded reduction depth of the indexer
+constexpr int kMaxExcl = 4;       // ties at a row's threshold that are cut by key index: the unselected ones are
+                                  // listed per row (up to this many) for the attention sweep
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;  // 1 s per wait, then give up
 
 // Device status codes (written once, first error wins).

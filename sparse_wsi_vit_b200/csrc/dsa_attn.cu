@@ -72,6 +72,7 @@ struct AttnParams {
   int B, H, Tq, Tk, nQT, nKT, nHP;
   const uint32_t* maskbits;
   const uint32_t *st_prefix, *st_kth, *st_neq;   // per query row, written by the indexer's select passes
+  const int32_t* st_excl;                        // [B*Tq][kMaxExcl] ties at the threshold that are not selected
   const uint32_t* kmax2;                         // [B*H] max squared key norm, float bits
   const __nv_bfloat16* q;
   int64_t qsb, qsh, qst;
@@ -103,6 +104,7 @@ struct AttnCtl {
   uint32_t abort_flag;
   uint32_t cta_exact;          // some row of the CTA needs the two-pass path
   uint32_t ticket;
+  int next_ex[32 * kSoftWarps];   // per softmax thread: next key tile with an unselected tie of its row to drop
 };
 
 constexpr size_t attn_smem_bytes() { return 1024 + kOffCtl + sizeof(AttnCtl) + 64; }
@@ -322,11 +324,42 @@ __device__ __forceinline__ bool softmax_pass(AttnCtl* ctl, uint32_t s_col, uint3
   return true;
 }
 
+// Rows whose ties at the threshold are cut by key index (a few per 10^4 rows on continuous data: two
+// keys with bit-identical scores around the K-th place) carry a list of the tied keys that are NOT
+// selected.  `score >= threshold` admits them; when the sweep reaches the tile of such a key, the
+// thread that owns its column clears that weight.  `tile_of(e)` = key tile relative to the CTA's
+// first one.  Returns the next tile (> j) in which this thread has to do so again, or INT_MAX.
+template <bool COUNT>
+__device__ __forceinline__ int drop_excluded(uint32_t (&w)[kSliceCols / 2], float& cnt, const int32_t* list, int n,
+                                             int kt0, int slice, int j) {
+  int nxt = 0x7fffffff;
+  for (int i = 0; i < n; ++i) {
+    const int e = __ldg(list + i);
+    if (((e & (kTile - 1)) / kSliceCols) != slice) continue;
+    const int t = e / kTile - kt0;
+    if (t == j) {
+      const int pos = e & (kSliceCols - 1);
+      const uint32_t keep = (pos & 1) ? 0x0000ffffu : 0xffff0000u;
+      // (opaque to the compiler on purpose: written as plain C++ the unrolled compare-and-clear is
+      // folded back into a dynamically indexed store, which moves the weights to local memory)
+#pragma unroll
+      for (int r = 0; r < kSliceCols / 2; ++r)
+        asm("{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, %2;\n\t@p and.b32 %0, %0, %3;\n\t}"
+            : "+r"(w[r])
+            : "r"(pos >> 1), "r"(r), "r"(keep));
+      if (COUNT) cnt -= 1.f;
+    } else if (t > j && t < nxt) {
+      nxt = t;
+    }
+  }
+  return nxt;
+}
+
 template <bool COUNT>
 __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_base, int slice, int nh, int nKT,
                                                     int lane, float thr, float sc, const float (&bound)[2],
-                                                    float (&l_out)[2], float& cnt, int* status,
-                                                    volatile uint32_t* abort_flag) {
+                                                    float (&l_out)[2], float& cnt, const AttnParams& p, bool warp_cut,
+                                                    int grow0, int kt0, int* status, volatile uint32_t* abort_flag) {
   Prof prof;
   prof.start();
   const uint32_t r_col = lane_base + kColR + slice * kSliceCols;
@@ -337,8 +370,14 @@ __device__ __forceinline__ bool softmax_tiles_split(AttnCtl* ctl, uint32_t lane_
   uint32_t w[kSliceCols / 2];
   cnt = 0.f;
   if (!convert_weights<COUNT>(ctl, r_col, 0, lane, neg_c, w, cnt, status, abort_flag, prof)) return false;
+  int* next_ex = &ctl->next_ex[threadIdx.x - 64];   // written by this thread before the loop: -1 = look the list up
   for (int j = 0; j < nKT; ++j) {
     const bool more = j + 1 < nKT;
+    if (warp_cut && *next_ex <= j) {                  // warp_cut: some row of this warp has cut ties (rare)
+      const int64_t grow = grow0 + (threadIdx.x & 127);
+      const int n_ex = static_cast<int>(p.st_neq[grow] - p.st_kth[grow]);
+      *next_ex = drop_excluded<COUNT>(w, cnt, p.st_excl + grow * kMaxExcl, n_ex, kt0, slice, j);
+    }
     if (!softmax_pass<false, COUNT>(ctl, s_col0, r_col, 0, j, lane, sc, -bound[0], neg_c, w, cnt, l[0][0], l[0][1],
                                     status, abort_flag, prof))
       return false;
@@ -713,11 +752,13 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 
     // Row constants from the indexer's select passes: threshold bits, how many keys equal
     // to the threshold are selected, how many exist.  The one-pass path is exact when
-    //   - the threshold is positive and every tie is selected (membership = score >= thr),
+    //   - the threshold is positive and at most kMaxExcl ties at it are left out (membership =
+    //     score >= thr, minus the row's listed keys),
     //   - every weight exceeds the 1e-6 clamp on the denominator (the clamp cannot bind),
     //   - the logits of the row are provably small (|s*sc| <= bound <= kMaxBound), both heads.
     // One row that fails sends the whole CTA to the two-pass bitmask path.
     bool flagged = false;
+    bool cut_row = false;                        // some of this row's ties at the threshold are cut
     float thr_ge = __int_as_float(0x7f800000);   // tail rows: nothing selected
     float bound[2] = {0.f, 0.f};
     if (row_ok) {
@@ -744,11 +785,16 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
         bound[x] = sqrtf(q2 * k2) * p.scale_log2 * 1.001f + 1e-3f;
         small = small && bound[x] <= kMaxBound;
       }
-      flagged = !(thr_bits != 0u && p.st_kth[grow] == p.st_neq[grow] && thr_ge >= 4e-6f && small);
+      const uint32_t n_cut = p.st_neq[grow] - p.st_kth[grow];     // ties at the threshold that are not selected
+      flagged = !(thr_bits != 0u && n_cut <= static_cast<uint32_t>(kMaxExcl) && thr_ge >= 4e-6f && small);
+      cut_row = n_cut != 0u;
     }
     if (__any_sync(0xffffffffu, flagged) && lane == 0) atomicOr(&ctl->cta_exact, 1u);
     asm volatile("bar.sync 2, %0;" ::"r"(32 * kSoftWarps) : "memory");
     const bool exact = *reinterpret_cast<volatile uint32_t*>(&ctl->cta_exact) != 0u;
+#ifdef SWV_PROFILE
+    if (exact && warp == 2 && lane == 0) atomicAdd(&g_attn_prof[62], 1ull);
+#endif
 
     // Output duty.  One-pass layout: slice s writes head s % 2, channels [d0, d0 + nd) with the 64
     // channels of a head divided among the slices that share it; two-pass layout: slices 0 and 1
@@ -764,8 +810,10 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
     float row_l = 0.f, row_mu = 0.f, row_mt = 0.f;   // row statistics of this CTA's key range (for the split merge)
     if (!exact) {
       float l_part[2], cnt = 0.f;
+      ctl->next_ex[threadIdx.x - 64] = cut_row ? -1 : 0x7fffffff;
       ok = softmax_tiles_split<kCount>(ctl, lane_base, slice, nh, nKT, lane, thr_ge, p.scale_log2, bound, l_part, cnt,
-                                       p.status, abort_flag);
+                                       p, __any_sync(0xffffffffu, cut_row), b * p.Tq + qt * kTile, kt0, p.status,
+                                       abort_flag);
       if (kCount && hp == 0 && row_ok) atomicAdd(p.member_count + static_cast<int64_t>(b) * p.Tq + qrow, static_cast<int>(cnt));
       // The column slices of a row add their partial sums through the indexer-query tile:
       // every routing-weight MMA that read it has retired once any warp has left its loop.
@@ -930,7 +978,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
-                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2);
+                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2, int32_t** excl);
 
 // How many CTAs share one (query tile, head pair): with grids of only a few waves the last wave is
 // far from full, so the key range is divided (1, 2 or 4 ways) to even the load out.
@@ -983,7 +1031,8 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
 
   float *wq = nullptr, *wk = nullptr;
   uint32_t *st_prefix = nullptr, *st_kth = nullptr, *st_neq = nullptr, *kmax2 = nullptr;
-  dsa_workspace_views(workspace, B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq, &kmax2);
+  int32_t* st_excl = nullptr;
+  dsa_workspace_views(workspace, B, Tq, Tk, &wq, &wk, &st_prefix, &st_kth, &st_neq, &kmax2, &st_excl);
   if (static_cast<int64_t>(B) * H > 1024) return SWV_ERR_UNSUPPORTED;
 
   CUtensorMap tm_wq, tm_wk, tm_q, tm_k, tm_v;
@@ -1009,7 +1058,7 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
   p.nKT = (Tk + kTile - 1) / kTile;
   p.nHP = (H + 1) / 2;
   p.maskbits = maskbits;
-  p.st_prefix = st_prefix; p.st_kth = st_kth; p.st_neq = st_neq;
+  p.st_prefix = st_prefix; p.st_kth = st_kth; p.st_neq = st_neq; p.st_excl = st_excl;
   p.kmax2 = kmax2;
   p.q = static_cast<const __nv_bfloat16*>(q); p.qsb = qs[0]; p.qsh = qs[1]; p.qst = qs[2];
   p.o = o; p.osb = os[0]; p.osh = os[1]; p.ost = os[2]; p.o_dtype = o_dtype;

@@ -147,6 +147,8 @@ struct IndexerParams {
   uint32_t* st_prefix;    // [B*Tq] known high bits of the threshold
   uint32_t* st_kth;       // [B*Tq] rank still to find inside the prefix bucket
   uint32_t* st_neq;       // [B*Tq] after the last pass: number of keys whose score equals the threshold
+  int32_t* st_excl;       // [B*Tq][kMaxExcl] EMIT: keys equal to the threshold that are NOT selected (ties cut by key
+                          // index), ascending, the first kMaxExcl of them
   // Key-range split: with few query tiles (a rank of a sequence-sharded run) `split` = 2 CTAs share
   // a query tile, each sweeping half of the key tiles; the part that finishes last merges.
   int split, nKT0;               // CTAs per query tile; key tiles of part 0
@@ -709,12 +711,16 @@ __global__ void __launch_bounds__(576, 1)
       // A second part starts behind part 0's share of the row: the keys above the threshold in part
       // 0's range plus the ties part 0 takes (ties are taken in ascending key order).
       uint32_t eq_seen = 0;
+      uint32_t ex_seen = 0;                                     // ties of the row left out so far (cut rows only)
       int cnt = 0;
       if (use_split && part == 1 && row_ok) {
-        eq_seen = min(p.st_eq0[grow], partial ? take_eq : 0xFFFFFFFFu);
+        const uint32_t eq0 = p.st_eq0[grow];
+        eq_seen = min(eq0, partial ? take_eq : 0xFFFFFFFFu);
         cnt = static_cast<int>(p.st_cnt0[grow] + eq_seen);
-        if (!partial) eq_seen = 0;
+        if (partial) ex_seen = eq0 - eq_seen;
+        else eq_seen = 0;
       }
+      int32_t* excl_row = p.st_excl + grow * kMaxExcl;
       int32_t* idx_row = p.idx + grow * p.top_k;
       float* sc_row = p.scores + grow * p.top_k;
       // 32-bit shared addresses: the staging tiles share the histogram's slot, then the exchange
@@ -807,6 +813,16 @@ __global__ void __launch_bounds__(576, 1)
               eb ^= low;
               ++eq_seen;
             }
+            // The ties that stay out are listed for the attention sweep, which otherwise selects
+            // by `score >= threshold` (one writer per row; a second part continues part 0's list).
+            if (ch == 0) {
+              while (eb != 0u) {
+                if (ex_seen < static_cast<uint32_t>(kMaxExcl))
+                  excl_row[ex_seen] = (kt0 + j) * kTile + c * 32 + (__ffs(eb) - 1);
+                eb &= eb - 1u;
+                ++ex_seen;
+              }
+            }
           }
         }
         int off = cnt, cnt_new = cnt;
@@ -887,7 +903,7 @@ __global__ void fill_valid_kernel(float* __restrict__ valid, int32_t* __restrict
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
 struct WorkspaceLayout {
-  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, kmax_off, flags_off, flags2_off;
+  size_t wq_off, wk_off, prefix_off, kth_off, neq_off, excl_off, kmax_off, flags_off, flags2_off;
   size_t flags3_off, tickets_off, cnt0_off, eq0_off, ghist_off, glist_off, gcnt_off;   // key-range split only
   int split;
   size_t total;
@@ -918,6 +934,8 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
   L.neq_off = off;
   off += align_up(static_cast<size_t>(B) * Tq * 4, 1024);
+  L.excl_off = off;     // per query row: the unselected keys among the ties at its threshold
+  off += align_up(static_cast<size_t>(B) * Tq * kMaxExcl * 4, 1024);
   L.kmax_off = off;     // per (batch, head) key-norm maxima of the attention kernel, up to 1024 entries
   off += 4096;
   const size_t tiles = static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile);
@@ -949,7 +967,7 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
 
 // Where the collapsed indexer queries / keys of the last indexer call live inside its workspace.
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
-                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2) {
+                         uint32_t** kth, uint32_t** neq, uint32_t** kmax2, int32_t** excl) {
   const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   *wq = reinterpret_cast<float*>(ws + L.wq_off);
@@ -958,6 +976,7 @@ void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, flo
   *kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
   *neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
   *kmax2 = reinterpret_cast<uint32_t*>(ws + L.kmax_off);
+  *excl = reinterpret_cast<int32_t*>(ws + L.excl_off);
 }
 
 template <typename T>
@@ -1040,6 +1059,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   p.st_prefix = reinterpret_cast<uint32_t*>(ws + L.prefix_off);
   p.st_kth = reinterpret_cast<uint32_t*>(ws + L.kth_off);
   p.st_neq = reinterpret_cast<uint32_t*>(ws + L.neq_off);
+  p.st_excl = reinterpret_cast<int32_t*>(ws + L.excl_off);
   p.idx = idx; p.scores = scores; p.maskbits = maskbits; p.status = status; p.pass = 0;
   p.kind = kKindFirst; p.only_flagged = 0;
   uint32_t* flags_a = reinterpret_cast<uint32_t*>(ws + L.flags_off);
@@ -1151,7 +1171,8 @@ int dsa_prologue_impl(void* q, const int64_t* qs, void* k, const int64_t* ks, in
 // whose context loads this library holds these bytes until the process exits.
 constexpr int kStaticMaxTokens = 8192;
 constexpr size_t kStaticScratchBytes =
-    2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + 3 * static_cast<size_t>(kStaticMaxTokens) * 4 + 4096 +
+    2 * static_cast<size_t>(kStaticMaxTokens) * kIdxDim * 4 + (3 + kMaxExcl) * static_cast<size_t>(kStaticMaxTokens) * 4 +
+    4096 +
     2 * 32 * 1024 /* tile flags: up to 8192 query tiles (a batch of one-token sequences) */ +
     8 * 1024 /* per-section rounding */;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];

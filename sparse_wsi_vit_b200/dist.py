@@ -90,18 +90,24 @@ def sharded_dsa_attention(q_loc, k_loc, v_loc, qi_loc, ki_loc, w, top_k, plan: S
     ki_all = all_gather_tokens(ki_loc, plan, group)
     if use_side:
         # Ordering contract: the gathers run on `comm_stream` behind everything already queued on
-        # the current stream; the attention waits for `kv_ready` on the current stream.  The gathered
-        # buffers are allocated while `comm_stream` is current, so they are marked as used by the
-        # current stream too: the caching allocator must not hand them back to `comm_stream` while
-        # the attention kernels still read them.
+        # the current stream; the attention waits for `kv_ready` on the current stream.  With batch 1
+        # the gathered buffers are allocated HERE, on the current stream: every later reader is
+        # ordered on the current stream, the only foreign writer (the gather) finishes before
+        # `kv_ready`, so the caching allocator may reuse them like any other block of this stream.
+        # (Allocating them under `comm_stream` and marking them as used by the current stream keeps
+        # each block out of the pool until the GPU catches up with the host: one device allocation
+        # per gather while the host runs ahead, which at 8 ranks costs more than the step.)
         cur = torch.cuda.current_stream(k_loc.device)
+        pre = k_loc.shape[0] == 1
+        outs = [x.new_empty((1, plan.world * plan.per_rank, *x.shape[2:])) if pre else None for x in (k_loc, v_loc)]
         comm_stream.wait_stream(cur)
         with torch.cuda.stream(comm_stream):
-            k_all = all_gather_tokens(k_loc, plan, group)
-            v_all = all_gather_tokens(v_loc, plan, group)
+            k_all = all_gather_tokens(k_loc, plan, group, out=outs[0])
+            v_all = all_gather_tokens(v_loc, plan, group, out=outs[1])
         kv_ready = comm_stream.record_event()
-        k_all.record_stream(cur)
-        v_all.record_stream(cur)
+        if not pre:
+            k_all.record_stream(cur)
+            v_all.record_stream(cur)
     else:
         k_all = all_gather_tokens(k_loc, plan, group)
         v_all = all_gather_tokens(v_loc, plan, group)

@@ -368,7 +368,8 @@ def test_random_shapes(swv, seed):
 
 
 @pytest.mark.parametrize("T,H,K,mode", [(16384, 8, 2048, "bench"), (65536, 2, 2048, "bench"), (1500, 2, 300, "ties"),
-                                        (900, 3, 800, "fewpos")])
+                                        (900, 3, 800, "fewpos"), (4096, 2, 301, "twins"), (3072, 3, 301, "triplets"),
+                                        (3072, 2, 302, "triplets"), (16384, 2, 2047, "twins")])
 def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode):
     """The dense attention sweep recomputes every score tile on the tensor cores and, on its one-pass
     path, treats a key as selected iff that score >= the row threshold the indexer found.  The
@@ -376,7 +377,9 @@ def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode
     recomputed tiles are bit-identical to the scores the selection was made on (one flipped key
     would be invisible in the output tolerance).  Benchmark-distributed inputs at 16384 and 65536
     tokens (one-pass path), heavily tied scores and rows with fewer than K positive scores (the
-    two-pass bitmask path)."""
+    two-pass bitmask path), and keys that exist twice or three times with K chosen so that EVERY
+    row's threshold falls inside such a group (ties cut by key index, one or two keys per row left
+    out: the one-pass path with the row's list of unselected ties)."""
     q, k, v, qi, ki, w = make_dsa_inputs(T, H, 64, 4, 64, seed=77 + T, dtype=torch.bfloat16, device=_dev())
     if mode == "ties":
         qi, ki = (qi.float() * 32).round() / 32, (ki.float() * 32).round() / 32
@@ -384,7 +387,19 @@ def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode
     if mode == "fewpos":
         qi, ki = qi.abs(), -ki.abs()
         ki[:, ::5] = ki[:, ::5].abs()
+    if mode == "twins":                       # key t + T/2 is key t: the twin sits in another key tile
+        ki[:, T // 2:] = ki[:, :T // 2]
+    if mode == "triplets":                    # keys 3m, 3m + 1, 3m + 2 are one key
+        ki[:, 1::3] = ki[:, 0::3]
+        ki[:, 2::3] = ki[:, 0::3]
     idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    if mode in ("twins", "triplets"):
+        # the rows really are cut: the (K+1)-th score equals the K-th on (nearly) every row
+        full = own_scores(qi[:, :256].contiguous(), ki, w)[0]
+        srt = full.sort(dim=-1, descending=True).values
+        assert float((srt[:, K - 1] == srt[:, K]).float().mean()) > 0.9
+        o_list = torch.empty((1, H, T, 64), dtype=torch.float32, device=_dev())
+        swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o_list)
     o = torch.empty((1, H, T, 64), dtype=torch.float32, device=_dev())
     from sparse_wsi_vit_b200.ops import dsa_attention_masked_count
     cnt = dsa_attention_masked_count(q, k, v, sel, o)
@@ -396,3 +411,5 @@ def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode
     swv.dsa_attention_masked(q, k, v, sel, o2)
     _check(swv)
     assert float((o - o2).abs().max()) < 1e-3
+    if mode in ("twins", "triplets"):
+        assert float((o2 - o_list).abs().max()) < 2e-2 and float((o2 - o_list).abs().mean()) < 1e-3
