@@ -227,6 +227,27 @@ int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], con
                                   void* o, const int64_t o_strides[4], int o_dtype, int B, int H, int Tq, int Tk, int D,
                                   int32_t* member_count, int* status, void* stream);
 
+/* Routing-weighted attention over the indexer's key lists as dense tensor-core tiles with a sparse
+ * softmax (the attention step of DSAAttentionFunction.forward, K:769-810 and K:450-564, for the lists
+ * swv_dsa_indexer_topk_fwd writes: bf16 q, k, v, head dim 64).  Same result as
+ * swv_dsa_attn_masked_fwd; membership and routing weights are READ from the lists instead of being
+ * recomputed from the indexer vectors:
+ *   idx  (B, Tq, top_k) int32 contiguous, every row strictly ASCENDING over its first min(top_k, Tk)
+ *        slots (the rest is ignored); top_k a multiple of 4, 16-byte aligned;
+ *   rw   (B, Tq, top_k) fp32 contiguous routing weights of those slots (scores * valid).
+ * A list that is not ascending gives a wrong result for that row but no invalid access.
+ * `maskbits` and `workspace` are the ones the indexer call filled: a (query tile, head pair) whose
+ * logits cannot be bounded below 2^40 is left to the kernel of swv_dsa_attn_masked_fwd, which this
+ * entry launches behind its own for those tiles only.  `scratch` (256-byte aligned, at least
+ * swv_dsa_attn_lists_scratch_bytes) is required.
+ */
+int swv_dsa_attn_lists_scratch_bytes(int B, int H, int Tq, int Tk, int top_k, size_t* bytes);
+int swv_dsa_attn_lists_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                           const void* v, const int64_t v_strides[4], const int32_t* idx, const float* rw, int top_k,
+                           const uint32_t* maskbits, void* workspace, void* o, const int64_t o_strides[4], int o_dtype,
+                           int B, int H, int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status,
+                           void* stream);
+
 /* Static block-sparse flash attention forward driven by a CSR list of key blocks per
  * query block (shared by all batches and heads):
  *   o[q] = softmax_j( q.k_j / sqrt(D) ) v_j   over the keys j the pattern lets q see;

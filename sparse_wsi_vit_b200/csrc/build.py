@@ -19,7 +19,7 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB = os.path.join(HERE, "libswv_b200.so")
-SOURCES = ["indexer.cu", "dsa_attn.cu", "dsa_gather.cu", "dsa_bwd.cu", "block_sparse.cu", "nsa.cu", "capi.cu"]
+SOURCES = ["indexer.cu", "dsa_attn.cu", "dsa_attn_lists.cu", "dsa_gather.cu", "dsa_bwd.cu", "block_sparse.cu", "nsa.cu", "capi.cu"]
 HEADERS = ["ptx.cuh", "common.cuh", os.path.join("..", "..", "include", "swv_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -17,8 +17,14 @@ int dsa_indexer_topk_static_impl(const void* q_idx, const int64_t* qs, const voi
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
-                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count);
+                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count,
+                         const uint32_t* only_flagged);
 int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes);
+int dsa_attn_lists_scratch_bytes_impl(int B, int H, int Tq, int Tk, int top_k, size_t* bytes);
+int dsa_attn_lists_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
+                        const int64_t* vs, const int32_t* idx, const float* rw, int top_k, const uint32_t* maskbits,
+                        void* workspace, void* o, const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D,
+                        void* scratch, size_t scratch_bytes, int* status, cudaStream_t st);
 int dsa_attn_gather_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, int dtype, const int32_t* idx, const int64_t* is, const float* valid,
                          const int64_t* vls, const float* rw, const int64_t* rs, void* o, const int64_t* os,
@@ -170,7 +176,21 @@ int swv_dsa_attn_masked_fwd(const void* q, const int64_t q_strides[4], const voi
                             int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status, void* stream) {
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, scratch, scratch_bytes, status,
-                                   static_cast<cudaStream_t>(stream), nullptr);
+                                   static_cast<cudaStream_t>(stream), nullptr, nullptr);
+}
+
+int swv_dsa_attn_lists_scratch_bytes(int B, int H, int Tq, int Tk, int top_k, size_t* bytes) {
+  return swv::dsa_attn_lists_scratch_bytes_impl(B, H, Tq, Tk, top_k, bytes);
+}
+
+int swv_dsa_attn_lists_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
+                           const void* v, const int64_t v_strides[4], const int32_t* idx, const float* rw, int top_k,
+                           const uint32_t* maskbits, void* workspace, void* o, const int64_t o_strides[4], int o_dtype,
+                           int B, int H, int Tq, int Tk, int D, void* scratch, size_t scratch_bytes, int* status,
+                           void* stream) {
+  return swv::dsa_attn_lists_impl(q, q_strides, k, k_strides, v, v_strides, idx, rw, top_k, maskbits, workspace, o,
+                                  o_strides, o_dtype, B, H, Tq, Tk, D, scratch, scratch_bytes, status,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],
@@ -180,7 +200,7 @@ int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], con
   if (member_count == nullptr) return SWV_ERR_NULL;
   return swv::dsa_attn_masked_impl(q, q_strides, k, k_strides, v, v_strides, maskbits, workspace, o, o_strides,
                                    o_dtype, B, H, Tq, Tk, D, nullptr, 0, status, static_cast<cudaStream_t>(stream),
-                                   member_count);
+                                   member_count, nullptr);
 }
 
 int swv_block_sparse_attn_fwd(const void* q, const int64_t q_strides[4], const void* k, const int64_t k_strides[4],

@@ -90,6 +90,9 @@ struct AttnParams {
   // Diagnostic instantiation only: [B*Tq] number of keys each query row treated as selected (summed
   // over the column slices; counted once, by head pair 0).
   int* member_count;
+  // When set: [B*nQT*nHP] only the (query tile, head pair)s with a non-zero entry are computed (the
+  // list-driven kernel leaves those with a too large logit bound to this one).
+  const uint32_t* only_flagged;
 };
 constexpr int kPartRec = kHeadDim + 4;                // output row + (l, m_used, m_true, pad)
 
@@ -548,6 +551,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
   const int lane = threadIdx.x & 31;
   const int cta = kSplit ? blockIdx.x / p.split : blockIdx.x;     // (batch, query tile, head pair)
   const int part = kSplit ? blockIdx.x - cta * p.split : 0;       // which share of the key tiles
+  if (p.only_flagged != nullptr && p.only_flagged[cta] == 0u) return;
   const int hp = cta % p.nHP;
   const int qt = (cta / p.nHP) % p.nQT;
   const int b = cta / (p.nHP * p.nQT);
@@ -977,12 +981,22 @@ __global__ void __launch_bounds__(kAttnThreads, 1)
 // ---------------------------------------------------------------------- host
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// kmax2[b*H + h] = float bits of the largest squared key norm of head h (for the logit bounds)
+int dsa_key_norm_max(const void* k, const int64_t* ks, int B, int H, int Tk, uint32_t* kmax2, cudaStream_t st) {
+  SWV_CUDA_OK(cudaMemsetAsync(kmax2, 0, static_cast<size_t>(B) * H * 4, st));
+  const int64_t total = static_cast<int64_t>(B) * H * Tk;
+  key_norm_max_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(k), ks[0], ks[1], ks[2], B, H, Tk, kmax2);
+  SWV_CUDA_OK(cudaGetLastError());
+  return SWV_OK;
+}
+
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
                          uint32_t** kth, uint32_t** neq, uint32_t** kmax2, int32_t** excl);
 
 // How many CTAs share one (query tile, head pair): with grids of only a few waves the last wave is
 // far from full, so the key range is divided (1, 2 or 4 ways) to even the load out.
-static int attn_split_factor(int B, int H, int Tq, int Tk) {
+int dsa_attn_split_factor(int B, int H, int Tq, int Tk) {
   const int64_t ctas = static_cast<int64_t>(B) * ((Tq + kTile - 1) / kTile) * ((H + 1) / 2);
   const int n_kt = (Tk + kTile - 1) / kTile;
   const int n_sm = sm_count();
@@ -1003,7 +1017,7 @@ static int attn_split_factor(int B, int H, int Tq, int Tk) {
 int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes) {
   if (!bytes) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
-  const int s = attn_split_factor(B, H, Tq, Tk);
+  const int s = dsa_attn_split_factor(B, H, Tq, Tk);
   const size_t ctas = static_cast<size_t>(B) * ((Tq + kTile - 1) / kTile) * ((H + 1) / 2);
   *bytes = s == 1 ? 0 : ((ctas * 4 + 255) / 256 * 256 + ctas * s * 2 * kTile * kPartRec * 4);
   return SWV_OK;
@@ -1012,7 +1026,8 @@ int dsa_attn_scratch_bytes_impl(int B, int H, int Tq, int Tk, size_t* bytes) {
 int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const int64_t* ks, const void* v,
                          const int64_t* vs, const uint32_t* maskbits, void* workspace, void* o,
                          const int64_t* os, int o_dtype, int B, int H, int Tq, int Tk, int D, void* scratch,
-                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count) {
+                         size_t scratch_bytes, int* status, cudaStream_t st, int* member_count,
+                         const uint32_t* only_flagged) {
   if (!q || !k || !v || !maskbits || !workspace || !o || !status || !qs || !ks || !vs || !os) return SWV_ERR_NULL;
   if (B < 1 || H < 1 || Tq < 1 || Tk < 1) return SWV_ERR_SHAPE;
   if (D != kHeadDim) return SWV_ERR_UNSUPPORTED;
@@ -1075,17 +1090,16 @@ int dsa_attn_masked_impl(const void* q, const int64_t* qs, const void* k, const 
     if (need > 0 && member_count == nullptr && scratch != nullptr && scratch_bytes >= need &&
         (reinterpret_cast<uintptr_t>(scratch) & 255) == 0) {
       const size_t ctas = static_cast<size_t>(B) * p.nQT * p.nHP;
-      p.split = attn_split_factor(B, H, Tq, Tk);
+      p.split = dsa_attn_split_factor(B, H, Tq, Tk);
       p.tickets = static_cast<uint32_t*>(scratch);
       p.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + (ctas * 4 + 255) / 256 * 256);
       SWV_CUDA_OK(cudaMemsetAsync(p.tickets, 0, ctas * 4, st));
     }
   }
-  SWV_CUDA_OK(cudaMemsetAsync(kmax2, 0, static_cast<size_t>(B) * H * 4, st));
-  {
-    const int64_t total = static_cast<int64_t>(B) * H * Tk;
-    key_norm_max_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(k), ks[0], ks[1], ks[2], B, H, Tk, kmax2);
+  p.only_flagged = only_flagged;
+  if (only_flagged == nullptr) {        // (the caller that passes flags has filled kmax2 already)
+    const int rck = dsa_key_norm_max(k, ks, B, H, Tk, kmax2, st);
+    if (rck != SWV_OK) return rck;
   }
   const unsigned grid = static_cast<unsigned>(B) * p.nQT * p.nHP * p.split;
   p.member_count = member_count;

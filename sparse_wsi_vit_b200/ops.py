@@ -206,6 +206,37 @@ def dsa_attention_masked(q, k, v, selection, o):
     return o
 
 
+def dsa_attention_lists(q, k, v, idx, rw, selection, o):
+    """The same attention as ``dsa_attention_masked`` driven by the indexer's ascending key lists:
+    dense tensor-core tiles, one exponential per SELECTED key (``idx``, ``rw`` (B,Tq,top_k) as
+    ``dsa_indexer_topk`` returns them, ``rw = scores * valid``); `selection` as for
+    ``dsa_attention_masked`` (used for the few tiles whose logits cannot be bounded)."""
+    mask, ws = selection
+    _require_cuda(q, k, v, idx, rw, mask, ws, o)
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    top_k = idx.shape[-1]
+    if q.dtype != torch.bfloat16 or D != 64 or top_k % 4:
+        raise SwvError("dsa_attention_lists needs bf16 q/k/v with head_dim 64 and top_k a multiple of 4")
+    if idx.dtype != torch.int32 or rw.dtype != torch.float32 or not idx.is_contiguous() or not rw.is_contiguous():
+        raise SwvError("dsa_attention_lists needs contiguous int32 idx and fp32 rw")
+    q, k, v = (t if _tma_ok(t) else t.contiguous() for t in (q, k, v))
+    dev = q.device
+    st = status_word(dev)
+    nscr = ctypes.c_size_t()
+    check(lib.swv_dsa_attn_lists_scratch_bytes(B, H, Tq, Tk, top_k, ctypes.byref(nscr)),
+          "swv_dsa_attn_lists_scratch_bytes")
+    scr = _buffer("attn_lists_scratch", dev, nscr.value)
+    rc = lib.swv_dsa_attn_lists_fwd(
+        q.data_ptr(), strides(q), k.data_ptr(), strides(k), v.data_ptr(), strides(v), idx.data_ptr(), rw.data_ptr(),
+        top_k, mask.data_ptr(), ws.data_ptr(), o.data_ptr(), strides(o), dtype_code(o.dtype), B, H, Tq, Tk, D,
+        scr.data_ptr(), nscr.value, st.data_ptr(), _stream(dev))
+    check(rc, "swv_dsa_attn_lists_fwd")
+    if _CHECK:
+        check_status(dev, "swv_dsa_attn_lists_fwd")
+    return o
+
+
 def dsa_attention_masked_count(q, k, v, selection, o):
     """Diagnostic: ``dsa_attention_masked`` (unsplit) that also returns, per query row, how many keys
     the kernel treated as selected, int32 (B, Tq); must equal min(top_k, Tk) everywhere."""
