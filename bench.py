@@ -36,8 +36,13 @@ H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
 METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 # kernels of this library launched per forward on one GPU: 2 head collapses, 6 radix-select tile
 # passes (4 of them return at once unless a query tile asked for the fallback), emit, valid fill,
-# key-norm maximum, attention (12; the sharded step launches the same on every rank)
-KERNELS_PER_STEP = 12
+# key-norm maximum, attention (12; the sharded step launches the same on every rank).  When the
+# selection is sparse enough for the list-driven attention kernel: + the tile-list build and the
+# launch of the dense sweep for flagged tiles (returns at once unless a tile was flagged) = 14.
+def kernels_per_step(T):
+    from sparse_wsi_vit_b200 import ops
+    lists = TOP_K % 4 == 0 and min(TOP_K, T) <= ops.LISTS_MAX_DENSITY * T
+    return 14 if lists else 12
 
 # DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, from one-pass ncu captures
 # (dram__bytes_read.sum + dram__bytes_write.sum): 3.15 GB + 0.07 GB on the 65536-token workload -- K, V
@@ -45,6 +50,8 @@ KERNELS_PER_STEP = 12
 # 62.7 MB + 64.8 MB at 16384 tokens, where they fit.  A profiler figure cannot be taken inside a timed
 # run, so the JSON line carries it with `traffic_source` saying so.
 ATTN_DRAM_BYTES_PER_LAUNCH = {65536: 3.225e9, 16384: 127.5e6}
+# the same for dsa_attn_lists_kernel (65536 tokens; it also reads the 1.6 GB of tile lists once per head pair)
+ATTN_LISTS_DRAM_BYTES_PER_LAUNCH = {65536: 4.12e9}
 
 
 def workload_config(T, world):
@@ -306,7 +313,7 @@ def run_ours(args):
                 cur.wait_event(qkv_ready)
             if timed_idx is not None:
                 ev_a[timed_idx].record(cur)
-            ops.dsa_attention_masked(qv, kv, vv, sel, o)
+            ops.dsa_attention_dense(qv, kv, vv, idx, scores, sel, o)
             if timed_idx is not None:
                 ev_b[timed_idx].record(cur)
             return o, idx
@@ -467,17 +474,23 @@ def run_ours(args):
                                  "d2h_bytes_per_step": (o_host.numel() * o_host.element_size() +
                                                         idx_host.numel() * 4) * world,
                                  "outputs_downloaded": "o and the int32 index lists idx"}},
-            "gpu_launches": args.steps * KERNELS_PER_STEP * world,
+            "gpu_launches": args.steps * kernels_per_step(T) * world,
             "clocks": clocks,
         }
         if world == 1:
             attn_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev_a, ev_b))
+            lists = kernels_per_step(T) == 14
             kept = 4.0 * T * min(TOP_K, T) * H * D
-            executed = 4.0 * T * T * H * D
+            # dense tiles on the tensor cores: the sweep multiplies Q K^T and P V over all keys (+ the
+            # routing-weight tiles); the list-driven kernel Q K^T and P [V | 1] with an 80-wide accumulator
+            executed = (2.0 * D + 2.0 * 80) * T * T * H if lists else 4.0 * T * T * H * D
             ach = kept / (attn_ms * 1e-3) / 1e12
             line["roofline"] = {
-                "kernel": "dsa_attn_masked_kernel", "bound": "tensor", "achieved": ach, "peak": tf_peak,
-                "unit": "TFLOP/s", "frac": ach / tf_peak, "traffic": ATTN_DRAM_BYTES_PER_LAUNCH.get(T),
+                "kernel": ("dsa_attn_lists_kernel (timed with dsa_tile_lists_kernel and key_norm_max_kernel, which "
+                           "it needs)" if lists else "dsa_attn_masked_kernel"),
+                "bound": "tensor", "achieved": ach, "peak": tf_peak,
+                "unit": "TFLOP/s", "frac": ach / tf_peak,
+                "traffic": (ATTN_LISTS_DRAM_BYTES_PER_LAUNCH if lists else ATTN_DRAM_BYTES_PER_LAUNCH).get(T),
                 "traffic_source": "one-pass ncu capture of this kernel on this workload, taken in a separate "
                                   "run (a constant of bench.py, not measured by this run)",
                 "peak_source": f"bf16_tflops_sustained of {peak_src}",
@@ -485,10 +498,18 @@ def run_ours(args):
                 "executed_flops": executed, "executed_tflops": executed / (attn_ms * 1e-3) / 1e12,
                 "executed_frac": executed / (attn_ms * 1e-3) / 1e12 / tf_peak,
                 "other_kernels_ms": ms - attn_ms,
-                # what actually bounds this kernel: one exp per (query, key, head) on the 16 exp lanes per SM
-                "exp_unit_floor_ms": T * float(T) * H / (16.0 * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3,
             }
-            line["roofline"]["exp_unit_frac"] = line["roofline"]["exp_unit_floor_ms"] / attn_ms
+            if lists:
+                # what bounds the list-driven kernel: shared-memory traffic per (128 x 128 tile, head pair) --
+                # K, V tiles in (64 KiB) and out to the tensor cores (K 32, V + ones 40, P 64 KiB), the fp16
+                # copy of S (64 KiB), list entries and barriers -- about 300 KiB at 128 bytes per clock and SM
+                tiles = (T / 128.0) ** 2 * (H / 2)
+                line["roofline"]["smem_floor_ms"] = tiles * 300.0 * 1024 / 128 / (148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3
+                line["roofline"]["smem_frac"] = line["roofline"]["smem_floor_ms"] / attn_ms
+            else:
+                # what bounds the sweep: one exp per (query, key, head) on the 16 exp lanes per SM
+                line["roofline"]["exp_unit_floor_ms"] = T * float(T) * H / (16.0 * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3
+                line["roofline"]["exp_unit_frac"] = line["roofline"]["exp_unit_floor_ms"] / attn_ms
             line["cpu_baseline"] = cpu_baseline(T, budget_s=15.0)
         print(json.dumps(line), flush=True)
     if world > 1:

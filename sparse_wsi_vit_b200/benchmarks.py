@@ -235,12 +235,13 @@ def static_encoder(steps=5, warmup=2, tokens=4096):
                       "dtype": "f32 in, bf16 attention", "ms": ms, "tokens_per_s": tokens / (ms * 1e-3)}), flush=True)
 
 
-def dsa_variants(steps=3, warmup=1, sizes=(16384, 65536)):
-    """The DSA attention step two ways on the same key lists (8 heads x 64, top-2048, bf16):
-    `dense_sweep` = all key tiles on the tensor cores with the selection applied inside the softmax
-    (dsa_attn_masked_kernel); `list_gather` = the literal operator, every selected key / value row
-    fetched per query and head (dsa_attn_gather_rows_kernel).  Also the dense sweep forced onto its
-    two-pass softmax (heavily tied indexer scores: thresholds whose ties are cut by key index)."""
+def dsa_variants(steps=3, warmup=1, sizes=(16384, 65536, 131072)):
+    """The DSA attention step three ways on the same key lists (8 heads x 64, top-2048, bf16):
+    `dense_sweep` = all key tiles on the tensor cores with the selection applied inside a dense softmax
+    (dsa_attn_masked_kernel); `list_tiles` = the same tensor-core tiles with a sparse softmax over
+    per-tile member lists (dsa_tile_lists_kernel + dsa_attn_lists_kernel); `list_gather` = the literal
+    operator, every selected key / value row fetched per query and head (dsa_attn_gather_rows_kernel).
+    Also the dense sweep forced onto its two-pass softmax (heavily tied indexer scores)."""
     from . import ops
     dev = torch.device("cuda", 0)
     H, D, IH, ID, K = 8, 64, 4, 64, 2048
@@ -259,6 +260,12 @@ def dsa_variants(steps=3, warmup=1, sizes=(16384, 65536)):
             o = torch.empty((1, H, T, D), dtype=torch.bfloat16, device=dev)
             line["dense_sweep" + tag + "_ms"] = _time_ms(lambda: ops.dsa_attention_masked(q, k, v, sel, o), steps, warmup)
             if tag == "":
+                o3 = torch.empty_like(o)
+                line["list_tiles_ms"] = _time_ms(lambda: ops.dsa_attention_lists(q, k, v, idx, scores, sel, o3), steps,
+                                                 warmup)
+                line["max_abs_diff_sweep_vs_list_tiles"] = float((o.float() - o3.float()).abs().max())
+                if T > 65536:
+                    continue            # (the row gather takes T * K time and adds nothing new beyond 65536)
                 rw = scores * valid
                 o2 = torch.empty_like(o)
                 ms = _time_ms(lambda: ops.dsa_attention_gather(q, k, v, idx, valid, rw, o2), steps, warmup)

@@ -237,6 +237,25 @@ def dsa_attention_lists(q, k, v, idx, rw, selection, o):
     return o
 
 
+# The list-driven kernel does a constant amount of work per (query tile, key tile) plus a little per
+# selected key (three list entries per thread and tile are held in registers), the dense sweep one
+# exponential per (query, key, head).  Measured on B200 (8 heads, top-2048): the lists win at 65536
+# tokens (one key in 32: 9.5 + 0.8 ms against 13.1-14.5 ms) and lose at 32768 (one in 16).
+LISTS_MAX_DENSITY = 1.0 / 24.0
+
+
+def dsa_attention_dense(q, k, v, idx, scores, selection, o):
+    """The attention step of the fused path on the tensor cores: the list-driven kernel
+    (``dsa_attention_lists``) for sparse selections, the dense sweep (``dsa_attention_masked``)
+    otherwise.  ``idx`` / ``scores`` / ``selection`` as ``dsa_indexer_topk(..., want_mask=True)``
+    returns them (slots beyond min(top_k, Tk) are ignored, so ``scores`` serve as routing weights)."""
+    Tk = k.shape[2]
+    top_k = idx.shape[-1]
+    if top_k % 4 == 0 and min(top_k, Tk) <= LISTS_MAX_DENSITY * Tk and os.environ.get("SWV_DSA_ATTN", "") != "sweep":
+        return dsa_attention_lists(q, k, v, idx, scores, selection, o)
+    return dsa_attention_masked(q, k, v, selection, o)
+
+
 def dsa_attention_masked_count(q, k, v, selection, o):
     """Diagnostic: ``dsa_attention_masked`` (unsplit) that also returns, per query row, how many keys
     the kernel treated as selected, int32 (B, Tq); must equal min(top_k, Tk) everywhere."""
@@ -287,7 +306,7 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
                                                    precollapsed=pre)
         if kv_ready is not None:
             torch.cuda.current_stream(dev).wait_event(kv_ready)
-        dsa_attention_masked(q, k, v, sel, o)
+        dsa_attention_dense(q, k, v, idx, scores, sel, o)
     else:
         idx, valid, scores = dsa_indexer_topk(q_idx, k_idx, w, top_k, workspace=ws, precollapsed=pre)
         if kv_ready is not None:

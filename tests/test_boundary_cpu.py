@@ -109,6 +109,17 @@ def test_argument_validation_happens_before_any_launch(swv):
     assert L.swv_dsa_attn_masked_fwd(*m(128, ok_strides)) == -8
     assert L.swv_dsa_attn_masked_fwd(*m(64, (ctypes.c_int64 * 4)(4096, 512, 64, 2))) == -2
     assert L.swv_dsa_attn_masked_fwd(*m(64, (ctypes.c_int64 * 4)(4096, 512, 63, 1))) == -2
+    # list-driven attention: required pointers, top_k a multiple of 4, head dim 64, scratch large enough
+    ls = lambda q_, D, K, scr, nscr: (q_, ok_strides, fake, ok_strides, fake, ok_strides, fake, fake, K, fake, fake, fake,
+                                      ok_strides, 0, 1, 2, 256, 256, D, scr, nscr, fake, null)
+    n = ctypes.c_size_t()
+    assert L.swv_dsa_attn_lists_scratch_bytes(1, 2, 256, 256, 64, ctypes.byref(n)) == 0 and n.value > 0
+    assert L.swv_dsa_attn_lists_scratch_bytes(1, 2, 0, 256, 64, ctypes.byref(n)) == -4
+    assert L.swv_dsa_attn_lists_fwd(*ls(null, 64, 64, fake, 1 << 30)) == -1
+    assert L.swv_dsa_attn_lists_fwd(*ls(fake, 64, 64, null, 1 << 30)) == -1
+    assert L.swv_dsa_attn_lists_fwd(*ls(fake, 64, 66, fake, 1 << 30)) == -8
+    assert L.swv_dsa_attn_lists_fwd(*ls(fake, 128, 64, fake, 1 << 30)) == -8
+    assert L.swv_dsa_attn_lists_fwd(*ls(fake, 64, 64, ctypes.c_void_p(0x1000), 16)) == -5
 
 
 def test_ops_refuse_cpu_tensors(swv):
