@@ -153,17 +153,19 @@ __host__ __device__ __forceinline__ uint32_t p_offset(uint32_t row, uint32_t col
 
 // ---- the tile lists: every (query tile, key tile) gets the list of its selected (row, key) pairs
 // with their routing weights, in any order, built from the ascending per-row lists.  One CTA per
-// query tile, one thread per row; the rows advance through their lists together, so the entries of
-// a tile are written within a short time of each other.
-__global__ void __launch_bounds__(kTile)
+// query tile, `parts` threads per row (one with many query tiles, more when few CTAs would leave the
+// GPU idle), each on a contiguous share of the row's list; the rows advance through their lists
+// together, so the entries of a tile are written within a short time of each other.
+__global__ void __launch_bounds__(1024)
     dsa_tile_lists_kernel(const int32_t* __restrict__ idx, const float* __restrict__ rw, int top_k, int n_valid, int Tq,
-                          int nQT, int nKT, int cap, uint32_t* __restrict__ tl_cnt, uint2* __restrict__ tl_ent,
-                          uint32_t* __restrict__ tl_over) {
+                          int nQT, int nKT, int cap, int parts, uint32_t* __restrict__ tl_cnt,
+                          uint2* __restrict__ tl_ent, uint32_t* __restrict__ tl_over) {
   extern __shared__ uint32_t cnt_s[];          // [nKT]
   const int b = blockIdx.x / nQT, qt = blockIdx.x % nQT;
-  const int row = threadIdx.x;
+  const int row = threadIdx.x & (kTile - 1);
+  const int part = threadIdx.x >> 7;
   const int qrow = qt * kTile + row;
-  for (int i = threadIdx.x; i < nKT; i += kTile) cnt_s[i] = 0u;
+  for (int i = threadIdx.x; i < nKT; i += blockDim.x) cnt_s[i] = 0u;
   __shared__ uint32_t over_s;
   if (threadIdx.x == 0) over_s = 0u;
   __syncthreads();
@@ -173,7 +175,10 @@ __global__ void __launch_bounds__(kTile)
     const int4* ip = reinterpret_cast<const int4*>(idx + grow * top_k);
     const float4* wp = reinterpret_cast<const float4*>(rw + grow * top_k);
     bool over = false;
-    for (int s = 0; s < n_valid; s += 4) {
+    const int groups = (n_valid + 3) >> 2;
+    const int s0 = 4 * static_cast<int>(static_cast<int64_t>(groups) * part / parts);
+    const int s1 = min(n_valid, 4 * static_cast<int>(static_cast<int64_t>(groups) * (part + 1) / parts));
+    for (int s = s0; s < s1; s += 4) {
       const int4 k4 = __ldg(ip + (s >> 2));
       const float4 w4 = __ldg(wp + (s >> 2));
       const int kk[4] = {k4.x, k4.y, k4.z, k4.w};
@@ -197,7 +202,7 @@ __global__ void __launch_bounds__(kTile)
     if (over) over_s = 1u;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < nKT; i += kTile) tl_cnt[tile0 + i] = min(cnt_s[i], static_cast<uint32_t>(cap));
+  for (int i = threadIdx.x; i < nKT; i += blockDim.x) tl_cnt[tile0 + i] = min(cnt_s[i], static_cast<uint32_t>(cap));
   if (threadIdx.x == 0) tl_over[blockIdx.x] = over_s;
 }
 
@@ -815,8 +820,10 @@ int dsa_attn_lists_impl(const void* q, const int64_t* qs, const void* k, const i
   // the per-tile lists from the per-row lists
   const int n_valid = top_k < Tk ? top_k : Tk;
   if (static_cast<size_t>(p.nKT) * 4 > 48 * 1024) return SWV_ERR_TOO_LARGE;
-  dsa_tile_lists_kernel<<<static_cast<unsigned>(B) * p.nQT, kTile, static_cast<size_t>(p.nKT) * 4, st>>>(
-      idx, rw, top_k, n_valid, Tq, p.nQT, p.nKT, L.cap, tl_cnt, tl_ent, tl_over);
+  int parts = (4 * sm_count() + B * p.nQT - 1) / (B * p.nQT);      // aim at four 128-thread groups per SM
+  parts = parts < 1 ? 1 : (parts > 8 ? 8 : parts);
+  dsa_tile_lists_kernel<<<static_cast<unsigned>(B) * p.nQT, kTile * parts, static_cast<size_t>(p.nKT) * 4, st>>>(
+      idx, rw, top_k, n_valid, Tq, p.nQT, p.nKT, L.cap, parts, tl_cnt, tl_ent, tl_over);
   SWV_CUDA_OK(cudaGetLastError());
   rc = dsa_key_norm_max(k, ks, B, H, Tk, kmax2, st);
   if (rc != SWV_OK) return rc;
