@@ -247,13 +247,8 @@ __device__ __forceinline__ void window_update(const uint32_t (&r0)[32], uint32_t
   for (int i = 0; i < 32; ++i) {
     int t = static_cast<int>(relu_bits(r0[i]) - lo);          // both < 2^31: negative iff below the window
     if (CHECK && i >= nvalid) t = -1;
-#ifdef SWV_SPEC_SKIP_BELOW
-    // scores below the window (the large majority) are not counted: nothing reads that counter
-    if (t >= 0) red_inc_shared(hrow + 4u + static_cast<uint32_t>(min(t >> 16, 256) << 2));
-#else
     const int bin = min(max(t >> 16, -1), 256);               // arithmetic shift keeps the sign
     red_inc_shared(hrow + 4u + static_cast<uint32_t>(bin << 2));
-#endif
   }
 }
 
@@ -530,10 +525,6 @@ __global__ void __launch_bounds__(576, 1)
       const uint32_t prefix = row_ok ? p.st_prefix[grow] : 0xFFFFu;
       const uint32_t lo = prefix << 16;
       uint16_t* lrow = list + row * kListStride;
-      // bucket [lo, lo + 2^16) of bit patterns as floats: -(float just below each edge) * 2^60
-      const bool fma_test = lo >= 0x36800000u && lo < 0x60000000u;    // 4e-6 <= edge < 2^65 (the products stay finite)
-      const float neg_a = -__uint_as_float(lo - 1u) * 0x1p60f;
-      const float neg_b = -__uint_as_float(lo + 65535u) * 0x1p60f;
       for (int j = 0; j < nKT; ++j) {
         const int a = j & 1;
         if (!mbar_wait_bounded(&ctl->acc_full[a], (j >> 1) & 1, abort_flag)) {
@@ -571,47 +562,8 @@ __global__ void __launch_bounds__(576, 1)
             }
           }
         };
-        // Full chunks first test on the FMA pipe (integer compares run at half rate and bound this
-        // pass): with a = the float just below the bucket's low edge and b = the float just below its
-        // high edge, saturate((s - a) * 2^60) - saturate((s - b) * 2^60) is exactly 1 for a score inside
-        // the bucket and 0 outside (one ulp of a score >= 4e-6 times 2^60 is far above 1; buckets
-        // nearer to zero take the integer scan).  Eight scores share a sum; only a group whose sum
-        // is not zero is scanned with integer arithmetic.
-        if (nvalid >= 32 && fma_test) {
-          float acc[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float sum = 0.f;
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float sc = __uint_as_float(r0[g * 8 + q]);
-              float sa, sb;
-              asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(sa) : "f"(sc), "f"(neg_a));
-              asm("fma.rn.sat.f32 %0, %1, 0f5D800000, %2;" : "=f"(sb) : "f"(sc), "f"(neg_b));
-              sum += sa - sb;
-            }
-            acc[g] = sum;
-          }
-          if ((acc[0] + acc[1]) + (acc[2] + acc[3]) > 0.f) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (acc[g] > 0.f) {
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                  const uint32_t t = relu_bits(r0[g * 8 + q]) - lo;
-                  if (t < 65536u) {
-                    const uint32_t pos = atomicAdd(cnt + row, 1u);
-                    if (pos < kListCap) lrow[pos] = static_cast<uint16_t>(t);
-                  }
-                }
-              }
-            }
-          }
-        } else if (nvalid >= 32) {
-          scan(std::false_type{});
-        } else {
-          scan(std::true_type{});
-        }
+        if (nvalid >= 32) scan(std::false_type{});
+        else scan(std::true_type{});
       }
       asm volatile("bar.sync 1, 512;" ::: "memory");
       uint32_t n = cnt[row];
