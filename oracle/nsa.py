@@ -1,4 +1,4 @@
-"""Builder-defined CPU oracle of NSA-style attention (compressed + selected + sliding-window
+"""Library-defined CPU oracle of NSA-style attention (compressed + selected + sliding-window
 branches, sigmoid gate).
 
 TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).  PARITY UNPINNED: the reference contains

@@ -87,7 +87,7 @@ def expand_block_mask(row_ptr, col_idx, block: int, Tq: int, Tk: int, rows=None)
 
 
 def block_sparse_attention(q, k, v, row_ptr, col_idx, block, dtype=torch.float32):
-    """Builder-defined oracle ("parity unpinned": no such code in the reference).
+    """Library-defined oracle ("parity unpinned": no such code in the reference).
 
     Plain softmax attention restricted to the listed key blocks; q (H,Tq,D),
     k, v (H,Tk,D).  Equivalent to dense SDPA under the expanded block mask, the

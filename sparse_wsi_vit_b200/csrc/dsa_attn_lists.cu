@@ -217,6 +217,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   ListCtl* ctl = reinterpret_cast<ListCtl*>(smem + kLOffCtl);
 
+#ifdef SWV_PROFILE
+  const long long t_cta0 = clock64();
+#endif
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int cta = kSplit ? blockIdx.x / p.split : blockIdx.x;     // (batch, query tile, head pair)
@@ -306,6 +309,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
   tc_fence_after();
   const bool skip = *reinterpret_cast<volatile uint32_t*>(&ctl->cta_flag) != 0u;
   if (skip && threadIdx.x == 0 && part == 0) p.flags[cta] = 1u;
+#ifdef SWV_PROFILE
+  const long long t_cta1 = clock64();
+#endif
 
   if (skip) {
     // nothing: the masked kernel redoes this (query tile, head pair)
@@ -700,6 +706,9 @@ __global__ void __launch_bounds__(kLThreads, 1)
   }
 
   // ---------------------------------------------------------------- teardown
+#ifdef SWV_PROFILE
+  const long long t_cta2 = clock64();
+#endif
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
@@ -707,6 +716,14 @@ __global__ void __launch_bounds__(kLThreads, 1)
     __syncwarp();
     tmem_dealloc(tmem_base, kLTmemCols);
   }
+#ifdef SWV_PROFILE
+  if (threadIdx.x == 64) {      // a softmax thread: [prologue, main + epilogue of this thread, teardown wait], CTA count
+    atomicAdd(&g_lists_prof[56], static_cast<unsigned long long>(t_cta1 - t_cta0));
+    atomicAdd(&g_lists_prof[57], static_cast<unsigned long long>(t_cta2 - t_cta1));
+    atomicAdd(&g_lists_prof[58], static_cast<unsigned long long>(clock64() - t_cta2));
+    atomicAdd(&g_lists_prof[59], 1ull);
+  }
+#endif
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
