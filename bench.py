@@ -528,7 +528,7 @@ def main():
                     "sparse-wsi-vit checkout; its own Triton kernels are then timed too (interpreter, 1024 tokens)")
     ap.add_argument("--top-k", type=int, default=None, help="keys per query of the dsa_fwd workload (default 2048; "
                     "e.g. --tokens 16384 --top-k 512 is a small case with the bench workload's one key in 32)")
-    ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "dsa_variants", "block_sparse", "nsa", "encoder", "static", "static2d"])
+    ap.add_argument("--workload", default="dsa_fwd", choices=["dsa_fwd", "dsa_variants", "dsa_backward", "block_sparse", "nsa", "encoder", "static", "static2d"])
     args = ap.parse_args()
     if args.top_k is not None:
         global TOP_K
@@ -536,7 +536,7 @@ def main():
     if args.workload != "dsa_fwd":
         from sparse_wsi_vit_b200.benchmarks import WORKLOADS
         kw = {}
-        if args.tokens is not None and args.workload in ("block_sparse", "dsa_variants"):
+        if args.tokens is not None and args.workload in ("block_sparse", "dsa_variants", "dsa_backward"):
             kw["sizes"] = (args.tokens,)
         elif args.tokens is not None and args.workload in ("nsa", "static"):
             kw["tokens"] = args.tokens

@@ -278,5 +278,38 @@ def dsa_variants(steps=3, warmup=1, sizes=(16384, 65536, 131072)):
         print(json.dumps(line), flush=True)
 
 
-WORKLOADS = {"dsa_variants": dsa_variants, "block_sparse": block_sparse_sweep, "nsa": nsa_forward, "encoder": encoder_slides,
+def dsa_backward(steps=3, warmup=1, sizes=(16384, 65536)):
+    """The two backward operators on the bench shapes (8 heads x 64, 4 x 64 indexer, top-2048, bf16
+    activations, fp32 gradients): gradients of the routing-weighted attention w.r.t. q, k, v and the
+    routing weights, and of the indexer w.r.t. its projections and head weights."""
+    from . import ops
+    dev = torch.device("cuda", 0)
+    H, D, IH, ID, K = 8, 64, 4, 64, 2048
+    for T in sizes:
+        g = torch.Generator().manual_seed(0)
+        q = (torch.randn(1, T, H, D, generator=g) / 8).to(torch.bfloat16).to(dev).transpose(1, 2)
+        k = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16).to(dev).transpose(1, 2)
+        v = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16).to(dev).transpose(1, 2)
+        qi = (torch.randn(1, T, IH, ID, generator=g) / 8).to(torch.bfloat16).to(dev)
+        ki = (torch.randn(1, T, IH, ID, generator=g) / 8).to(torch.bfloat16).to(dev)
+        w = torch.randn(IH, generator=g).to(dev)
+        idx, valid, scores, sel = ops.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+        o = torch.empty((1, H, T, D), dtype=torch.bfloat16, device=dev)
+        ops.dsa_attention_dense(q, k, v, idx, scores, sel, o)
+        d_out = torch.randn(1, T, H, D, generator=g).to(torch.bfloat16).to(dev).transpose(1, 2)
+        rw = scores * valid
+        ms_attn = _time_ms(lambda: ops.dsa_attention_bwd(d_out, q, k, v, o, idx, valid, rw), steps, warmup)
+        d_scores = torch.randn(1, T, K, generator=g).to(dev)
+        ms_idx = _time_ms(lambda: ops.dsa_indexer_bwd(d_scores, qi, ki, w, idx, valid), steps, warmup)
+        ops.check_status(dev, "dsa backward")
+        pairs = float(T) * min(K, T)
+        print(json.dumps({"workload": "dsa_backward", "tokens": T, "heads": H, "head_dim": D, "top_k": K,
+                          "attention_bwd_ms": ms_attn, "indexer_bwd_ms": ms_idx,
+                          # per selected (query, key) pair and head: q, k, v, dO rows read, dk, dv rows reduced
+                          "attention_bwd_gathered_GBps": pairs * H * D * (3 * 2 + 2 * 4) / (ms_attn * 1e-3) / 1e9}),
+              flush=True)
+        del idx, valid, scores, sel, rw, d_scores
+
+
+WORKLOADS = {"dsa_backward": dsa_backward, "dsa_variants": dsa_variants, "block_sparse": block_sparse_sweep, "nsa": nsa_forward, "encoder": encoder_slides,
              "static": static_encoder, "static2d": static2d_encoder}
