@@ -837,7 +837,9 @@ int dsa_attn_lists_impl(const void* q, const int64_t* qs, const void* k, const i
   // the per-tile lists from the per-row lists
   const int n_valid = top_k < Tk ? top_k : Tk;
   if (static_cast<size_t>(p.nKT) * 4 > 48 * 1024) return SWV_ERR_TOO_LARGE;
-  int parts = (4 * sm_count() + B * p.nQT - 1) / (B * p.nQT);      // aim at four 128-thread groups per SM
+  // one thread per row once there are two query tiles per SM (more threads per row spread the writes of
+  // a query tile over more key tiles at a time: measured slower at 512 query tiles), more with fewer
+  int parts = (2 * sm_count() + B * p.nQT - 1) / (B * p.nQT);
   parts = parts < 1 ? 1 : (parts > 8 ? 8 : parts);
   dsa_tile_lists_kernel<<<static_cast<unsigned>(B) * p.nQT, kTile * parts, static_cast<size_t>(p.nKT) * 4, st>>>(
       idx, rw, top_k, n_valid, Tq, p.nQT, p.nKT, L.cap, parts, tl_cnt, tl_ent, tl_over);
