@@ -500,12 +500,13 @@ def run_ours(args):
                 "other_kernels_ms": ms - attn_ms,
             }
             if lists:
-                # what bounds the list-driven kernel: shared-memory traffic per (128 x 128 tile, head pair) --
-                # K, V tiles in (64 KiB) and out to the tensor cores (K 32, V + ones 40, P 64 KiB), the fp16
-                # copy of S (64 KiB), list entries and barriers -- about 300 KiB at 128 bytes per clock and SM
+                # what bounds the list-driven kernel: the tensor pipe is occupied nearly all the time (24 MMA
+                # instructions per (128 x 128 tile, head pair): 2 x 4 for Q K^T, 2 x 8 for P [V | 1]) although its
+                # math units are active only ~40 % of it.  Those 24 instructions take 1634 cycles when nothing
+                # else runs on the SM (micro-benchmark); the floor below is that figure over all tile pairs.
                 tiles = (T / 128.0) ** 2 * (H / 2)
-                line["roofline"]["smem_floor_ms"] = tiles * 300.0 * 1024 / 128 / (148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3
-                line["roofline"]["smem_frac"] = line["roofline"]["smem_floor_ms"] / attn_ms
+                line["roofline"]["mma_issue_floor_ms"] = tiles * 1634.0 / (148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3
+                line["roofline"]["mma_issue_frac"] = line["roofline"]["mma_issue_floor_ms"] / attn_ms
             else:
                 # what bounds the sweep: one exp per (query, key, head) on the 16 exp lanes per SM
                 line["roofline"]["exp_unit_floor_ms"] = T * float(T) * H / (16.0 * 148 * (clocks.get("sm_mhz") or 1965.0) * 1e6) * 1e3
