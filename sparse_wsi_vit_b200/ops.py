@@ -242,6 +242,9 @@ def dsa_attention_lists(q, k, v, idx, rw, selection, o):
 # exponential per (query, key, head).  Measured on B200 (8 heads, top-2048): the lists win at 65536
 # tokens (one key in 32: 9.5 + 0.8 ms against 13.1-14.5 ms) and lose at 32768 (one in 16).
 LISTS_MAX_DENSITY = 1.0 / 24.0
+# The tile lists take (Tq / 128) * (Tk / 128) * capacity * 8 bytes (1.6 GB at 65536 tokens, 9.7 GB at
+# 262144); beyond this the fused path stays with the dense sweep.
+LISTS_MAX_SCRATCH_BYTES = 16 << 30
 
 
 def dsa_attention_dense(q, k, v, idx, scores, selection, o):
@@ -249,10 +252,15 @@ def dsa_attention_dense(q, k, v, idx, scores, selection, o):
     (``dsa_attention_lists``) for sparse selections, the dense sweep (``dsa_attention_masked``)
     otherwise.  ``idx`` / ``scores`` / ``selection`` as ``dsa_indexer_topk(..., want_mask=True)``
     returns them (slots beyond min(top_k, Tk) are ignored, so ``scores`` serve as routing weights)."""
+    B, H, Tq, _ = q.shape
     Tk = k.shape[2]
     top_k = idx.shape[-1]
     if top_k % 4 == 0 and min(top_k, Tk) <= LISTS_MAX_DENSITY * Tk and os.environ.get("SWV_DSA_ATTN", "") != "sweep":
-        return dsa_attention_lists(q, k, v, idx, scores, selection, o)
+        nscr = ctypes.c_size_t()
+        check(lib.swv_dsa_attn_lists_scratch_bytes(B, H, Tq, Tk, top_k, ctypes.byref(nscr)),
+              "swv_dsa_attn_lists_scratch_bytes")
+        if nscr.value <= LISTS_MAX_SCRATCH_BYTES:
+            return dsa_attention_lists(q, k, v, idx, scores, selection, o)
     return dsa_attention_masked(q, k, v, selection, o)
 
 
