@@ -72,7 +72,7 @@ int nsa_attn_impl(const void* q, const int64_t* qs, const void* k, const int64_t
 
 extern "C" {
 
-int swv_version(void) { return 101; }
+int swv_version(void) { return 102; }
 
 const char* swv_strerror(int code) {
   switch (code) {
