@@ -1,27 +1,31 @@
-// DSA attention over the indexer's ASCENDING key lists as dense tensor-core tiles with a SPARSE
-// softmax (the attention step of the reference's DSAAttentionFunction.forward, kernels.py:769-810,
-// 450-564, for bf16 inputs with head dim 64).
+// DSA attention over the indexer's key lists as dense tensor-core tiles with a SPARSE softmax (the
+// attention step of the reference's DSAAttentionFunction.forward, kernels.py:769-810, 450-564, for
+// bf16 inputs with head dim 64).
 //
 // One CTA owns 128 query rows of one head pair and sweeps all key tiles, like dsa_attn_masked_kernel:
-//   S_h = Q_h K_h^T   tcgen05.mma, Q resident in TMEM (A operand), K tiles by TMA, fp32 into TMEM
-//   O_h += P_h V_h    tcgen05.mma, P in shared memory, V tiles by TMA, O resident in TMEM
-// but nothing is computed per (query, key) pair on the CUDA cores.  A row selects 1 key in 32, so a
-// thread (one query row of one head) copies its row of S out of TMEM into a private strip of shared
-// memory (as fp16, the only dense step), then walks its own key list -- which is sorted, so the
-// entries of the current tile are the next few -- and for each of them reads the logit at that
-// column, takes ONE exponential, multiplies by the routing weight from the list and stores the
-// bf16 product into the (otherwise zero) P tile.  Per tile and head that is 128 x 4 exponentials
-// instead of 128 x 128, and no recomputation of the indexer scores: membership and weights come from
-// the lists.
+//   S_h = Q_h K_h^T        tcgen05.mma, Q resident in TMEM (A operand), K tiles by TMA, fp32 into TMEM
+//   O_h += P_h [V_h | 1]   tcgen05.mma, P in shared memory, V tiles by TMA, O resident in TMEM; the
+//                          accumulator is 80 wide, its column 64 collects the row sums of P
+// but only the SELECTED (query, key) pairs are touched on the CUDA cores.  A row selects 1 key in 32
+// or fewer, i.e. a 128 x 128 tile holds ~512 selected pairs.  dsa_tile_lists_kernel first turns the
+// per-row lists (idx, routing weights) into one list per (query tile, key tile).  Per tile the 256
+// softmax threads then
+//   1. copy S_h out of TMEM into shared memory as fp16, every thread its own row of one head (the
+//      only dense step: conversions, no exponentials);
+//   2. clear the entries of P they wrote for the previous tile (once PV of that tile has retired);
+//   3. share the tile's pairs evenly (2-3 each, loaded a tile ahead): per pair and head one logit
+//      read, ONE exponential, times the routing weight, one bf16 store into the otherwise zero P tile.
+// Per tile and head that is ~512 exponentials instead of 128 x 128, with no recomputation of the
+// indexer scores: membership and weights come from the lists.
 //
-// Stabiliser: p' = 2^(s*c - bound) with `bound` a Cauchy-Schwarz bound of the row's logits (no
-// running maximum, no rescaling of O); the exact maximum m over the row's valid selected logits
-// is tracked beside it and the reference's clamp is applied at the end:
-//   out = O' * 2^(bound - m) / max(l' * 2^(bound - m), 1e-6).
-// A CTA with a row whose bound exceeds kMaxBound writes nothing and raises its entry of `flags`; the
-// host then runs dsa_attn_masked_kernel for the flagged CTAs only.
+// Stabiliser: p' = 2^(s*c - bound) with `bound` a Cauchy-Schwarz bound of the row's logits (no running
+// maximum, no rescaling of O).  out = O' / l'.  The reference's clamp max(l, 1e-6) acts on
+// l = l' * 2^(bound - m) >= l', so it cannot bind when l' >= 1e-6; l' == 0 means every weight of the
+// row is zero (output 0).  A (query tile, head pair) with a row in between, with a bound above
+// kLMaxBound or with an over-full tile list raises its entry of `flags`; the host then runs
+// dsa_attn_masked_kernel for the flagged ones only.
 //
-// TMEM (512 columns allocated): Q_h bf16x2 [32h, +32) | S_h fp32 [64 + 128h, +128) | O_h fp32 [320 + 64h, +64).
+// TMEM (512 columns allocated): Q_h bf16x2 [32h, +32) | S_h fp32 [64 + 128h, +128) | O_h fp32 [320 + 80h, +80).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
