@@ -232,10 +232,11 @@ int swv_dsa_attn_masked_count_fwd(const void* q, const int64_t q_strides[4], con
  * swv_dsa_indexer_topk_fwd writes: bf16 q, k, v, head dim 64).  Same result as
  * swv_dsa_attn_masked_fwd; membership and routing weights are READ from the lists instead of being
  * recomputed from the indexer vectors:
- *   idx  (B, Tq, top_k) int32 contiguous, every row strictly ASCENDING over its first min(top_k, Tk)
- *        slots (the rest is ignored); top_k a multiple of 4, 16-byte aligned;
+ *   idx  (B, Tq, top_k) int32 contiguous: the keys of every row in its first min(top_k, Tk) slots (the
+ *        rest is ignored), in any order, each key at most once; top_k a multiple of 4, 16-byte aligned;
  *   rw   (B, Tq, top_k) fp32 contiguous routing weights of those slots (scores * valid).
- * A list that is not ascending gives a wrong result for that row but no invalid access.
+ * A key listed twice in a row counts once (the reference would add it twice); a key index outside
+ * [0, Tk) is dropped.
  * `maskbits` and `workspace` are the ones the indexer call filled: a (query tile, head pair) whose
  * logits cannot be bounded below 2^40 is left to the kernel of swv_dsa_attn_masked_fwd, which this
  * entry launches behind its own for those tiles only.  `scratch` (256-byte aligned, at least

@@ -156,7 +156,7 @@ __host__ __device__ __forceinline__ uint32_t p_offset(uint32_t row, uint32_t col
 }
 
 // ---- the tile lists: every (query tile, key tile) gets the list of its selected (row, key) pairs
-// with their routing weights, in any order, built from the ascending per-row lists.  One CTA per
+// with their routing weights, in any order, built from the per-row lists.  One CTA per
 // query tile, `parts` threads per row (one with many query tiles, more when few CTAs would leave the
 // GPU idle), each on a contiguous share of the row's list; the rows advance through their lists
 // together, so the entries of a tile are written within a short time of each other.

@@ -207,7 +207,7 @@ def dsa_attention_masked(q, k, v, selection, o):
 
 
 def dsa_attention_lists(q, k, v, idx, rw, selection, o):
-    """The same attention as ``dsa_attention_masked`` driven by the indexer's ascending key lists:
+    """The same attention as ``dsa_attention_masked`` driven by the indexer's key lists:
     dense tensor-core tiles, one exponential per SELECTED key (``idx``, ``rw`` (B,Tq,top_k) as
     ``dsa_indexer_topk`` returns them, ``rw = scores * valid``); `selection` as for
     ``dsa_attention_masked`` (used for the few tiles whose logits cannot be bounded)."""

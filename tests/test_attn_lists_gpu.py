@@ -129,3 +129,22 @@ def test_fused_path_picks_the_kernel_by_density(swv, monkeypatch):
     o_sweep = swv.dsa_sparse_attention(q, k, v, qi, ki, w, K, out_dtype=torch.float32)
     swv.check_status(_dev())
     assert float((o_lists - o_sweep).abs().max()) < 2e-3
+
+
+def test_slot_order_of_a_row_does_not_matter(swv):
+    """The per-tile lists are built from the rows' slots in whatever order they come."""
+    from sparse_wsi_vit_b200.ops import dsa_attention_lists
+    T, H, K = 2048, 2, 64
+    q, k, v, qi, ki, w = make_dsa_inputs(T, H, 64, 4, 64, seed=12, dtype=torch.bfloat16, device=_dev())
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    o1 = torch.empty((1, H, T, 64), dtype=torch.float32, device=_dev())
+    dsa_attention_lists(q, k, v, idx, scores, sel, o1)
+    g = torch.Generator(device="cpu").manual_seed(1)
+    perm = torch.stack([torch.randperm(K, generator=g) for _ in range(T)]).to(_dev())[None]
+    o2 = torch.empty_like(o1)
+    dsa_attention_lists(q, k, v, torch.gather(idx, 2, perm).contiguous(), torch.gather(scores, 2, perm).contiguous(), sel,
+                        o2)
+    swv.check_status(_dev())
+    # the same products, added by the tensor cores in the same (key) order: identical up to the order in
+    # which a tile's bf16 entries were rounded -- they are rounded one by one, so bit for bit
+    assert torch.equal(o1, o2)
