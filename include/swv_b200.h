@@ -61,6 +61,13 @@ const char* swv_strerror(int code);
  * indexer vectors swv_dsa_attn_masked_fwd reads. */
 int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes);
 
+/* The same for a call with `top_k` keys per query.  For a sparse selection on a long key range
+ * (at least 16384 keys, at most one key in 8, top_k <= 4915) it is larger than
+ * swv_dsa_workspace_bytes: swv_dsa_indexer_topk_fwd then has room for per-row candidate lists and
+ * selects in two sweeps over the score tiles instead of three (same results).  With the smaller
+ * workspace the entry takes the three-sweep form. */
+int swv_dsa_workspace_bytes_topk(int B, int Tq, int Tk, int top_k, size_t* bytes);
+
 /* Bytes of the tile-major membership bitmask for B x Tq x Tk:
  * [B][ceil(Tq/128)][ceil(Tk/128)][128 rows][4 x uint32]; bit c of word w of
  * row r says whether key 128*kt + 32*w + c is selected for query 128*qt + r. */

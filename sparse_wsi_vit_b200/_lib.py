@@ -19,7 +19,7 @@ EXPORTS = [
     "swv_nsa_importance_bytes", "swv_nsa_select_blocks_fwd", "swv_nsa_selected_attn_fwd", "swv_nsa_combine_fwd",
     "swv_nsa_workspace_bytes", "swv_nsa_attn_fwd", "swv_dsa_attn_scratch_bytes", "swv_dsa_attn_masked_count_fwd",
     "swv_dsa_attn_bwd", "swv_dsa_indexer_bwd", "swv_dsa_prologue_fwd", "swv_dsa_attn_lists_fwd",
-    "swv_dsa_attn_lists_scratch_bytes",
+    "swv_dsa_attn_lists_scratch_bytes", "swv_dsa_workspace_bytes_topk",
 ]
 
 
@@ -64,6 +64,7 @@ def _load():
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, i64p,
         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p, c_void_p]
     lib.swv_dsa_attn_lists_scratch_bytes.argtypes = [c_int, c_int, c_int, c_int, c_int, POINTER(c_size_t)]
+    lib.swv_dsa_workspace_bytes_topk.argtypes = [c_int, c_int, c_int, c_int, POINTER(c_size_t)]
     lib.swv_dsa_attn_masked_count_fwd.argtypes = [
         c_void_p, i64p, c_void_p, i64p, c_void_p, i64p, c_void_p, c_void_p, c_void_p, i64p, c_int,
         c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]

@@ -5,6 +5,7 @@
 
 namespace swv {
 int dsa_workspace_bytes_impl(int B, int Tq, int Tk, size_t* bytes);
+int dsa_workspace_bytes_topk_impl(int B, int Tq, int Tk, int top_k, size_t* bytes);
 int dsa_mask_bytes_impl(int B, int Tq, int Tk, size_t* bytes);
 int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_idx, const int64_t* ks, int dtype,
                           const float* w, int B, int Tq, int Tk, int IH, int ID, int top_k, int32_t* idx,
@@ -100,6 +101,10 @@ const char* swv_strerror(int code) {
 
 int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes) {
   return swv::dsa_workspace_bytes_impl(B, Tq, Tk, bytes);
+}
+
+int swv_dsa_workspace_bytes_topk(int B, int Tq, int Tk, int top_k, size_t* bytes) {
+  return swv::dsa_workspace_bytes_topk_impl(B, Tq, Tk, top_k, bytes);
 }
 
 int swv_dsa_mask_bytes(int B, int Tq, int Tk, size_t* bytes) { return swv::dsa_mask_bytes_impl(B, Tq, Tk, bytes); }

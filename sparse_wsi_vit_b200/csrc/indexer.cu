@@ -132,8 +132,9 @@ constexpr int kListStride = 513;                   // uint16 per row (+1: bank s
 constexpr int kListBytes = kTile * kListStride * 2;
 constexpr int kHistBytes = (kTile * kHistStride * 4 > kListBytes + kTile * 4) ? kTile * kHistStride * 4
                                                                               : kListBytes + kTile * 4;
-constexpr int kKindFirst = 0, kKindMid = 1, kKindCand = 2, kKindSpec = 3;
+constexpr int kKindFirst = 0, kKindMid = 1, kKindCand = 2, kKindSpec = 3, kKindEstimate = 4;
 constexpr int kSampleTiles = 8;                    // speculative pass: key tiles sampled for the top-byte guess
+constexpr int kEstimateTiles = 32;                 // estimate pass: key tiles sampled (evenly spread over the key range)
 constexpr int kTmemCols = 256;                     // two 128-column score buffers
 
 struct IndexerParams {
@@ -164,6 +165,17 @@ struct IndexerParams {
   float* scores;
   uint32_t* maskbits;     // may be null
   int* status;
+  // Estimate / collect / select (the short form of the selection for sparse top-k on long key ranges):
+  // the estimate pass leaves a LOWER bound of every row's threshold in st_prefix (the value at
+  // rank_num / rank_den times the row's rank in a sample of the keys); the collect pass (EMIT with
+  // `collect` set) lists every key at or above it -- a superset of the selection, in ascending key
+  // order, per part -- and a per-row kernel selects the exact top-k from those lists.
+  int collect;                   // EMIT: write candidates instead of the final lists
+  int rank_num, rank_den;        // ESTIMATE: safety factor on the rank
+  int cand_cap;                  // candidates per (row, part)
+  int32_t* cand_idx;             // [B*Tq][split][cand_cap]
+  float* cand_sc;                // [B*Tq][split][cand_cap]
+  uint32_t* cand_cnt;            // [B*Tq][split] candidates found (may exceed cand_cap: the tile is flagged then)
 };
 
 struct TileSmemCtl {
@@ -269,13 +281,13 @@ __global__ void __launch_bounds__(576, 1)
 
   const int tile = blockIdx.x / p.split;         // (batch, query tile)
   const int part = blockIdx.x - tile * p.split;  // which share of the key range
-  if (MODE == kModeHist && p.only_flagged != 0 && p.flags_in[tile] == 0u) return;
+  if (p.only_flagged != 0 && p.flags_in[tile] == 0u) return;
   // Which launches split the key range: the speculative pass always; the candidate pass unless the
   // speculative pass failed for the tile; emit unless the candidate pass said otherwise; the
   // classic histogram passes never.  An unsplit tile is swept by part 0 alone.
   bool use_split = false;
   if (p.split > 1) {
-    if (MODE == kModeEmit) use_split = p.flags_unsplit[tile] == 0u;
+    if (MODE == kModeEmit) use_split = p.collect != 0 || p.flags_unsplit[tile] == 0u;
     else if (p.kind == kKindSpec) use_split = true;
     else if (p.kind == kKindCand) use_split = p.flags_spec[tile] == 0u;
     if (!use_split && part != 0) return;
@@ -289,9 +301,13 @@ __global__ void __launch_bounds__(576, 1)
   const int nKT = (use_split ? (part == 0 ? p.nKT0 : p.nKT - p.nKT0) : p.nKT);   // key tiles of this CTA
   // The speculative pass first streams a sample of nSample key tiles twice (top byte, then second
   // byte of every row's estimated threshold; the same tiles for every part), then its key range.
-  const int nSample = (MODE == kModeHist && p.kind == kKindSpec) ? min(p.nKT, kSampleTiles) : 0;
+  const bool estimate = MODE == kModeHist && p.kind == kKindEstimate;
+  const int nSample = (MODE == kModeHist && p.kind == kKindSpec) ? min(p.nKT, kSampleTiles)
+                      : estimate                                 ? min(p.nKT, kEstimateTiles)
+                                                                 : 0;
   const int nPre = 2 * nSample;
-  const int nIt = nKT + nPre;
+  const int nIt = estimate ? nPre : nKT + nPre;       // the estimate pass streams only its sample
+  const int sample_step = estimate ? p.nKT / nSample : 1;   // ... spread evenly over the key range
 
   if (threadIdx.x == 0) {
     ctl->overflow = 0;
@@ -326,7 +342,7 @@ __global__ void __launch_bounds__(576, 1)
       tma_load_3d(sm_q, &tm_q, &ctl->q_full, 0, qt * kTile, b);
       tma_load_3d(sm_q + kTileBytes / 2, &tm_q, &ctl->q_full, 32, qt * kTile, b);
       for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? (it < nSample ? it : it - nSample) : kt0 + it - nPre;
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) * sample_step : kt0 + it - nPre;
         const int s = it % kStages;
         if (!mbar_wait_bounded(&ctl->k_empty[s], ((it / kStages) & 1) ^ 1, abort_flag)) {
           record_status(p.status, kDevWaitStageEmpty);
@@ -378,7 +394,7 @@ __global__ void __launch_bounds__(576, 1)
     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
     bool ok = true;
 
-    if (MODE == kModeHist && p.kind == kKindSpec) {
+    if (MODE == kModeHist && (p.kind == kKindSpec || p.kind == kKindEstimate)) {
       // Speculative fusion of the two first radix passes.  Phase 1 estimates, per row, the top 16
       // bits of the K-th largest score from a sample of key tiles (rank scaled to the sample; two
       // 8-bit histogram rounds).  Phase 2 streams all keys against a 2^24-wide window of bit
@@ -394,39 +410,43 @@ __global__ void __launch_bounds__(576, 1)
       const uint32_t hrow_s = smem_u32(hrow);
       const uint32_t k_eff = static_cast<uint32_t>(min(p.top_k, p.Tk));
       uint32_t zeros = 0, lo = 0, rank = 1, est_hi = 0;
-      for (int it = 0; it < nIt; ++it) {
-        const int j = it < nPre ? (it < nSample ? it : it - nSample) : kt0 + it - nPre;
-        const int a = it & 1;
-        if (it == nSample || it == nPre) {
-          // ---- end of a sample round: take the digit that holds the scaled rank, clear the histogram
-          if (it == nSample) {
-            if (zeros != 0u) atomicAdd(hrow, zeros);
-            const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nSample * kTile));
-            rank = static_cast<uint32_t>((static_cast<uint64_t>(k_eff) * n_s + p.Tk - 1) / p.Tk);
-            rank = max(rank, 1u);
-          }
-          asm volatile("bar.sync 1, 512;" ::: "memory");
-          uint32_t cum = 0, digit = 0;
-          for (int bin = 255; bin >= 0; --bin) {
-            const uint32_t c = hrow[bin];
-            if (cum + c >= rank) {
-              digit = static_cast<uint32_t>(bin);
-              break;
-            }
-            cum += c;
-          }
-          rank -= min(cum, rank - 1u);
-          if (it == nSample) {
-            est_hi = digit;
-            lo = digit << 24;
-          } else {
-            const uint32_t est16 = (est_hi << 8) | digit;
-            lo = (est16 > 128u ? est16 - 128u : 0u) << 16;
-          }
-          asm volatile("bar.sync 1, 512;" ::: "memory");
-          for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
-          asm volatile("bar.sync 1, 512;" ::: "memory");
+      // end of a sample round: take the digit that holds the scaled rank, clear the histogram
+      auto end_round = [&](bool first_round) {
+        if (first_round) {
+          if (zeros != 0u) atomicAdd(hrow, zeros);
+          const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nSample * kTile));
+          uint64_t want = static_cast<uint64_t>(k_eff) * n_s;
+          if (estimate) want = want * static_cast<uint32_t>(p.rank_num) / static_cast<uint32_t>(p.rank_den);
+          rank = static_cast<uint32_t>((want + p.Tk - 1) / p.Tk);
+          rank = max(rank, 1u);
         }
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        uint32_t cum = 0, digit = 0;
+        for (int bin = 255; bin >= 0; --bin) {
+          const uint32_t c = hrow[bin];
+          if (cum + c >= rank) {
+            digit = static_cast<uint32_t>(bin);
+            break;
+          }
+          cum += c;
+        }
+        rank -= min(cum, rank - 1u);
+        if (first_round) {
+          est_hi = digit;
+          lo = digit << 24;
+        } else {
+          const uint32_t est16 = (est_hi << 8) | digit;
+          if (estimate) lo = est16 << 16;                 // the low edge of the bucket that holds the scaled rank
+          else lo = (est16 > 128u ? est16 - 128u : 0u) << 16;
+        }
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        for (int i = et; i < kTile * kHistStride; i += 512) sm_hist[i] = 0u;
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+      };
+      for (int it = 0; it < nIt; ++it) {
+        const int j = it < nPre ? (it < nSample ? it : it - nSample) * sample_step : kt0 + it - nPre;
+        const int a = it & 1;
+        if (it == nSample || it == nPre) end_round(it == nSample);
         // (a wait that gave up keeps looping without work: every thread passes the same barriers)
         if (ok && !mbar_wait_bounded(&ctl->acc_full[a], (it >> 1) & 1, abort_flag)) {
           record_status(p.status, kDevWaitAccFull);
@@ -452,6 +472,11 @@ __global__ void __launch_bounds__(576, 1)
           else window_update<true>(r0, hrow_s, lo, nvalid);
         }
       }
+      if (estimate) {
+        // a lower bound of the row's threshold (the collect pass lists every key at or above it)
+        end_round(false);
+        if (ch == 0 && row_ok) p.st_prefix[grow] = (ok && *abort_flag == 0u) ? lo : 0u;
+      } else {
       asm volatile("bar.sync 1, 512;" ::: "memory");
       // Split key range: every part publishes its histogram; the part that arrives last adds the
       // other one's to its own and finishes the tile (the estimate, hence the window, is the same
@@ -510,6 +535,7 @@ __global__ void __launch_bounds__(576, 1)
         }
       }
       }
+      }   // (not the estimate pass)
     } else if (MODE == kModeHist && p.kind == kKindCand) {
       // Candidate pass: the top 16 bits of every row's threshold are known.  The low 16 bits of
       // the scores inside that bucket are collected per row (a few dozen on continuous data) and
@@ -702,8 +728,10 @@ __global__ void __launch_bounds__(576, 1)
       // costs the L2 a sector write each).  A tile that would overrun the ring writes directly.
       const int ch = ew >> 2;
       const uint32_t thr = row_ok ? p.st_prefix[grow] : 0xFFFFFFFFu;
-      const uint32_t take_eq = row_ok ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
-      const uint32_t n_eq = row_ok ? p.st_neq[grow] : 0u;      // how many keys == thr exist
+      // (collect: `thr` is the estimate pass's lower bound, every key at or above it is listed)
+      const bool collect = p.collect != 0;
+      const uint32_t take_eq = row_ok && !collect ? p.st_kth[grow] : 0u;   // how many keys == thr to keep
+      const uint32_t n_eq = row_ok && !collect ? p.st_neq[grow] : 0u;      // how many keys == thr exist
       const bool partial = row_ok && take_eq < n_eq;            // ties cut by key index (lowest first)
       const bool warp_partial = __any_sync(0xffffffffu, partial);
       const uint32_t thr_min = partial ? thr + 1u : thr;        // member iff bits >= thr_min (+ chosen ties)
@@ -713,7 +741,7 @@ __global__ void __launch_bounds__(576, 1)
       uint32_t eq_seen = 0;
       uint32_t ex_seen = 0;                                     // ties of the row left out so far (cut rows only)
       int cnt = 0;
-      if (use_split && part == 1 && row_ok) {
+      if (use_split && part == 1 && row_ok && !collect) {
         const uint32_t eq0 = p.st_eq0[grow];
         eq_seen = min(eq0, partial ? take_eq : 0xFFFFFFFFu);
         cnt = static_cast<int>(p.st_cnt0[grow] + eq_seen);
@@ -721,16 +749,20 @@ __global__ void __launch_bounds__(576, 1)
         else eq_seen = 0;
       }
       int32_t* excl_row = p.st_excl + grow * kMaxExcl;
-      int32_t* idx_row = p.idx + grow * p.top_k;
-      float* sc_row = p.scores + grow * p.top_k;
+      // collect: every part has its own list of the row; capacity cand_cap instead of top_k
+      const int cap_out = collect ? p.cand_cap : p.top_k;
+      const int64_t cand_row = (grow * p.split + part) * p.cand_cap;
+      int32_t* idx_row = collect ? p.cand_idx + cand_row : p.idx + grow * p.top_k;
+      float* sc_row = collect ? p.cand_sc + cand_row : p.scores + grow * p.top_k;
       // 32-bit shared addresses: the staging tiles share the histogram's slot, then the exchange
       // words [2][128 rows][4 quarters] x 8 B, then the two rings
       const uint32_t stage = smem_u32(sm_hist) + static_cast<uint32_t>(ew * (32 * 32) + lane * 4) * 4u;
       const uint32_t xchg = smem_u32(sm_hist) + static_cast<uint32_t>(kEpiWarps * (32 * 32)) * 4u;
       const uint32_t ring_i = xchg + 2u * kTile * 4u * 8u + static_cast<uint32_t>(row * kRingStride) * 4u;
       const uint32_t ring_s = ring_i + static_cast<uint32_t>(kTile * kRingStride) * 4u;
-      const bool vec_ok = ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.scores)) & 15) == 0 &&
-                          (p.top_k & 3) == 0;
+      const bool vec_ok = collect ? (p.cand_cap & 3) == 0
+                                  : ((reinterpret_cast<uintptr_t>(p.idx) | reinterpret_cast<uintptr_t>(p.scores)) & 15) == 0 &&
+                                        (p.top_k & 3) == 0;
       int flushed = cnt;                                        // entries of the row below this index are not this CTA's to write
       // entries [from, to) of the row leave the ring
       auto flush = [&](int from, int to) {
@@ -834,7 +866,7 @@ __global__ void __launch_bounds__(576, 1)
         }
         // (identical for the row's four threads) entries of earlier tiles are visible since the barrier
         const bool ring_ok = cnt_new - flushed <= kRing;
-        const int upto = min(ring_ok ? (cnt & ~7) : cnt, p.top_k);
+        const int upto = min(ring_ok ? (cnt & ~7) : cnt, cap_out);
         if (row_ok && ch == (j & 3) && upto > flushed) flush(flushed, upto);
         uint32_t mine = fw[0];
 #pragma unroll
@@ -842,7 +874,7 @@ __global__ void __launch_bounds__(576, 1)
         while (mine != 0u) {
           const int i = __ffs(mine) - 1;
           mine &= mine - 1u;
-          if (row_ok && off < p.top_k) {
+          if (row_ok && off < cap_out) {
             (void)checked_index(key0 + i, p.Tk, p.status);
             const uint32_t v = relu_bits(lds32(stage + static_cast<uint32_t>((i >> 2) * 32 * 16 + (i & 3) * 4)));
             if (ring_ok) {
@@ -855,7 +887,7 @@ __global__ void __launch_bounds__(576, 1)
           }
           ++off;
         }
-        flushed = ring_ok ? max(flushed, upto) : min(cnt_new, p.top_k);
+        flushed = ring_ok ? max(flushed, upto) : min(cnt_new, cap_out);
         cnt = cnt_new;
         if (mask_row != nullptr && ch == (j & 3)) {
           mask_row[static_cast<int64_t>(j) * kTile] = make_uint4(fw[0], fw[1], fw[2], fw[3]);
@@ -863,7 +895,14 @@ __global__ void __launch_bounds__(576, 1)
         __syncwarp();   // the staging tile is rewritten by the next tile
       }
       asm volatile("bar.sync %0, 128;" ::"r"(1 + quarter) : "memory");
-      if (row_ok && ch == 0) flush(flushed, min(cnt, p.top_k));
+      if (row_ok && ch == 0) flush(flushed, min(cnt, cap_out));
+      if (collect) {
+        // how many candidates this part found for the row; a list over capacity flags the query tile
+        if (row_ok && ch == 0) {
+          p.cand_cnt[grow * p.split + part] = static_cast<uint32_t>(cnt);
+          if (cnt > cap_out || !ok) p.flags_out[tile] = 1u;
+        }
+      }
     }
   }
 
@@ -873,6 +912,212 @@ __global__ void __launch_bounds__(576, 1)
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- exact top-k of every row among the candidates the collect pass listed (all keys at or above a
+// lower bound of the row's threshold, ascending per part).  One warp per row: the candidates' score
+// bits go to shared memory, a 4 x 8-bit radix select finds the k-th largest (lanes with the same digit
+// add to the histogram with one atomic), then the candidates are filtered in order: keys above the
+// threshold and the first `take` keys equal to it, ascending.  The row's membership bits are collected
+// in shared memory and written as the row's 16-byte pieces of the tile-major mask; unselected ties go
+// to the row's exclusion list.  A row with fewer than k candidates (the lower bound was too high) flags
+// its query tile for the exact passes.
+struct SelectParams {
+  int B, Tq, Tk, top_k, k_eff, nQT, nKT, split, cand_cap;
+  const int32_t* cand_idx;
+  const float* cand_sc;
+  const uint32_t* cand_cnt;
+  uint32_t* flags;             // [B*nQT]
+  int32_t* idx;
+  float* scores;
+  uint32_t *st_prefix, *st_kth, *st_neq;
+  int32_t* st_excl;
+  uint32_t* maskbits;          // may be null
+};
+constexpr int kSelWarps = 4;                      // one row per CTA of four warps (~22 KB of shared memory each)
+
+__global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const SelectParams p) {
+  extern __shared__ uint32_t sel_smem[];
+  constexpr int kThreads = 32 * kSelWarps;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t row = blockIdx.x;
+  const int cap_all = p.split * p.cand_cap;
+  uint32_t* sc_s = sel_smem;                     // the candidates' score bits, later their output slots
+  uint32_t* hist = sc_s + cap_all;               // 256 bins
+  uint32_t* xch = hist + 256;                    // 32 words of exchange between the warps
+  const int b = static_cast<int>(row / p.Tq), t = static_cast<int>(row % p.Tq);
+  const int tile = b * p.nQT + t / kTile;
+  if (*reinterpret_cast<volatile uint32_t*>(p.flags + tile) != 0u) return;
+  int n_part[2] = {0, 0};
+  for (int q = 0; q < p.split; ++q) n_part[q] = static_cast<int>(p.cand_cnt[row * p.split + q]);
+  if (n_part[0] > p.cand_cap || n_part[1] > p.cand_cap) return;      // (flagged by the collect pass)
+  const int n = n_part[0] + n_part[1];
+  if (n < p.k_eff) {
+    if (tid == 0) p.flags[tile] = 1u;
+    return;
+  }
+  const uint32_t t0 = p.st_prefix[row];
+  for (int q = 0, off = 0; q < p.split; off += n_part[q], ++q) {
+    const float* src = p.cand_sc + (row * p.split + q) * p.cand_cap;
+#pragma unroll 4
+    for (int i = tid; i < n_part[q]; i += kThreads) sc_s[off + i] = __float_as_uint(src[i]);
+  }
+  hist[tid] = 0u;
+  hist[tid + 128] = 0u;
+  if (tid < 32) xch[tid] = 0u;
+  __syncthreads();
+  // ---- k-th largest bit pattern (scores are >= 0: bit patterns order like the values).  Every
+  // candidate is >= the row's lower bound t0 and the threshold lies a little above it, so the select
+  // runs on u = bits - t0 as three 8-bit digits of a 24-bit number (candidates with u >= 2^24, far
+  // above the threshold, are only counted).
+  uint32_t kth = static_cast<uint32_t>(p.k_eff), n_eq = 0, prefix = 0;
+  {
+    uint32_t big = 0;
+    for (int i = tid; i < n; i += kThreads) big += (sc_s[i] - t0 >= (1u << 24)) ? 1u : 0u;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) big += __shfl_xor_sync(0xffffffffu, big, o);
+    if (lane == 0 && big != 0u) atomicAdd(&xch[0], big);
+    __syncthreads();
+    big = xch[0];
+    if (big >= kth) {                              // the threshold is far above the bound: leave it to the exact passes
+      if (tid == 0) p.flags[tile] = 1u;
+      return;
+    }
+    kth -= big;
+  }
+  for (int pass = 0; pass < 3; ++pass) {
+    const int shift = 16 - 8 * pass;
+    for (int i = tid; i < n; i += kThreads) {
+      const uint32_t u = sc_s[i] - t0;
+      if (u < (1u << 24) && (pass == 0 || (u >> (shift + 8)) == (prefix >> (shift + 8))))
+        atomicAdd(&hist[(u >> shift) & 255u], 1u);
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // lane l owns bins 8 * (31 - l) .. + 7: lane 0 the highest digits
+      uint32_t c = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) c += hist[(31 - lane) * 8 + i];
+      uint32_t cum = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, cum, o);
+        if (lane >= o) cum += up;
+      }
+      const uint32_t hit = __ballot_sync(0xffffffffu, cum >= kth);     // never empty: the counted candidates are >= kth
+      const int L = __ffs(hit) - 1;
+      if (lane == L) {
+        uint32_t above = cum - c;
+        for (int i = 7; i >= 0; --i) {
+          const uint32_t h = hist[(31 - lane) * 8 + i];
+          if (above + h >= kth) {
+            xch[1] = static_cast<uint32_t>((31 - lane) * 8 + i);      // the digit
+            xch[2] = above;
+            xch[3] = h;
+            break;
+          }
+          above += h;
+        }
+      }
+    }
+    __syncthreads();
+    prefix |= xch[1] << shift;
+    kth -= xch[2];
+    n_eq = xch[3];
+    __syncthreads();
+    hist[tid] = 0u;
+    hist[tid + 128] = 0u;
+    __syncthreads();
+  }
+  const uint32_t thr = prefix + t0, take = kth;  // `take` of the n_eq keys equal to the threshold are selected
+  // ---- filter, ascending.  First in shared memory only: every candidate's score is replaced by its
+  // output slot (or a code for "unselected tie" / "rejected").  Every warp takes a contiguous quarter
+  // of the candidates: the quarters are counted first (keys above the threshold, ties), then every warp
+  // knows where its quarter starts and walks it on its own.
+  constexpr uint32_t kRejected = 0xffffffffu, kCutTie = 0x80000000u;
+  const uint32_t lt = (1u << lane) - 1u;
+  {
+    const int quarter = ((n + kThreads - 1) / kThreads) * 32;       // candidates per warp, a multiple of 32
+    const int lo_i = warp * quarter, hi_i = min(n, lo_i + quarter);
+    uint32_t gt = 0, eq = 0;
+    for (int i = lo_i + lane; i < hi_i; i += 32) {
+      const uint32_t v = sc_s[i];
+      gt += v > thr ? 1u : 0u;
+      eq += v == thr ? 1u : 0u;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      gt += __shfl_xor_sync(0xffffffffu, gt, o);
+      eq += __shfl_xor_sync(0xffffffffu, eq, o);
+    }
+    if (lane == 0) {
+      xch[4 + 2 * warp] = gt;
+      xch[5 + 2 * warp] = eq;
+    }
+    __syncthreads();
+    uint32_t out = 0, eq_seen = 0, ex_seen = 0;       // totals of the quarters before this one
+    for (int w = 0; w < warp; ++w) {
+      const uint32_t g = xch[4 + 2 * w], e = xch[5 + 2 * w];
+      const uint32_t tk = min(e, take > eq_seen ? take - eq_seen : 0u);   // ties of that quarter that are selected
+      out += g + tk;
+      ex_seen += e - tk;
+      eq_seen += e;
+    }
+    for (int base = lo_i; base < hi_i; base += 32) {
+      const int i = base + lane;
+      const bool in = i < hi_i;
+      const uint32_t v = in ? sc_s[i] : 0u;
+      const bool is_eq = in && v == thr;
+      const uint32_t eq_mask = __ballot_sync(0xffffffffu, is_eq);
+      const bool taken = is_eq && eq_seen + __popc(eq_mask & lt) < take;
+      const uint32_t taken_mask = __ballot_sync(0xffffffffu, taken);
+      const bool sel = (in && v > thr) || taken;
+      const uint32_t sel_mask = __ballot_sync(0xffffffffu, sel);
+      if (in) {
+        uint32_t code = kRejected;
+        if (sel) code = out + __popc(sel_mask & lt);
+        else if (is_eq) code = kCutTie | (ex_seen + __popc((eq_mask & ~taken_mask) & lt));
+        sc_s[i] = code;
+      }
+      out += __popc(sel_mask);
+      eq_seen += __popc(eq_mask);
+      ex_seen += __popc(eq_mask & ~taken_mask);
+    }
+  }
+  __syncthreads();
+  // ---- then the outputs: independent steps over the candidate lists in global memory
+  int32_t* idx_row = p.idx + row * p.top_k;
+  float* sc_row = p.scores + row * p.top_k;
+  const int qt = t / kTile, r = t % kTile;
+  for (int q = 0, off = 0; q < p.split; off += n_part[q], ++q) {
+    const int32_t* ksrc = p.cand_idx + (row * p.split + q) * p.cand_cap;
+    const float* vsrc = p.cand_sc + (row * p.split + q) * p.cand_cap;
+#pragma unroll 4
+    for (int i = tid; i < n_part[q]; i += kThreads) {
+      const uint32_t code = sc_s[off + i];
+      const int key = ksrc[i];
+      const float val = vsrc[i];
+      if (code == kRejected || (code & kCutTie)) {
+        // the collect pass set the bit of every candidate
+        if (p.maskbits != nullptr) {
+          const size_t word = (((static_cast<size_t>(b) * p.nQT + qt) * p.nKT + (key >> 7)) * kTile + r) * 4 + ((key & 127) >> 5);
+          atomicAnd(p.maskbits + word, ~(1u << (key & 31)));
+        }
+        if (code != kRejected) {
+          const uint32_t e = code & ~kCutTie;
+          if (e < static_cast<uint32_t>(kMaxExcl)) p.st_excl[row * kMaxExcl + e] = key;
+        }
+      } else {
+        idx_row[code] = key;
+        sc_row[code] = val;
+      }
+    }
+  }
+  if (tid == 0) {
+    p.st_prefix[row] = thr;
+    p.st_kth[row] = take;
+    p.st_neq[row] = n_eq;
   }
 }
 
@@ -965,6 +1210,32 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
   return L;
 }
 
+// The short form of the selection (estimate, collect, select) needs candidate lists behind the base
+// layout: 2.5 k candidates per row (1.6 k expected), divided over the parts of a split key range.
+struct FastLayout {
+  bool ok;                 // the shape qualifies
+  int cand_cap;            // per (row, part)
+  size_t idx_off, sc_off, cnt_off, total;
+};
+static FastLayout fast_layout(int B, int Tq, int Tk, int top_k) {
+  FastLayout F;
+  const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
+  const int k_eff = top_k < Tk ? top_k : Tk;
+  const int64_t cap_all = (static_cast<int64_t>(k_eff) * 5 / 2 + 15) / 16 * 16;
+  F.ok = Tk >= 16384 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 8 <= Tk && cap_all <= 12288;
+  F.cand_cap = static_cast<int>(cap_all / L.split);
+  const size_t rows = static_cast<size_t>(B) * Tq;
+  size_t off = L.total;
+  F.idx_off = off;
+  off += align_up(rows * cap_all * 4, 1024);
+  F.sc_off = off;
+  off += align_up(rows * cap_all * 4, 1024);
+  F.cnt_off = off;
+  off += align_up(rows * L.split * 4, 1024);
+  F.total = F.ok ? off : L.total;
+  return F;
+}
+
 // Where the collapsed indexer queries / keys of the last indexer call live inside its workspace.
 void dsa_workspace_views(void* workspace, int B, int Tq, int Tk, float** wq, float** wk, uint32_t** prefix,
                          uint32_t** kth, uint32_t** neq, uint32_t** kmax2, int32_t** excl) {
@@ -987,6 +1258,13 @@ static void launch_collapse(const void* x, const int64_t* s, const float* w, flo
   const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);
   collapse_heads_kernel<T><<<blocks, threads, 0, st>>>(static_cast<const T*>(x), s[0], s[1], s[2], s[3], w, out, B,
                                                          Tn, IH, ID);
+}
+
+int dsa_workspace_bytes_topk_impl(int B, int Tq, int Tk, int top_k, size_t* bytes) {
+  if (bytes == nullptr) return SWV_ERR_NULL;
+  if (B < 1 || Tq < 1 || Tk < 1 || top_k < 1) return SWV_ERR_SHAPE;
+  *bytes = fast_layout(B, Tq, Tk, top_k).total;
+  return SWV_OK;
 }
 
 int dsa_workspace_bytes_impl(int B, int Tq, int Tk, size_t* bytes) {
@@ -1089,6 +1367,51 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   //   bytes 2-3: one candidate-list pass; tiles whose list overflowed (massive ties) redo the two
   //              classic histogram passes.
   const size_t hs = tile_smem_bytes(kModeHist);
+  p.collect = 0; p.rank_num = 1; p.rank_den = 1; p.cand_cap = 0;
+  p.cand_idx = nullptr; p.cand_sc = nullptr; p.cand_cnt = nullptr;
+  const FastLayout F = fast_layout(B, Tq, Tk, top_k);
+  if (F.ok && allow_split && workspace_bytes >= F.total) {
+    // Sparse top-k on a long key range, and the caller brought the larger workspace
+    // (swv_dsa_workspace_bytes_topk): TWO sweeps instead of three.
+    //   estimate: a lower bound of every row's threshold from a sample of 32 key tiles -- the value at
+    //             1.6 x the row's rank in the sample (5.4 standard deviations of safety at one key in 32);
+    //   collect : one sweep lists every key at or above the bound (1.6 k per row expected), ascending, and
+    //             writes their membership bits;
+    //   select  : per row, the exact k-th largest among its candidates, the final lists, the bits of the
+    //             rejected candidates cleared.
+    // A query tile with a row that found fewer than k candidates, or more than the lists hold, is
+    // flagged and redone by the four classic histogram passes and the emit pass (which return at once
+    // for unflagged tiles).
+    p.cand_cap = F.cand_cap;
+    p.cand_idx = reinterpret_cast<int32_t*>(ws + F.idx_off);
+    p.cand_sc = reinterpret_cast<float*>(ws + F.sc_off);
+    p.cand_cnt = reinterpret_cast<uint32_t*>(ws + F.cnt_off);
+    SWV_CUDA_OK(cudaMemsetAsync(flags_a, 0, static_cast<size_t>(B) * p.nQT * 4, st));
+    p.pass = 0; p.kind = kKindEstimate; p.only_flagged = 0; p.rank_num = 8; p.rank_den = 5;
+    indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+    p.collect = 1; p.flags_out = flags_a;
+    indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
+    {
+      SelectParams sp;
+      sp.B = B; sp.Tq = Tq; sp.Tk = Tk; sp.top_k = top_k; sp.k_eff = top_k < Tk ? top_k : Tk;
+      sp.nQT = p.nQT; sp.nKT = p.nKT; sp.split = L.split; sp.cand_cap = F.cand_cap;
+      sp.cand_idx = p.cand_idx; sp.cand_sc = p.cand_sc; sp.cand_cnt = p.cand_cnt;
+      sp.flags = flags_a; sp.idx = idx; sp.scores = scores;
+      sp.st_prefix = p.st_prefix; sp.st_kth = p.st_kth; sp.st_neq = p.st_neq; sp.st_excl = p.st_excl;
+      sp.maskbits = maskbits;
+      const size_t sel_smem = (static_cast<size_t>(L.split) * F.cand_cap + 256 + 32) * 4;
+      SWV_CUDA_OK(cudaFuncSetAttribute(dsa_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(sel_smem)));
+      const int64_t rows = static_cast<int64_t>(B) * Tq;
+      dsa_select_kernel<<<static_cast<unsigned>(rows), 32 * kSelWarps, sel_smem, st>>>(sp);
+    }
+    p.collect = 0; p.only_flagged = 1; p.flags_in = flags_a; p.flags_unsplit = flags_a;
+    for (int pass = 0; pass < 4; ++pass) {
+      p.pass = pass; p.kind = pass == 0 ? kKindFirst : kKindMid;
+      indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
+    }
+    indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
+  } else {
   p.pass = 1; p.kind = kKindSpec; p.only_flagged = 0; p.flags_out = flags_a;
   indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
   p.only_flagged = 1; p.flags_in = flags_a;
@@ -1105,6 +1428,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   }
   p.only_flagged = 0;
   indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
+  }
 
   const int64_t total = static_cast<int64_t>(B) * Tq * top_k;
   const int k_eff = top_k < Tk ? top_k : Tk;

@@ -60,9 +60,14 @@ def _buffer(kind, dev, nbytes):
     return buf
 
 
-def workspace_bytes(B, Tq, Tk):
+def workspace_bytes(B, Tq, Tk, top_k=None):
+    """Bytes of indexer workspace; with ``top_k`` the size that also lets a sparse selection on a long
+    key range take the two-sweep form (room for per-row candidate lists)."""
     n = ctypes.c_size_t()
-    check(lib.swv_dsa_workspace_bytes(B, Tq, Tk, ctypes.byref(n)), "swv_dsa_workspace_bytes")
+    if top_k is None:
+        check(lib.swv_dsa_workspace_bytes(B, Tq, Tk, ctypes.byref(n)), "swv_dsa_workspace_bytes")
+    else:
+        check(lib.swv_dsa_workspace_bytes_topk(B, Tq, Tk, top_k, ctypes.byref(n)), "swv_dsa_workspace_bytes_topk")
     return n.value
 
 
@@ -72,11 +77,13 @@ def mask_bytes(B, Tq, Tk):
     return n.value
 
 
-def dsa_prologue(qkv_q, qkv_k, q_idx, k_idx, w, coords=None, coord_high=1.0, theta=10000.0, skip_tokens=0):
+def dsa_prologue(qkv_q, qkv_k, q_idx, k_idx, w, coords=None, coord_high=1.0, theta=10000.0, skip_tokens=0,
+                 top_k=None):
     """Token-local prologue in one launch: optional in-place 2-D RoPE of q and k (TOKEN-major
     (B,T,H,D) views of the projection output; ``coords`` (B,T,2) or (T,2), one row per token) and the
     indexer head collapse.  Returns the indexer workspace holding the collapsed vectors; pass it to
-    ``dsa_indexer_topk(..., workspace=ws, precollapsed=True)``."""
+    ``dsa_indexer_topk(..., workspace=ws, precollapsed=True)``.  ``top_k``: size the workspace for an
+    indexer call with that many keys per query (see ``workspace_bytes``)."""
     _require_cuda(q_idx, k_idx, w)
     B, T, IH, ID = q_idx.shape
     if k_idx.shape != q_idx.shape:
@@ -84,7 +91,7 @@ def dsa_prologue(qkv_q, qkv_k, q_idx, k_idx, w, coords=None, coord_high=1.0, the
     if k_idx.dtype != q_idx.dtype:
         k_idx = k_idx.to(q_idx.dtype)
     dev = q_idx.device
-    ws = torch.empty(workspace_bytes(B, T, T), dtype=torch.uint8, device=dev)
+    ws = torch.empty(workspace_bytes(B, T, T, top_k), dtype=torch.uint8, device=dev)
     w32 = w.detach().to(torch.float32).contiguous()
     cptr, qp, kp, qs, ks, qdt, H, D = None, None, None, None, None, 0, 1, 4
     if coords is not None:
@@ -128,7 +135,7 @@ def dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=False, out=None, mask=Non
         scores = torch.empty((B, Tq, top_k), dtype=torch.float32, device=dev)
     else:
         idx, valid, scores = out
-    nws = workspace_bytes(B, Tq, Tk)
+    nws = workspace_bytes(B, Tq, Tk, top_k)
     # a selection handle keeps its own workspace (the attention reads it); plain calls share one
     if workspace is not None:
         ws = workspace
@@ -307,7 +314,8 @@ def dsa_sparse_attention(q, k, v, q_idx, k_idx, w, top_k, out_dtype=None, return
     if rope is not None or (dense and q_idx.shape == k_idx.shape and kv_ready is None):
         # one launch for the token-local steps between the projections and the indexer
         coords, coord_high, theta, skip = rope if rope is not None else (None, 1.0, 10000.0, 0)
-        ws = dsa_prologue(q.transpose(1, 2), k.transpose(1, 2), q_idx, k_idx, w, coords, coord_high, theta, skip)
+        ws = dsa_prologue(q.transpose(1, 2), k.transpose(1, 2), q_idx, k_idx, w, coords, coord_high, theta, skip,
+                          top_k=top_k)
         pre = True
     if dense:
         idx, valid, scores, sel = dsa_indexer_topk(q_idx, k_idx, w, top_k, want_mask=True, workspace=ws,
