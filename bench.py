@@ -34,15 +34,24 @@ if ROOT not in sys.path:
 
 H, D, IH, ID, TOP_K = 8, 64, 4, 64, 2048
 METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
-# kernels of this library launched per forward on one GPU: 2 head collapses, 6 radix-select tile
-# passes (4 of them return at once unless a query tile asked for the fallback), emit, valid fill,
-# key-norm maximum, attention (12; the sharded step launches the same on every rank).  When the
-# selection is sparse enough for the list-driven attention kernel: + the tile-list build and the
-# launch of the dense sweep for flagged tiles (returns at once unless a tile was flagged) = 14.
+# kernels of this library launched per forward on one GPU: 2 head collapses; the selection -- for a
+# sparse top-k on a long key range estimate, collect, select and 5 launches of the exact passes that
+# return at once unless a query tile was flagged (8), otherwise 6 radix-select tile passes (4 of them
+# returning at once unless flagged) and emit (7); valid fill; key-norm maximum; attention.  When the
+# selection is sparse enough for the list-driven attention kernel: + the tile-list build and the launch
+# of the dense sweep for flagged tiles (returns at once unless a tile was flagged).  The sharded step
+# launches the same on every rank.
 def kernels_per_step(T):
     from sparse_wsi_vit_b200 import ops
-    lists = TOP_K % 4 == 0 and min(TOP_K, T) <= ops.LISTS_MAX_DENSITY * T
-    return 14 if lists else 12
+    k_eff = min(TOP_K, T)
+    two_sweep = 49152 <= T <= 262144 and k_eff * 16 <= T and k_eff * 5 // 2 <= 12288
+    lists = TOP_K % 4 == 0 and k_eff <= ops.LISTS_MAX_DENSITY * T
+    return 2 + (8 if two_sweep else 7) + 1 + (4 if lists else 2)
+
+
+def uses_list_kernel(T):
+    from sparse_wsi_vit_b200 import ops
+    return TOP_K % 4 == 0 and min(TOP_K, T) <= ops.LISTS_MAX_DENSITY * T
 
 # DRAM bytes (read + write) of one dsa_attn_masked_kernel launch, from one-pass ncu captures
 # (dram__bytes_read.sum + dram__bytes_write.sum): 3.15 GB + 0.07 GB on the 65536-token workload -- K, V
@@ -479,7 +488,7 @@ def run_ours(args):
         }
         if world == 1:
             attn_ms = statistics.mean(a.elapsed_time(b) for a, b in zip(ev_a, ev_b))
-            lists = kernels_per_step(T) == 14
+            lists = uses_list_kernel(T)
             kept = 4.0 * T * min(TOP_K, T) * H * D
             # dense tiles on the tensor cores: the sweep multiplies Q K^T and P V over all keys (+ the
             # routing-weight tiles); the list-driven kernel Q K^T and P [V | 1] with an 80-wide accumulator

@@ -1222,7 +1222,10 @@ static FastLayout fast_layout(int B, int Tq, int Tk, int top_k) {
   const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
   const int k_eff = top_k < Tk ? top_k : Tk;
   const int64_t cap_all = (static_cast<int64_t>(k_eff) * 5 / 2 + 15) / 16 * 16;
-  F.ok = Tk >= 16384 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 8 <= Tk && cap_all <= 12288;
+  // Worth it where the sweeps dominate: the sample (2 x 32 key tiles) is a small part of a sweep and the
+  // per-row select (rows x 1.6 k candidates) is small beside one (measured: 5.3 against 6.5 ms at 65536
+  // tokens and one key in 32; slower than the three-sweep form at 16384 and 32768 tokens).
+  F.ok = Tk >= 49152 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 16 <= Tk && cap_all <= 12288;
   F.cand_cap = static_cast<int>(cap_all / L.split);
   const size_t rows = static_cast<size_t>(B) * Tq;
   size_t off = L.total;

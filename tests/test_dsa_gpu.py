@@ -413,3 +413,33 @@ def test_attention_kernel_selects_exactly_the_indexer_members(swv, T, H, K, mode
     assert float((o - o2).abs().max()) < 1e-3
     if mode in ("twins", "triplets"):
         assert float((o2 - o_list).abs().max()) < 2e-2 and float((o2 - o_list).abs().mean()) < 1e-3
+
+
+@pytest.mark.parametrize("mode", ["sample_too_high", "sample_too_low", "plain"])
+def test_two_sweep_selection_and_its_fallback(swv, mode):
+    """Sparse top-k on a long key range takes the short form of the selection: a lower bound of every
+    row's threshold from a sample of key tiles (every 12th tile at this size), one sweep that lists the
+    keys above it, a per-row exact select.  When the sample misleads -- its keys score much higher or
+    much lower than the rest -- rows find too few candidates or the lists overflow, and the query tiles
+    are redone by the exact passes.  All three cases must give the exact top-k of the library's own scores."""
+    T, K = 49152, 1024
+    q, k, v, qi, ki, w = make_dsa_inputs(T, 1, 64, 4, 64, seed=123, dtype=torch.bfloat16, device=_dev())
+    if mode != "plain":
+        tiles = ki.view(1, T // 128, 128, 4, 64)
+        scale = 3.0 if mode == "sample_too_high" else 0.05
+        tiles[:, ::12] = (tiles[:, ::12].float() * scale).to(torch.bfloat16)    # the sampled key tiles
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi, ki, w, K, want_mask=True)
+    _check(swv)
+    rows = torch.arange(0, T, 397, device=_dev())
+    full = own_scores(qi[:, rows].contiguous(), ki, w)[0].cpu()
+    ridx, rvalid, rsel = O.topk_lower_index(full, K)
+    assert torch.equal(idx[0, rows].cpu(), ridx)
+    assert torch.equal(scores[0, rows].cpu(), rsel)
+    assert bool((valid == 1).all())
+    # the membership mask agrees with the lists (the attention's dense sweep reads it)
+    o1 = torch.empty((1, 1, T, 64), dtype=torch.float32, device=_dev())
+    o2 = torch.empty_like(o1)
+    swv.dsa_attention_masked(q, k, v, sel, o1)
+    swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o2)
+    _check(swv)
+    assert float((o1 - o2).abs().max()) < 2e-2
