@@ -916,7 +916,7 @@ __global__ void __launch_bounds__(576, 1)
 }
 
 // ---- exact top-k of every row among the candidates the collect pass listed (all keys at or above a
-// lower bound of the row's threshold, ascending per part).  One warp per row: the candidates' score
+// lower bound of the row's threshold, ascending per part).  One CTA of four warps per row: the candidates' score
 // bits go to shared memory, a 4 x 8-bit radix select finds the k-th largest (lanes with the same digit
 // add to the histogram with one atomic), then the candidates are filtered in order: keys above the
 // threshold and the first `take` keys equal to it, ascending.  The row's membership bits are collected
@@ -948,7 +948,13 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   uint32_t* xch = hist + 256;                    // 32 words of exchange between the warps
   const int b = static_cast<int>(row / p.Tq), t = static_cast<int>(row % p.Tq);
   const int tile = b * p.nQT + t / kTile;
-  if (*reinterpret_cast<volatile uint32_t*>(p.flags + tile) != 0u) return;
+  // Another row of the same query tile may flag the tile while this CTA starts: ONE thread reads the
+  // flag, so the whole CTA takes the same way (threads that left alone would leave the exchange words
+  // and the histogram of the others unwritten).
+  __shared__ uint32_t tile_flagged;
+  if (tid == 0) tile_flagged = *reinterpret_cast<volatile uint32_t*>(p.flags + tile);
+  __syncthreads();
+  if (tile_flagged != 0u) return;
   int n_part[2] = {0, 0};
   for (int q = 0; q < p.split; ++q) n_part[q] = static_cast<int>(p.cand_cnt[row * p.split + q]);
   if (n_part[0] > p.cand_cap || n_part[1] > p.cand_cap) return;      // (flagged by the collect pass)
@@ -1108,7 +1114,7 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
           const uint32_t e = code & ~kCutTie;
           if (e < static_cast<uint32_t>(kMaxExcl)) p.st_excl[row * kMaxExcl + e] = key;
         }
-      } else {
+      } else if (code < static_cast<uint32_t>(p.k_eff)) {     // (always: gt + take == k_eff)
         idx_row[code] = key;
         sc_row[code] = val;
       }

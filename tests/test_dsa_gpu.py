@@ -443,3 +443,35 @@ def test_two_sweep_selection_and_its_fallback(swv, mode):
     swv.dsa_attention_gather(q, k, v, idx, valid, scores * valid, o2)
     _check(swv)
     assert float((o1 - o2).abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("scale", [1.0, 1.1, 1.15, 1.25])
+def test_two_sweep_selection_on_a_rank_share(swv, scale):
+    """One rank's share of a sharded slide: a ragged query range (49 tiles and 2 rows) against a long
+    ragged key range (448 tiles and 2 keys), the key range split over two CTAs per query tile.  The
+    sampled key tiles are scaled a little, so that the lower bound is marginal: in the same query tile
+    some rows find enough candidates and others do not (they flag the tile while their neighbours are
+    being selected)."""
+    Tq, Tk, K = 6274, 57346, 2048
+    q, k, v, qi, ki, w = make_dsa_inputs(Tk, 2, 64, 4, 64, seed=31, dtype=torch.bfloat16, device=_dev())
+    step = ((Tk + 127) // 128) // 32
+    for t in range(0, 32 * step, step):                                        # the sampled key tiles
+        ki[:, t * 128:(t + 1) * 128] = (ki[:, t * 128:(t + 1) * 128].float() * scale).to(torch.bfloat16)
+    qi_loc = qi[:, Tk - Tq:].contiguous()
+    idx, valid, scores, sel = swv.dsa_indexer_topk(qi_loc, ki, w, K, want_mask=True)
+    _check(swv)
+    assert int(idx.min()) >= 0 and int(idx.max()) < Tk
+    rows = torch.arange(0, Tq, 97, device=_dev())
+    full = own_scores(qi_loc[:, rows].contiguous(), ki, w)[0].cpu()
+    ridx, rvalid, rsel = O.topk_lower_index(full, K)
+    assert torch.equal(idx[0, rows].cpu(), ridx)
+    assert torch.equal(scores[0, rows].cpu(), rsel)
+    # every row: K distinct keys in ascending order
+    assert bool((idx[0, :, 1:] > idx[0, :, :-1]).all())
+    q_loc = q[:, :, Tk - Tq:].contiguous()
+    o1 = torch.empty((1, 2, Tq, 64), dtype=torch.float32, device=_dev())
+    o2 = torch.empty_like(o1)
+    swv.dsa_attention_masked(q_loc, k, v, sel, o1)
+    swv.dsa_attention_gather(q_loc, k, v, idx, valid, scores * valid, o2)
+    _check(swv)
+    assert float((o1 - o2).abs().max()) < 2e-2
