@@ -957,18 +957,15 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   if (tile_flagged != 0u) return;
   int n_part[2] = {0, 0};
   for (int q = 0; q < p.split; ++q) n_part[q] = static_cast<int>(p.cand_cnt[row * p.split + q]);
-  if (n_part[0] > p.cand_cap || n_part[1] > p.cand_cap) return;      // (flagged by the collect pass)
+  if (static_cast<uint32_t>(n_part[0]) > static_cast<uint32_t>(p.cand_cap) ||
+      static_cast<uint32_t>(n_part[1]) > static_cast<uint32_t>(p.cand_cap))
+    return;                                                          // (flagged by the collect pass)
   const int n = n_part[0] + n_part[1];
   if (n < p.k_eff) {
     if (tid == 0) p.flags[tile] = 1u;
     return;
   }
   const uint32_t t0 = p.st_prefix[row];
-  for (int q = 0, off = 0; q < p.split; off += n_part[q], ++q) {
-    const float* src = p.cand_sc + (row * p.split + q) * p.cand_cap;
-#pragma unroll 4
-    for (int i = tid; i < n_part[q]; i += kThreads) sc_s[off + i] = __float_as_uint(src[i]);
-  }
   hist[tid] = 0u;
   hist[tid + 128] = 0u;
   if (tid < 32) xch[tid] = 0u;
@@ -976,11 +973,31 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   // ---- k-th largest bit pattern (scores are >= 0: bit patterns order like the values).  Every
   // candidate is >= the row's lower bound t0 and the threshold lies a little above it, so the select
   // runs on u = bits - t0 as three 8-bit digits of a 24-bit number (candidates with u >= 2^24, far
-  // above the threshold, are only counted).
+  // above the threshold, are only counted).  The candidates come in with 16-byte loads (the lists
+  // start on 32-byte boundaries and their capacity is a multiple of 8, so the last load may bring up
+  // to three unused entries); the same loop counts the far-above ones and bins the first digit.
   uint32_t kth = static_cast<uint32_t>(p.k_eff), n_eq = 0, prefix = 0;
   {
     uint32_t big = 0;
-    for (int i = tid; i < n; i += kThreads) big += (sc_s[i] - t0 >= (1u << 24)) ? 1u : 0u;
+    for (int q = 0, off = 0; q < p.split; off += n_part[q], ++q) {
+      const float4* src4 = reinterpret_cast<const float4*>(p.cand_sc + (row * p.split + q) * p.cand_cap);
+      const int nq = n_part[q], n4 = (nq + 3) >> 2;
+#pragma unroll 4
+      for (int i4 = tid; i4 < n4; i4 += kThreads) {
+        const float4 x = __ldg(src4 + i4);
+        const uint32_t xb[4] = {__float_as_uint(x.x), __float_as_uint(x.y), __float_as_uint(x.z), __float_as_uint(x.w)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i = i4 * 4 + e;
+          if (i < nq) {
+            sc_s[off + i] = xb[e];
+            const uint32_t u = xb[e] - t0;
+            if (u >= (1u << 24)) ++big;
+            else atomicAdd(&hist[u >> 16], 1u);
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) big += __shfl_xor_sync(0xffffffffu, big, o);
     if (lane == 0 && big != 0u) atomicAdd(&xch[0], big);
@@ -994,12 +1011,13 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   }
   for (int pass = 0; pass < 3; ++pass) {
     const int shift = 16 - 8 * pass;
-    for (int i = tid; i < n; i += kThreads) {
-      const uint32_t u = sc_s[i] - t0;
-      if (u < (1u << 24) && (pass == 0 || (u >> (shift + 8)) == (prefix >> (shift + 8))))
-        atomicAdd(&hist[(u >> shift) & 255u], 1u);
+    if (pass > 0) {
+      for (int i = tid; i < n; i += kThreads) {
+        const uint32_t u = sc_s[i] - t0;
+        if (u < (1u << 24) && (u >> (shift + 8)) == (prefix >> (shift + 8))) atomicAdd(&hist[(u >> shift) & 255u], 1u);
+      }
+      __syncthreads();
     }
-    __syncthreads();
     if (warp == 0) {
       // lane l owns bins 8 * (31 - l) .. + 7: lane 0 the highest digits
       uint32_t c = 0;
@@ -1097,26 +1115,35 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   float* sc_row = p.scores + row * p.top_k;
   const int qt = t / kTile, r = t % kTile;
   for (int q = 0, off = 0; q < p.split; off += n_part[q], ++q) {
-    const int32_t* ksrc = p.cand_idx + (row * p.split + q) * p.cand_cap;
-    const float* vsrc = p.cand_sc + (row * p.split + q) * p.cand_cap;
-#pragma unroll 4
-    for (int i = tid; i < n_part[q]; i += kThreads) {
-      const uint32_t code = sc_s[off + i];
-      const int key = ksrc[i];
-      const float val = vsrc[i];
-      if (code == kRejected || (code & kCutTie)) {
-        // the collect pass set the bit of every candidate
-        if (p.maskbits != nullptr) {
-          const size_t word = (((static_cast<size_t>(b) * p.nQT + qt) * p.nKT + (key >> 7)) * kTile + r) * 4 + ((key & 127) >> 5);
-          atomicAnd(p.maskbits + word, ~(1u << (key & 31)));
+    const int4* ksrc4 = reinterpret_cast<const int4*>(p.cand_idx + (row * p.split + q) * p.cand_cap);
+    const float4* vsrc4 = reinterpret_cast<const float4*>(p.cand_sc + (row * p.split + q) * p.cand_cap);
+    const int nq = n_part[q], n4 = (nq + 3) >> 2;
+#pragma unroll 2
+    for (int i4 = tid; i4 < n4; i4 += kThreads) {
+      const int4 kk = __ldg(ksrc4 + i4);
+      const float4 vv = __ldg(vsrc4 + i4);
+      const int keys[4] = {kk.x, kk.y, kk.z, kk.w};
+      const float vals[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int i = i4 * 4 + e;
+        if (i >= nq) break;
+        const uint32_t code = sc_s[off + i];
+        const int key = keys[e];
+        if (code == kRejected || (code & kCutTie)) {
+          // the collect pass set the bit of every candidate
+          if (p.maskbits != nullptr) {
+            const size_t word = (((static_cast<size_t>(b) * p.nQT + qt) * p.nKT + (key >> 7)) * kTile + r) * 4 + ((key & 127) >> 5);
+            atomicAnd(p.maskbits + word, ~(1u << (key & 31)));
+          }
+          if (code != kRejected) {
+            const uint32_t ex = code & ~kCutTie;
+            if (ex < static_cast<uint32_t>(kMaxExcl)) p.st_excl[row * kMaxExcl + ex] = key;
+          }
+        } else if (code < static_cast<uint32_t>(p.k_eff)) {     // (always: gt + take == k_eff)
+          idx_row[code] = key;
+          sc_row[code] = vals[e];
         }
-        if (code != kRejected) {
-          const uint32_t e = code & ~kCutTie;
-          if (e < static_cast<uint32_t>(kMaxExcl)) p.st_excl[row * kMaxExcl + e] = key;
-        }
-      } else if (code < static_cast<uint32_t>(p.k_eff)) {     // (always: gt + take == k_eff)
-        idx_row[code] = key;
-        sc_row[code] = val;
       }
     }
   }
