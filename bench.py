@@ -44,7 +44,8 @@ METRIC = "dsa_sparse_attn_fwd_tokens_per_s"
 def kernels_per_step(T):
     from sparse_wsi_vit_b200 import ops
     k_eff = min(TOP_K, T)
-    two_sweep = 49152 <= T <= 262144 and k_eff * 16 <= T and k_eff * 5 // 2 <= 12288
+    # the library sizes a larger workspace exactly where it takes the two-sweep form of the selection
+    two_sweep = ops.workspace_bytes(1, T, T, TOP_K) > ops.workspace_bytes(1, T, T)
     lists = TOP_K % 4 == 0 and k_eff <= ops.LISTS_MAX_DENSITY * T
     return 2 + (8 if two_sweep else 7) + 1 + (4 if lists else 2)
 

@@ -16,6 +16,7 @@
 //      tile-major membership bitmask.  Ties at the threshold go to the lower key index.
 //   4. fill_valid_kernel : valid[.., s] = s < min(K, Tk); zero padding of idx/scores.
 // The N x N score matrix never reaches global memory.
+#include <cmath>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -166,12 +167,12 @@ struct IndexerParams {
   uint32_t* maskbits;     // may be null
   int* status;
   // Estimate / collect / select (the short form of the selection for sparse top-k on long key ranges):
-  // the estimate pass leaves a LOWER bound of every row's threshold in st_prefix (the value at
-  // rank_num / rank_den times the row's rank in a sample of the keys); the collect pass (EMIT with
+  // the estimate pass leaves a LOWER bound of every row's threshold in st_prefix (the value at rank
+  // `est_rank` of a sample of the keys, a little below the rank of the threshold); the collect pass (EMIT with
   // `collect` set) lists every key at or above it -- a superset of the selection, in ascending key
   // order, per part -- and a per-row kernel selects the exact top-k from those lists.
   int collect;                   // EMIT: write candidates instead of the final lists
-  int rank_num, rank_den;        // ESTIMATE: safety factor on the rank
+  int est_rank;                  // ESTIMATE: the rank (in the sample of kEstimateTiles key tiles) of the lower bound
   int cand_cap;                  // candidates per (row, part)
   int32_t* cand_idx;             // [B*Tq][split][cand_cap]
   float* cand_sc;                // [B*Tq][split][cand_cap]
@@ -415,9 +416,8 @@ __global__ void __launch_bounds__(576, 1)
         if (first_round) {
           if (zeros != 0u) atomicAdd(hrow, zeros);
           const uint32_t n_s = static_cast<uint32_t>(min(p.Tk, nSample * kTile));
-          uint64_t want = static_cast<uint64_t>(k_eff) * n_s;
-          if (estimate) want = want * static_cast<uint32_t>(p.rank_num) / static_cast<uint32_t>(p.rank_den);
-          rank = static_cast<uint32_t>((want + p.Tk - 1) / p.Tk);
+          const uint64_t want = static_cast<uint64_t>(k_eff) * n_s;
+          rank = estimate ? static_cast<uint32_t>(p.est_rank) : static_cast<uint32_t>((want + p.Tk - 1) / p.Tk);
           rank = max(rank, 1u);
         }
         asm volatile("bar.sync 1, 512;" ::: "memory");
@@ -952,11 +952,15 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
   // flag, so the whole CTA takes the same way (threads that left alone would leave the exchange words
   // and the histogram of the others unwritten).
   __shared__ uint32_t tile_flagged;
+  // (the row's counts and lower bound are asked for before the flag is waited for: one memory
+  // latency instead of three in a row)
+  int n_part[2] = {0, 0};
+  n_part[0] = static_cast<int>(__ldg(p.cand_cnt + row * p.split));
+  if (p.split > 1) n_part[1] = static_cast<int>(__ldg(p.cand_cnt + row * p.split + 1));
+  const uint32_t t0 = __ldcg(p.st_prefix + row);
   if (tid == 0) tile_flagged = *reinterpret_cast<volatile uint32_t*>(p.flags + tile);
   __syncthreads();
   if (tile_flagged != 0u) return;
-  int n_part[2] = {0, 0};
-  for (int q = 0; q < p.split; ++q) n_part[q] = static_cast<int>(p.cand_cnt[row * p.split + q]);
   if (static_cast<uint32_t>(n_part[0]) > static_cast<uint32_t>(p.cand_cap) ||
       static_cast<uint32_t>(n_part[1]) > static_cast<uint32_t>(p.cand_cap))
     return;                                                          // (flagged by the collect pass)
@@ -965,7 +969,6 @@ __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const Select
     if (tid == 0) p.flags[tile] = 1u;
     return;
   }
-  const uint32_t t0 = p.st_prefix[row];
   hist[tid] = 0u;
   hist[tid + 128] = 0u;
   if (tid < 32) xch[tid] = 0u;
@@ -1244,10 +1247,11 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
 }
 
 // The short form of the selection (estimate, collect, select) needs candidate lists behind the base
-// layout: 2.5 k candidates per row (1.6 k expected), divided over the parts of a split key range.
+// layout: 2.5 k candidates per row (1.3-1.6 k expected), divided over the parts of a split key range.
 struct FastLayout {
   bool ok;                 // the shape qualifies
   int cand_cap;            // per (row, part)
+  int est_rank;            // rank in the sample at which the estimate pass takes a row's lower bound
   size_t idx_off, sc_off, cnt_off, total;
 };
 static FastLayout fast_layout(int B, int Tq, int Tk, int top_k) {
@@ -1256,9 +1260,25 @@ static FastLayout fast_layout(int B, int Tq, int Tk, int top_k) {
   const int k_eff = top_k < Tk ? top_k : Tk;
   const int64_t cap_all = (static_cast<int64_t>(k_eff) * 5 / 2 + 15) / 16 * 16;
   // Worth it where the sweeps dominate: the sample (2 x 32 key tiles) is a small part of a sweep and the
-  // per-row select (rows x 1.6 k candidates) is small beside one (measured: 5.3 against 6.5 ms at 65536
+  // per-row select (rows x 1.5 k candidates) is small beside one (measured: 5.0 against 6.5 ms at 65536
   // tokens and one key in 32; slower than the three-sweep form at 16384 and 32768 tokens).
   F.ok = Tk >= 49152 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 16 <= Tk && cap_all <= 12288;
+  // The lower bound is the sample's value at rank r = m * mu, mu = k n_s / Tk the expected number of a
+  // row's selected keys inside the sample of n_s keys.  Too high a bound (the row finds fewer than k
+  // candidates) needs more than r of the row's selected keys inside the sample: (m - 1) sqrt(mu)
+  // standard deviations, set to 4.75 (one row in a million; a query tile has 128).  Too low a bound
+  // overflows the lists: the candidates number about m k (1 +- 1 / sqrt(r)), plus ~5 % for rounding
+  // the bound down to a multiple of 2^16 bit patterns; the capacity must lie 4 standard deviations
+  // above that, which holds from about one key in 80 on.  Sparser selections keep the three sweeps.
+  F.est_rank = 0;
+  if (F.ok) {
+    const double n_s = static_cast<double>(kEstimateTiles) * kTile;
+    const double mu = static_cast<double>(k_eff) * n_s / Tk;
+    const double r = std::ceil(mu + 4.75 * std::sqrt(mu));
+    const double z_over = (static_cast<double>(cap_all) / (1.05 * (r / mu) * k_eff) - 1.0) * std::sqrt(r);
+    F.ok = z_over >= 4.0;
+    F.est_rank = static_cast<int>(r);
+  }
   F.cand_cap = static_cast<int>(cap_all / L.split);
   const size_t rows = static_cast<size_t>(B) * Tq;
   size_t off = L.total;
@@ -1403,15 +1423,15 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
   //   bytes 2-3: one candidate-list pass; tiles whose list overflowed (massive ties) redo the two
   //              classic histogram passes.
   const size_t hs = tile_smem_bytes(kModeHist);
-  p.collect = 0; p.rank_num = 1; p.rank_den = 1; p.cand_cap = 0;
+  p.collect = 0; p.est_rank = 0; p.cand_cap = 0;
   p.cand_idx = nullptr; p.cand_sc = nullptr; p.cand_cnt = nullptr;
   const FastLayout F = fast_layout(B, Tq, Tk, top_k);
   if (F.ok && allow_split && workspace_bytes >= F.total) {
     // Sparse top-k on a long key range, and the caller brought the larger workspace
     // (swv_dsa_workspace_bytes_topk): TWO sweeps instead of three.
-    //   estimate: a lower bound of every row's threshold from a sample of 32 key tiles -- the value at
-    //             1.6 x the row's rank in the sample (5.4 standard deviations of safety at one key in 32);
-    //   collect : one sweep lists every key at or above the bound (1.6 k per row expected), ascending, and
+    //   estimate: a lower bound of every row's threshold from a sample of 32 key tiles -- the value a
+    //             little below the row's rank in the sample (4.75 standard deviations of safety);
+    //   collect : one sweep lists every key at or above the bound (1.5 k per row at one key in 32), ascending, and
     //             writes their membership bits;
     //   select  : per row, the exact k-th largest among its candidates, the final lists, the bits of the
     //             rejected candidates cleared.
@@ -1423,7 +1443,7 @@ int dsa_indexer_topk_impl(const void* q_idx, const int64_t* qs, const void* k_id
     p.cand_sc = reinterpret_cast<float*>(ws + F.sc_off);
     p.cand_cnt = reinterpret_cast<uint32_t*>(ws + F.cnt_off);
     SWV_CUDA_OK(cudaMemsetAsync(flags_a, 0, static_cast<size_t>(B) * p.nQT * 4, st));
-    p.pass = 0; p.kind = kKindEstimate; p.only_flagged = 0; p.rank_num = 8; p.rank_den = 5;
+    p.pass = 0; p.kind = kKindEstimate; p.only_flagged = 0; p.est_rank = F.est_rank;
     indexer_tiles_kernel<kModeHist><<<grid, 576, hs, st>>>(tm_q, tm_k, p);
     p.collect = 1; p.flags_out = flags_a;
     indexer_tiles_kernel<kModeEmit><<<grid, 576, tile_smem_bytes(kModeEmit), st>>>(tm_q, tm_k, p);
