@@ -1247,7 +1247,7 @@ static WorkspaceLayout workspace_layout(int B, int Tq, int Tk) {
 }
 
 // The short form of the selection (estimate, collect, select) needs candidate lists behind the base
-// layout: 2.5 k candidates per row (1.3-1.6 k expected), divided over the parts of a split key range.
+// layout: 2.0-2.5 k candidates per row (1.3-1.7 k expected), divided over the parts of a split key range.
 struct FastLayout {
   bool ok;                 // the shape qualifies
   int cand_cap;            // per (row, part)
@@ -1258,25 +1258,27 @@ static FastLayout fast_layout(int B, int Tq, int Tk, int top_k) {
   FastLayout F;
   const WorkspaceLayout L = workspace_layout(B, Tq, Tk);
   const int k_eff = top_k < Tk ? top_k : Tk;
-  const int64_t cap_all = (static_cast<int64_t>(k_eff) * 5 / 2 + 15) / 16 * 16;
   // Worth it where the sweeps dominate: the sample (2 x 32 key tiles) is a small part of a sweep and the
-  // per-row select (rows x 1.5 k candidates) is small beside one (measured: 5.0 against 6.5 ms at 65536
+  // per-row select (rows x 1.5 k candidates) is small beside one (measured: 4.7 against 6.5 ms at 65536
   // tokens and one key in 32; slower than the three-sweep form at 16384 and 32768 tokens).
-  F.ok = Tk >= 49152 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 16 <= Tk && cap_all <= 12288;
+  F.ok = Tk >= 49152 && Tk <= 262144 && static_cast<int64_t>(k_eff) * 16 <= Tk;
   // The lower bound is the sample's value at rank r = m * mu, mu = k n_s / Tk the expected number of a
   // row's selected keys inside the sample of n_s keys.  Too high a bound (the row finds fewer than k
   // candidates) needs more than r of the row's selected keys inside the sample: (m - 1) sqrt(mu)
   // standard deviations, set to 4.75 (one row in a million; a query tile has 128).  Too low a bound
   // overflows the lists: the candidates number about m k (1 +- 1 / sqrt(r)), plus ~5 % for rounding
-  // the bound down to a multiple of 2^16 bit patterns; the capacity must lie 4 standard deviations
-  // above that, which holds from about one key in 80 on.  Sparser selections keep the three sweeps.
+  // the bound down to a multiple of 2^16 bit patterns; the lists hold 4.5 standard deviations more
+  // than that (2.0 k at one key in 32, 2.4 k at one in 64), and beyond 2.5 k -- selections sparser
+  // than about one key in 70 -- the three sweeps are kept.
   F.est_rank = 0;
+  int64_t cap_all = 16;
   if (F.ok) {
     const double n_s = static_cast<double>(kEstimateTiles) * kTile;
     const double mu = static_cast<double>(k_eff) * n_s / Tk;
     const double r = std::ceil(mu + 4.75 * std::sqrt(mu));
-    const double z_over = (static_cast<double>(cap_all) / (1.05 * (r / mu) * k_eff) - 1.0) * std::sqrt(r);
-    F.ok = z_over >= 4.0;
+    const double cap = 1.05 * (r / mu) * k_eff * (1.0 + 4.5 / std::sqrt(r));
+    cap_all = (static_cast<int64_t>(std::ceil(cap)) + 15) / 16 * 16;
+    F.ok = cap <= 2.5 * k_eff && cap_all <= 12288;
     F.est_rank = static_cast<int>(r);
   }
   F.cand_cap = static_cast<int>(cap_all / L.split);
