@@ -182,23 +182,35 @@ __global__ void __launch_bounds__(1024)
     const int groups = (n_valid + 3) >> 2;
     const int s0 = 4 * static_cast<int>(static_cast<int64_t>(groups) * part / parts);
     const int s1 = min(n_valid, 4 * static_cast<int>(static_cast<int64_t>(groups) * (part + 1) / parts));
-    for (int s = s0; s < s1; s += 4) {
-      const int4 k4 = __ldg(ip + (s >> 2));
-      const float4 w4 = __ldg(wp + (s >> 2));
-      const int kk[4] = {k4.x, k4.y, k4.z, k4.w};
-      const float ww[4] = {w4.x, w4.y, w4.z, w4.w};
+    // four groups of four slots are asked for at a time: the loop is bound by the latency of its loads
+    // (measured at 512 query tiles: 0.77 ms one group at a time, 0.69 ms with four, 0.91 ms with eight,
+    // which spread a query tile's writes over too many key tiles at a time)
+    for (int s = s0; s < s1; s += 16) {
+      int4 k4[4];
+      float4 w4[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        if (s + e < n_valid) {
-          const uint32_t key = static_cast<uint32_t>(kk[e]);
-          const uint32_t kt = key >> 7, col = key & 127u;
-          if (kt < static_cast<uint32_t>(nKT)) {            // (a key index beyond the key range is dropped)
-            const uint32_t pos = atomicAdd(&cnt_s[kt], 1u);
-            if (pos < static_cast<uint32_t>(cap))
-              tl_ent[(tile0 + kt) * cap + pos] =
-                  make_uint2(strip_offset(row, col) | (p_offset(row, col) << 16), __float_as_uint(ww[e]));
-            else
-              over = true;
+      for (int g = 0; g < 4; ++g) {
+        const bool in = s + 4 * g < s1;
+        k4[g] = in ? __ldg(ip + (s >> 2) + g) : make_int4(0, 0, 0, 0);
+        w4[g] = in ? __ldg(wp + (s >> 2) + g) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const int kk[4] = {k4[g].x, k4[g].y, k4[g].z, k4[g].w};
+        const float ww[4] = {w4[g].x, w4[g].y, w4[g].z, w4[g].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          if (s + 4 * g + e < s1) {
+            const uint32_t key = static_cast<uint32_t>(kk[e]);
+            const uint32_t kt = key >> 7, col = key & 127u;
+            if (kt < static_cast<uint32_t>(nKT)) {            // (a key index beyond the key range is dropped)
+              const uint32_t pos = atomicAdd(&cnt_s[kt], 1u);
+              if (pos < static_cast<uint32_t>(cap))
+                tl_ent[(tile0 + kt) * cap + pos] =
+                    make_uint2(strip_offset(row, col) | (p_offset(row, col) << 16), __float_as_uint(ww[e]));
+              else
+                over = true;
+            }
           }
         }
       }
