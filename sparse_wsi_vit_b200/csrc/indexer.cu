@@ -935,7 +935,8 @@ struct SelectParams {
   int32_t* st_excl;
   uint32_t* maskbits;          // may be null
 };
-constexpr int kSelWarps = 4;                      // one row per CTA of four warps (~22 KB of shared memory each)
+constexpr int kSelWarps = 4;                      // one row per CTA of four warps (~17 KB of shared memory at 4 k candidates;
+                                                  // eight warps per row measured slower)
 
 __global__ void __launch_bounds__(32 * kSelWarps) dsa_select_kernel(const SelectParams p) {
   extern __shared__ uint32_t sel_smem[];

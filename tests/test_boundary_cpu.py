@@ -56,6 +56,26 @@ def test_size_queries(swv):
     assert L.swv_dsa_attn_scratch_bytes(1, 8, 8192, 65536, ctypes.byref(n)) == 0 and n.value > 0
     assert L.swv_dsa_attn_scratch_bytes(1, 8, 256, 1024, ctypes.byref(n)) == 0 and n.value == 0
     assert L.swv_dsa_attn_scratch_bytes(0, 8, 1, 1, ctypes.byref(n)) == -4
+    # the workspace with room for per-row candidate lists (two-sweep selection): larger than the base
+    # workspace exactly on long key ranges with a selection between about one key in 70 and one in 16
+    def topk_extra(T, K, Tq=None):
+        a, c = ctypes.c_size_t(), ctypes.c_size_t()
+        assert L.swv_dsa_workspace_bytes(1, Tq or T, T, ctypes.byref(a)) == 0
+        assert L.swv_dsa_workspace_bytes_topk(1, Tq or T, T, K, ctypes.byref(c)) == 0
+        assert c.value >= a.value and c.value % 256 == 0
+        return c.value - a.value
+    rows = 65536
+    extra = topk_extra(65536, 2048)
+    assert 2 * rows * 1.6 * 2048 * 4 < extra < 2 * rows * 2.5 * 2048 * 4 + (1 << 20)   # (key, score) lists
+    assert topk_extra(65536, 2048, Tq=8192) * 7 < extra                # sized by the query rows of the call
+    assert topk_extra(131072, 2048) > 0                                # one key in 64
+    assert topk_extra(49152, 1024) > 0                                 # one key in 48
+    assert topk_extra(16384, 512) == 0 and topk_extra(32768, 1024) == 0    # short key ranges
+    assert topk_extra(65536, 8192) == 0                                # one key in 8: too dense
+    assert topk_extra(262144, 2048) == 0                               # one key in 128: the sample is too small
+    assert topk_extra(300000, 8192) == 0                               # beyond 262144 keys
+    assert L.swv_dsa_workspace_bytes_topk(1, 1, 1, 0, ctypes.byref(n)) == -4
+    assert L.swv_dsa_workspace_bytes_topk(1, 1, 1, 1, None) == -1
     # NSA sizes
     assert L.swv_nsa_importance_bytes(1, 2, 65536, 4095, 16, 64, ctypes.byref(n)) == 0
     assert n.value == 2 * 65536 * 1024 * 4
