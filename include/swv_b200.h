@@ -62,7 +62,8 @@ const char* swv_strerror(int code);
 int swv_dsa_workspace_bytes(int B, int Tq, int Tk, size_t* bytes);
 
 /* The same for a call with `top_k` keys per query.  For a sparse selection on a long key range
- * (49152 to 262144 keys, between about one key in 70 and one in 16 selected, top_k <= 4915) it is larger than
+ * (49152 to 262144 keys, between about one key in 70 and one in 16 selected, candidate lists of at
+ * most 12288 entries per row, i.e. top_k up to about 5000) it is larger than
  * swv_dsa_workspace_bytes: swv_dsa_indexer_topk_fwd then has room for per-row candidate lists and
  * selects in two sweeps over the score tiles instead of three (same results).  With the smaller
  * workspace the entry takes the three-sweep form. */
